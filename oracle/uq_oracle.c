@@ -1,0 +1,237 @@
+/*
+ * CPU oracle for the UltraQuant FP4 paged verify-attention path.  TEST INFRASTRUCTURE ONLY:
+ * the tests, the smoke check and the CPU-baseline leg of the benchmark link this file; the
+ * product library never does.
+ *
+ * It restates, in plain C, the reference's CPU algorithm (reference file:line given at each
+ * function).  Parity is pinned: this file reproduces the reference's frozen vectors
+ * (cuda/vectors, sycl/vectors: attention outputs; cuda/vectors cache bytes: encoder) and the
+ * fixtures generated from the reference's own Python functions (see tests/golden/).
+ *
+ * Build: make -C oracle      ->  oracle/libuq_oracle.so
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* e2m1 magnitudes, code & 7 -> value (uqmt/attn.py:46) */
+static const float kGrid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+
+int uqo_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/*
+ * Encoder for one group of 32 values (uqmt/attn.py:52-66, frozen twin tools/gen_vectors.py:18-30).
+ *   amax  = max |x| clamped below at 1e-30
+ *   e     = clamp(ceil(log2(amax / 6)), -127, 127), all in fp32.  log2 is evaluated as the
+ *           correctly rounded fp32 value (double log2 rounded to float), which is what the
+ *           reference's torch CPU kernel returns on every probed point.
+ *   y     = clamp(x / 2^e, -6, 6)
+ *   code  = FIRST index minimising | |y| - grid[i] |  (ties go to the smaller magnitude),
+ *           OR-ed with 8 when y < 0 (so -0.0 has no sign bit, but a negative value that
+ *           rounds to magnitude 0 keeps it: nibble 0x8)
+ *   byte  = e + 127
+ * Packing: low nibble = even element.
+ */
+static void encode_group(const float* x, uint8_t* packed16, uint8_t* scale) {
+  float amax = 0.0f;
+  for (int i = 0; i < 32; i++) {
+    float a = fabsf(x[i]);
+    if (a > amax) amax = a;
+  }
+  if (!(amax >= 1e-30f)) amax = 1e-30f;
+  float r = amax / 6.0f;
+  float e = ceilf((float)log2((double)r));
+  if (e < -127.0f) e = -127.0f;
+  if (e > 127.0f) e = 127.0f;
+  float sc = (float)ldexp(1.0, (int)e); /* exp2(e) in fp32; 2^-127 is a representable denormal */
+  uint8_t codes[32];
+  for (int i = 0; i < 32; i++) {
+    float y = x[i] / sc;
+    if (y < -6.0f) y = -6.0f;
+    if (y > 6.0f) y = 6.0f;
+    float a = fabsf(y);
+    int best = 0;
+    float bd = fabsf(a - kGrid[0]);
+    for (int c = 1; c < 8; c++) {
+      float d = fabsf(a - kGrid[c]);
+      if (d < bd) { bd = d; best = c; }
+    }
+    codes[i] = (uint8_t)(best | ((y < 0.0f) ? 8 : 0));
+  }
+  for (int i = 0; i < 16; i++) packed16[i] = (uint8_t)(codes[2 * i] | (codes[2 * i + 1] << 4));
+  *scale = (uint8_t)((int)e + 127);
+}
+
+/* x: n_groups*32 floats -> packed n_groups*16 bytes, scales n_groups bytes. */
+void uqo_quantize_fp4(const float* x, size_t n_groups, uint8_t* packed, uint8_t* scales) {
+#pragma omp parallel for schedule(static)
+  for (long long g = 0; g < (long long)n_groups; g++) encode_group(x + g * 32, packed + g * 16, scales + g);
+}
+
+/* Decoder (uqmt/attn.py:69-78): +-grid[c & 7] * 2^(s - 127); sign-bit-on-zero decodes to (-)0. */
+static inline float decode_one(uint8_t nib, float sc) {
+  float v = kGrid[nib & 7];
+  return ((nib & 8) ? -v : v) * sc;
+}
+static inline float scale_of(uint8_t s) { return (float)ldexp(1.0, (int)s - 127); }
+
+void uqo_dequantize_fp4(const uint8_t* packed, const uint8_t* scales, size_t n_groups, float* out) {
+#pragma omp parallel for schedule(static)
+  for (long long g = 0; g < (long long)n_groups; g++) {
+    float sc = scale_of(scales[g]);
+    for (int i = 0; i < 16; i++) {
+      uint8_t b = packed[g * 16 + i];
+      out[g * 32 + 2 * i] = decode_one(b & 0xF, sc);
+      out[g * 32 + 2 * i + 1] = decode_one(b >> 4, sc);
+    }
+  }
+}
+
+/*
+ * Append (uqmt/vllm_adapter.py:48-59): encode key/value [T,Hkv,D] and write token t at flat
+ * slot = page * PAGE + offset, i.e. row ((page*Hkv + h)*PAGE + offset) of the four cache arrays.
+ */
+void uqo_append_kv(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const float* key, const float* value,
+                   const int64_t* slots, int T, int HKV, int D, int PAGE) {
+  const int ng = D / 32;
+  for (int t = 0; t < T; t++) {
+    int64_t pg = slots[t] / PAGE, off = slots[t] % PAGE;
+    for (int h = 0; h < HKV; h++) {
+      size_t row = ((size_t)pg * HKV + h) * PAGE + off;
+      for (int g = 0; g < ng; g++) {
+        encode_group(key + ((size_t)t * HKV + h) * D + g * 32, kc + row * (D / 2) + g * 16, ks + row * ng + g);
+        encode_group(value + ((size_t)t * HKV + h) * D + g * 32, vc + row * (D / 2) + g * 16, vs + row * ng + g);
+      }
+    }
+  }
+}
+
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static void decode_row(const uint8_t* codes, const uint8_t* scales, int D, float* out) {
+  for (int g = 0; g < D / 32; g++) {
+    float sc = scale_of(scales[g]);
+    for (int i = 0; i < 16; i++) {
+      uint8_t b = codes[g * 16 + i];
+      out[g * 32 + 2 * i] = decode_one(b & 0xF, sc);
+      out[g * 32 + 2 * i + 1] = decode_one(b >> 4, sc);
+    }
+  }
+}
+
+/*
+ * Attention oracle (uqmt/attn.py:402-422, frozen twin tools/gen_vectors.py:45-65).
+ *   q bf16 bits [B,K,HQ,D]; caches as in cuda/uq_decode.h:3-6; out fp32 [B,K,HQ,D].
+ *   Query j of sequence b sees lim = seq_len - K + j + 1 keys; lim <= 0 -> zero row.
+ * Extension used only by the context-split tests: the sequence may be a shard that starts at
+ * global position pos_offset (keys [0, n_local) of this cache are global positions
+ * pos_offset .. pos_offset + n_local), in which case lim is clamped to the shard, and when
+ * lse_out != NULL the natural-log sum-exp of the scaled scores over the shard is written per
+ * row [B,K,HQ] (-inf for an empty row).  pos_offset = NULL, lse_out = NULL is the reference op.
+ * seq_lens are always GLOBAL lengths (they include the K draft tokens).
+ * n_local[b] (NULL = whole sequence) is the number of keys this cache holds for sequence b.
+ */
+void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
+                   const int32_t* block_table, const int32_t* seq_lens, const int32_t* pos_offset,
+                   const int32_t* n_local, int B, int K, int HQ, int HKV, int D, int PAGE, int max_pages,
+                   float sm_scale, float* out, float* lse_out) {
+  const int G = HQ / HKV, ng = D / 32;
+  memset(out, 0, sizeof(float) * (size_t)B * K * HQ * D);
+  if (lse_out)
+    for (size_t i = 0; i < (size_t)B * K * HQ; i++) lse_out[i] = -INFINITY;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+  for (int b = 0; b < B; b++) {
+    for (int hk = 0; hk < HKV; hk++) {
+      const int n_glob = seq_lens[b];
+      const int off = pos_offset ? pos_offset[b] : 0;
+      int n = n_local ? n_local[b] : n_glob;
+      if (n_glob <= 0 || n <= 0) continue;
+      float* kd = (float*)malloc(sizeof(float) * (size_t)n * D);
+      float* vd = (float*)malloc(sizeof(float) * (size_t)n * D);
+      float* sc = (float*)malloc(sizeof(float) * (size_t)n);
+      for (int t = 0; t < n; t++) {
+        size_t row = ((size_t)block_table[(size_t)b * max_pages + t / PAGE] * HKV + hk) * PAGE + t % PAGE;
+        decode_row(kc + row * (D / 2), ks + row * ng, D, kd + (size_t)t * D);
+        decode_row(vc + row * (D / 2), vs + row * ng, D, vd + (size_t)t * D);
+      }
+      for (int j = 0; j < K; j++) {
+        int lim = n_glob - K + j + 1 - off;
+        if (lim > n) lim = n;
+        if (lim <= 0) continue;
+        for (int g = 0; g < G; g++) {
+          const int h = hk * G + g;
+          const uint16_t* qr = q + (((size_t)b * K + j) * HQ + h) * D;
+          float qf[512];
+          for (int d = 0; d < D; d++) qf[d] = bf16_to_f32(qr[d]);
+          float mx = -INFINITY;
+          for (int t = 0; t < lim; t++) {
+            double acc = 0.0;
+            const float* kr = kd + (size_t)t * D;
+            for (int d = 0; d < D; d++) acc += (double)qf[d] * (double)kr[d];
+            float s = (float)acc * sm_scale;
+            sc[t] = s;
+            if (s > mx) mx = s;
+          }
+          double l = 0.0;
+          for (int t = 0; t < lim; t++) {
+            float p = expf(sc[t] - mx);
+            sc[t] = p;
+            l += p;
+          }
+          float* o = out + (((size_t)b * K + j) * HQ + h) * D;
+          double od[512];
+          for (int d = 0; d < D; d++) od[d] = 0.0;
+          for (int t = 0; t < lim; t++) {
+            const float* vr = vd + (size_t)t * D;
+            const double p = sc[t];
+            for (int d = 0; d < D; d++) od[d] += p * (double)vr[d];
+          }
+          for (int d = 0; d < D; d++) o[d] = (float)(od[d] / l);
+          if (lse_out) lse_out[((size_t)b * K + j) * HQ + h] = mx + (float)log(l);
+        }
+      }
+      free(kd);
+      free(vd);
+      free(sc);
+    }
+  }
+}
+
+/*
+ * Merge of context-split partials (no reference twin; same math as the reference's in-GPU
+ * split-KV combine, cuda/uq_decode.cu:353-388, in natural-log domain):
+ *   out = sum_r exp(lse_r - max) * o_r / sum_r exp(lse_r - max);  all-(-inf) row -> 0.
+ * o [R,rows,D], lse [R,rows] -> out [rows,D].
+ */
+void uqo_merge(const float* o, const float* lse, int R, size_t rows, int D, float* out) {
+  for (size_t i = 0; i < rows; i++) {
+    float mx = -INFINITY;
+    for (int r = 0; r < R; r++)
+      if (lse[(size_t)r * rows + i] > mx) mx = lse[(size_t)r * rows + i];
+    for (int d = 0; d < D; d++) out[i * D + d] = 0.0f;
+    if (mx == -INFINITY) continue;
+    double den = 0.0;
+    for (int r = 0; r < R; r++) den += exp((double)lse[(size_t)r * rows + i] - mx);
+    for (int r = 0; r < R; r++) {
+      double w = exp((double)lse[(size_t)r * rows + i] - mx) / den;
+      if (w == 0.0) continue;
+      for (int d = 0; d < D; d++) out[i * D + d] += (float)(w * o[((size_t)r * rows + i) * D + d]);
+    }
+  }
+}

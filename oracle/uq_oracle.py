@@ -1,0 +1,123 @@
+"""numpy front end of the C oracle (oracle/uq_oracle.c).  TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke check and the benchmark's CPU-baseline leg may import this module;
+the product package never does.  Each function mirrors one reference CPU function:
+  quantize_fp4 / dequantize_fp4   uqmt/attn.py:52-78
+  append_kv                       uqmt/vllm_adapter.py:48-59
+  reference                       uqmt/attn.py:402-422
+Arrays are numpy; bf16 queries are passed as uint16 bit patterns.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build(force=False):
+    """Compile oracle/libuq_oracle.so with gcc (a second or two)."""
+    so = os.path.join(_HERE, "libuq_oracle.so")
+    src = os.path.join(_HERE, "uq_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "-B", "libuq_oracle.so"])
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        so = os.path.join(_HERE, "libuq_oracle.so")
+        if not os.path.exists(so):
+            build()
+        L = ctypes.CDLL(so)
+        vp, i32, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+        L.uqo_max_threads.restype = i32
+        L.uqo_quantize_fp4.argtypes = [vp, sz, vp, vp]
+        L.uqo_dequantize_fp4.argtypes = [vp, vp, sz, vp]
+        L.uqo_append_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
+        L.uqo_reference.argtypes = [vp] * 9 + [i32] * 7 + [f32, vp, vp]
+        L.uqo_merge.argtypes = [vp, vp, i32, sz, i32, vp]
+        _LIB = L
+    return _LIB
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def max_threads():
+    return int(lib().uqo_max_threads())
+
+
+def bf16_bits(x):
+    """fp32 numpy array -> bf16 bit patterns (round to nearest even), as uint16."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + 0x7FFF
+    return ((u + r) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(bits):
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def quantize_fp4(x):
+    """x [..., D] float -> (packed uint8 [..., D/2], scales uint8 [..., D/32])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    D = x.shape[-1]
+    assert D % 32 == 0, "head_dim must be a multiple of 32"
+    packed = np.empty(x.shape[:-1] + (D // 2,), np.uint8)
+    scales = np.empty(x.shape[:-1] + (D // 32,), np.uint8)
+    lib().uqo_quantize_fp4(_p(x), x.size // 32, _p(packed), _p(scales))
+    return packed, scales
+
+
+def dequantize_fp4(packed, scales):
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), np.float32)
+    lib().uqo_dequantize_fp4(_p(packed), _p(scales), scales.size, _p(out))
+    return out
+
+
+def append_kv(kc, ks, vc, vs, key, value, slot_mapping):
+    """In-place append of key/value [T,Hkv,D] at flat slots (page * PAGE + offset)."""
+    for a in (kc, ks, vc, vs):
+        assert a.flags["C_CONTIGUOUS"] and a.dtype == np.uint8
+    key = np.ascontiguousarray(key, dtype=np.float32)
+    value = np.ascontiguousarray(value, dtype=np.float32)
+    slots = np.ascontiguousarray(slot_mapping, dtype=np.int64)
+    T, HKV, D = key.shape
+    lib().uqo_append_kv(_p(kc), _p(ks), _p(vc), _p(vs), _p(key), _p(value), _p(slots), T, HKV, D, kc.shape[2])
+
+
+def reference(q_bits, kc, ks, vc, vs, block_table, seq_lens, sm_scale=None, pos_offset=None, n_local=None,
+              return_lse=False):
+    """q_bits uint16 [B,K,Hq,D] (bf16 bit patterns) -> out fp32 [B,K,Hq,D] (and natural-log lse [B,K,Hq])."""
+    q_bits = np.ascontiguousarray(q_bits, dtype=np.uint16)
+    B, K, HQ, D = q_bits.shape
+    _, HKV, PAGE, _ = kc.shape
+    bt = np.ascontiguousarray(block_table, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    po = None if pos_offset is None else np.ascontiguousarray(pos_offset, dtype=np.int32)
+    nl = None if n_local is None else np.ascontiguousarray(n_local, dtype=np.int32)
+    kc, ks, vc, vs = (np.ascontiguousarray(a, dtype=np.uint8) for a in (kc, ks, vc, vs))
+    out = np.empty((B, K, HQ, D), np.float32)
+    lse = np.empty((B, K, HQ), np.float32) if return_lse else None
+    sm = float(sm_scale) if sm_scale is not None else D ** -0.5
+    lib().uqo_reference(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), _p(po), _p(nl),
+                        B, K, HQ, HKV, D, PAGE, bt.shape[1], sm, _p(out), _p(lse))
+    return (out, lse) if return_lse else out
+
+
+def merge(o, lse):
+    """o [R,rows...,D], lse [R,rows...] (natural log) -> merged [rows...,D]."""
+    o = np.ascontiguousarray(o, dtype=np.float32)
+    lse = np.ascontiguousarray(lse, dtype=np.float32)
+    R, D = o.shape[0], o.shape[-1]
+    rows = lse[0].size
+    out = np.empty(o.shape[1:], np.float32)
+    lib().uqo_merge(_p(o), _p(lse), R, rows, D, _p(out))
+    return out

@@ -1,0 +1,186 @@
+"""Generates the fixtures in this directory.  Needs the reference checkout (default /root/reference,
+or argv[1]); the tests themselves never read the reference, only the .npz files written here.
+
+Two kinds of fixture:
+  ref_cuda_<set>.npz / ref_sycl_<case>.npz   the reference's own frozen known-answer vectors
+      (cuda/vectors, sycl/vectors: cache bytes, page table, seq_lens, bf16 queries, fp32 outputs),
+      repacked unchanged into one compressed file per case set.
+  gen_*.npz   inputs and outputs of the reference's Python functions run here
+      (uqmt.attn.quantize_fp4 / dequantize_fp4 / reference / build_paged_cache,
+       uqmt.vllm_adapter.append_kv), for the cases the frozen vectors do not cover.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+OUT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REF)
+from uqmt.attn import build_paged_cache, dequantize_fp4, quantize_fp4, reference  # noqa: E402
+from uqmt.vllm_adapter import append_kv  # noqa: E402
+
+
+def save(name, **arrs):
+    np.savez_compressed(os.path.join(OUT, name), **arrs)
+    print(name, {k: getattr(v, "shape", v) for k, v in arrs.items()})
+
+
+def repack_cuda_vectors():
+    d = os.path.join(REF, "cuda", "vectors")
+    sets = {}
+    for line in open(os.path.join(d, "manifest.txt")):
+        t = line.split()
+        name, K = t[1], int(t[2])
+        B, HQ, HKV, D, PAGE, pages, max_pages = map(int, t[3:10])
+        s = sets.setdefault(name, dict(meta=np.array([B, HQ, HKV, D, PAGE, pages, max_pages], np.int32), Ks=[]))
+        s["Ks"].append(K)
+    for name, s in sets.items():
+        B, HQ, HKV, D, PAGE, pages, max_pages = (int(x) for x in s["meta"])
+        f = lambda suf, dt: np.fromfile(os.path.join(d, f"{name}_{suf}.bin"), dtype=dt)
+        arrs = dict(meta=s["meta"], Ks=np.array(s["Ks"], np.int32),
+                    kc=f("kc", np.uint8).reshape(pages, HKV, PAGE, D // 2), ks=f("ks", np.uint8).reshape(pages, HKV, PAGE, D // 32),
+                    vc=f("vc", np.uint8).reshape(pages, HKV, PAGE, D // 2), vs=f("vs", np.uint8).reshape(pages, HKV, PAGE, D // 32),
+                    bt=f("bt", np.int32).reshape(B, max_pages), sl=f("sl", np.int32))
+        for K in s["Ks"]:
+            arrs[f"q_K{K}"] = f(f"K{K}_q", np.uint16).reshape(B, K, HQ, D)
+            arrs[f"ref_K{K}"] = f(f"K{K}_ref", np.float32).reshape(B, K, HQ, D)
+        save(f"ref_cuda_{name}.npz", **arrs)
+
+
+SYCL_KEEP = ("b2k16_d128_p32", "b3k2_d64_p16", "b4k3_d128_p64_g1", "edge_short_k4", "b1k8_d128_p64")
+
+
+def repack_sycl_vectors():
+    d = os.path.join(REF, "sycl", "vectors")
+    for line in open(os.path.join(d, "manifest.txt")):
+        t = line.split()
+        name = t[0]
+        if name not in SYCL_KEEP:
+            continue
+        B, K, HQ, HKV, D, PAGE, max_pages = map(int, t[1:8])
+        f = lambda suf, dt: np.fromfile(os.path.join(d, f"{name}.{suf}.bin"), dtype=dt)
+        kc = f("kc", np.uint8)
+        pages = kc.size // (HKV * PAGE * (D // 2))
+        save(f"ref_sycl_{name}.npz", meta=np.array([B, HQ, HKV, D, PAGE, pages, max_pages], np.int32), Ks=np.array([K], np.int32),
+             sm_scale=np.float32(t[8]), kc=kc.reshape(pages, HKV, PAGE, D // 2), ks=f("ks", np.uint8).reshape(pages, HKV, PAGE, D // 32),
+             vc=f("vc", np.uint8).reshape(pages, HKV, PAGE, D // 2), vs=f("vs", np.uint8).reshape(pages, HKV, PAGE, D // 32),
+             bt=f("bt", np.int32).reshape(B, max_pages), sl=f("sl", np.int32),
+             **{f"q_K{K}": f("q", np.uint16).reshape(B, K, HQ, D), f"ref_K{K}": f("ref", np.float32).reshape(B, K, HQ, D)})
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def gen_codec():
+    """Encoder known answers: wide dynamic range, bf16/fp16 inputs (exact rounding ties), all-zero
+    groups, +-1e30 / 1e-30 extremes, signed zeros, and amax on both sides of every power-of-two
+    boundary of amax/6 (the place where a sloppy log2 flips the scale byte)."""
+    g = torch.Generator().manual_seed(11)
+    wide = torch.randn(256, 128, generator=g) * torch.exp2(torch.randint(-40, 40, (256, 1), generator=g).float())
+    b16 = torch.randn(512, 128, generator=g).bfloat16().float()
+    f16 = (torch.randn(256, 128, generator=g) * 3).half().float()
+    ties = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0,
+                         0.0, -0.0, 0.1, -0.1, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 7.0, -7.0, 0.2500001, 0.7499999, 5.0000005, 4.9999995])
+    ties = torch.stack([ties * (2.0 ** k) for k in (-3, 0, 5)] + [ties * 0.9, ties * 1.1]).reshape(-1, 32)
+    special = torch.zeros(8, 32)
+    special[1, 3] = 1e30
+    special[2, 5] = -1e30
+    special[3, 7] = 1e-30
+    special[4, :] = 1e-38
+    special[5, 0] = -0.0
+    special[6, :] = torch.tensor([-1e-9] * 31 + [6.0])
+    special[7, :] = 3e38
+    ks = torch.arange(-120, 121, dtype=torch.float32)
+    base = 6.0 * torch.exp2(ks)
+    ulps = []
+    for j in (-2, -1, 0, 1, 2, 3):
+        u = base.clone().view(torch.int32) + j
+        ulps.append(u.view(torch.float32))
+    edge_amax = torch.cat(ulps)
+    edges = torch.zeros(edge_amax.numel(), 32)
+    edges[:, 0] = edge_amax
+    edges[:, 1] = -edge_amax * 0.41
+    edges[:, 2] = edge_amax * 0.13
+    x32 = torch.cat([ties, special, edges])
+    arrs = {}
+    for name, x in (("wide", wide), ("bf16in", b16), ("fp16in", f16), ("g32", x32)):
+        p, s = quantize_fp4(x)
+        arrs[f"{name}_x"] = x.numpy()
+        arrs[f"{name}_packed"] = p.numpy()
+        arrs[f"{name}_scales"] = s.numpy()
+        arrs[f"{name}_deq"] = dequantize_fp4(p, s).numpy()
+    # every (nibble, scale byte) pair decodes exactly
+    allb = torch.arange(256, dtype=torch.uint8).reshape(1, 16, 16).repeat(256, 1, 1)   # [scale byte, group, 16 packed bytes]
+    arrs["all_packed"] = allb.numpy()
+    arrs["all_scales"] = torch.arange(256, dtype=torch.uint8).reshape(256, 1, 1).repeat(1, 16, 1).numpy()
+    arrs["all_deq"] = dequantize_fp4(torch.from_numpy(arrs["all_packed"]), torch.from_numpy(arrs["all_scales"])).numpy()
+    save("gen_codec.npz", **arrs)
+
+
+def make_case(B, K, HQ, HKV, D, PAGE, seq_lens, seed, keep_raw_pages=0):
+    """Seeded synthetic case: bf16 N(0,1) queries; fp32 N(0,1) K/V with a lognormal(0, 0.5)
+    multiplier per K channel; encoded by the reference encoder; physical pages permuted."""
+    g = torch.Generator().manual_seed(seed)
+    T = max(max(seq_lens), 1)
+    chan = torch.exp(0.5 * torch.randn(1, HKV, 1, D, generator=g))
+    k = torch.randn(B, HKV, T, D, generator=g) * chan
+    v = torch.randn(B, HKV, T, D, generator=g)
+    q = torch.randn(B, K, HQ, D, generator=g).bfloat16()
+    c = build_paged_cache(k, v, page_size=PAGE, seq_lens=seq_lens, shuffle=True, generator=g)
+    ref = reference(q, c.kc, c.ks, c.vc, c.vs, c.block_table, c.seq_lens)
+    arrs = dict(meta=np.array([B, HQ, HKV, D, PAGE, c.kc.shape[0], c.block_table.shape[1]], np.int32), Ks=np.array([K], np.int32),
+                kc=c.kc.numpy(), ks=c.ks.numpy(), vc=c.vc.numpy(), vs=c.vs.numpy(), bt=c.block_table.numpy(), sl=c.seq_lens.numpy(),
+                **{f"q_K{K}": bits(q), f"ref_K{K}": ref.numpy()})
+    if keep_raw_pages:
+        # fp32 K/V of the first logical pages of sequence 0 (+ the physical ids they landed on): encoder check
+        n = keep_raw_pages
+        arrs["raw_k"] = k[0, :, : n * PAGE].reshape(HKV, n, PAGE, D).permute(1, 0, 2, 3).contiguous().numpy()
+        arrs["raw_v"] = v[0, :, : n * PAGE].reshape(HKV, n, PAGE, D).permute(1, 0, 2, 3).contiguous().numpy()
+        arrs["raw_pages"] = c.block_table[0, :n].numpy()
+    return arrs
+
+
+def gen_cases():
+    # configuration 0 of the benchmark contract: the CPU-runnable parity case
+    save("gen_cfg0.npz", **make_case(2, 4, 8, 2, 128, 64, [1000, 777], 0, keep_raw_pages=4))
+    # head_dim 256 (136 B per head per token): no frozen vector exists for it
+    save("gen_d256.npz", **make_case(2, 8, 16, 2, 256, 64, [700, 130], 1005))
+    # K=8, G=8 (64 rows) with ragged lengths incl. an empty sequence and seq_len < K
+    save("gen_k8g8.npz", **make_case(4, 8, 16, 2, 128, 64, [515, 0, 5, 128], 1006))
+    # G=7 (not a power of two), K=3, PAGE=32
+    save("gen_g7.npz", **make_case(2, 3, 14, 2, 128, 32, [100, 33], 1007))
+    # D=64, PAGE=64, K=8
+    save("gen_d64.npz", **make_case(2, 8, 16, 2, 64, 64, [321, 64], 1008))
+
+
+def gen_append():
+    """append_kv known answer: 8 new bf16 tokens per sequence written through a permuted page table."""
+    g = torch.Generator().manual_seed(21)
+    pages, HKV, PAGE, D, B, Kn = 12, 2, 64, 128, 3, 8
+    kc = torch.randint(0, 256, (pages, HKV, PAGE, D // 2), generator=g, dtype=torch.uint8)
+    ks = torch.randint(100, 140, (pages, HKV, PAGE, D // 32), generator=g, dtype=torch.uint8)
+    vc = torch.randint(0, 256, (pages, HKV, PAGE, D // 2), generator=g, dtype=torch.uint8)
+    vs = torch.randint(100, 140, (pages, HKV, PAGE, D // 32), generator=g, dtype=torch.uint8)
+    before = [t.clone() for t in (kc, ks, vc, vs)]
+    bt = torch.randperm(pages, generator=g).reshape(B, 4)
+    seq = torch.tensor([70, 8, 250])   # lengths AFTER the append; new tokens are the last 8 positions
+    pos = torch.stack([torch.arange(int(n) - Kn, int(n)) for n in seq])          # [B, 8]
+    slots = (bt.gather(1, pos // PAGE) * PAGE + pos % PAGE).reshape(-1)
+    key = (torch.randn(B * Kn, HKV, D, generator=g) * 2).bfloat16()
+    val = torch.randn(B * Kn, HKV, D, generator=g).bfloat16()
+    key[3, 1, 32:64] = 0   # an all-zero group
+    append_kv(kc, ks, vc, vs, key, val, slots)
+    save("gen_append.npz", kc0=before[0].numpy(), ks0=before[1].numpy(), vc0=before[2].numpy(), vs0=before[3].numpy(),
+         key=bits(key), value=bits(val), slots=slots.numpy().astype(np.int64),
+         kc1=kc.numpy(), ks1=ks.numpy(), vc1=vc.numpy(), vs1=vs.numpy())
+
+
+if __name__ == "__main__":
+    repack_cuda_vectors()
+    repack_sycl_vectors()
+    gen_codec()
+    gen_cases()
+    gen_append()
