@@ -1,0 +1,190 @@
+// Host side of libuq_b200: argument checks, kernel choice, and the exported entry points — the
+// reference's C++ surface (include/uq_decode.h) and the C ABI (include/uq_b200.h).
+//
+// Dispatch (the reference's is a template tree over variant / BLOCK_M / warps / stages, reference
+// cuda/uq_decode.cu:402-626; this library has two kernels and ignores those hints):
+//   tcgen05 kernel  when head_dim, page size and row count are ones it serves (uq_verify_tc.cu)
+//   CUDA-core kernel otherwise, and always for few query rows (uq_verify_fma.cu)
+// followed by the combine kernel.  Every check happens before the first launch, so
+// cudaErrorInvalidValue means nothing was enqueued (callers of the reference skip on it).
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+
+#include "uq_b200.h"
+#include "uq_common.cuh"
+#include "uq_decode.h"
+
+__device__ unsigned int g_uq_status[4];
+
+cudaError_t uq_append_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, cudaStream_t);
+cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
+cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
+bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
+int uq_verify_tc_splits(const UQParams&, const UQLaunch&);
+cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, cudaStream_t);
+cudaError_t uq_merge_dispatch(const float*, const float*, int, size_t, int, void*, cudaStream_t);
+
+namespace {
+
+std::atomic<unsigned long long> g_launches{0};
+thread_local int t_last_path = 0;
+thread_local cudaEvent_t t_ev_before = nullptr, t_ev_after = nullptr;
+
+int pow2ceil(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// UQ_B200_CFG="path=fma" or "path=tc" forces a kernel (a forced tc on an unserved shape is invalid value).
+int forced_path() {
+  const char* e = std::getenv("UQ_B200_CFG");
+  if (!e) return 0;
+  if (std::strstr(e, "path=fma")) return 1;
+  if (std::strstr(e, "path=tc")) return 2;
+  return 0;
+}
+
+// Device address of the current device's status record (the symbol's name is only a host-side handle).
+unsigned int* status_ptr() {
+  static unsigned int* cached[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_uq_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    cached[dev] = reinterpret_cast<unsigned int*>(ptr);
+  }
+  return cached[dev];
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+bool shape_ok(const UQParams& p) {
+  if (p.fmt != 0) return false;   // NVFP4 is not served
+  if (p.B < 0 || p.K < 1 || p.HQ < 1 || p.HKV < 1 || p.HQ % p.HKV) return false;
+  if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
+  if (p.PAGE < 1 || p.max_pages < 0) return false;
+  if (p.nsplit < 1 || p.nsplit > 128) return false;
+  if (uq_block_m(p.K, p.HQ, p.HKV) > 128) return false;   // the reference's limit on rows per tile
+  return p.q && p.kc && p.ks && p.vc && p.vs && p.block_table && p.seq_lens && p.mo && p.ml;
+}
+
+cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s) {
+  if (!shape_ok(p)) return cudaErrorInvalidValue;
+  if (!o_part && !p.out) return cudaErrorInvalidValue;
+  if (p.B == 0) return cudaSuccess;
+  UQLaunch x{};
+  x.pos_offset = pos_offset;
+  x.G = p.HQ / p.HKV;
+  x.rows = p.K * x.G;
+  x.BM = uq_block_m(p.K, p.HQ, p.HKV);
+  x.sc2 = p.sm_scale * 1.4426950408889634f;
+  x.status = status_ptr();
+  if (!x.status) return cudaErrorInitializationError;
+  const int forced = forced_path();
+  bool tc = forced != 1 && uq_verify_tc_serves(p, x);
+  if (forced == 2 && !tc) return cudaErrorInvalidValue;
+  cudaError_t e;
+  const bool timed = t_ev_before && t_ev_after;
+  if (timed) cudaEventRecord(t_ev_before, s);
+  if (tc) {
+    x.ns_eff = uq_verify_tc_splits(p, x);
+    e = uq_verify_tc_dispatch(p, x, s);
+    t_last_path = 2;
+  } else {
+    // enough CTAs for ~4 per SM, never more slots than the caller's scratch holds or pages exist
+    const int want = std::max(1, 4 * sm_count() / std::max(1, p.B * p.HKV));
+    x.ns_eff = std::max(1, std::min(std::min(p.nsplit, want), std::max(1, p.max_pages)));
+    e = uq_verify_fma_dispatch(p, x, s);
+    t_last_path = 1;
+  }
+  if (timed) cudaEventRecord(t_ev_after, s);
+  if (e != cudaSuccess) return e;
+  g_launches += 2;
+  return uq_combine_dispatch(p, x, o_part, lse_part, s);
+}
+
+}  // namespace
+
+// ---- the reference's C++ surface -------------------------------------------------------------------
+int uq_block_m(int K, int HQ, int HKV) { return std::max(16, pow2ceil(K * pow2ceil(HQ / std::max(1, HKV)))); }
+size_t uq_mo_elems(const UQParams& p) { return (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV) * p.D; }
+size_t uq_ml_elems(const UQParams& p) { return (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV); }
+size_t uq_workspace_bytes(const UQParams& p) { return (uq_mo_elems(p) + uq_ml_elems(p)) * sizeof(float); }
+int uq_has_sm90() { return 0; }
+
+cudaError_t uq_decode_launch(const UQParams& p, int /*nwarps*/, int /*stages*/, cudaStream_t s) { return run(p, nullptr, nullptr, nullptr, s); }
+
+cudaError_t uq_decode_launch_ws(UQParams p, void* workspace, int nwarps, int stages, cudaStream_t s) {
+  if (!workspace) return cudaErrorInvalidValue;
+  p.mo = reinterpret_cast<float*>(workspace);
+  p.ml = p.mo + uq_mo_elems(p);
+  return uq_decode_launch(p, nwarps, stages, s);
+}
+
+// ---- the C ABI ---------------------------------------------------------------------------------------
+extern "C" {
+
+int uqb_block_m(int K, int HQ, int HKV) { return uq_block_m(K, HQ, HKV); }
+size_t uqb_mo_elems(const UQParams* p) { return uq_mo_elems(*p); }
+size_t uqb_ml_elems(const UQParams* p) { return uq_ml_elems(*p); }
+size_t uqb_workspace_bytes(const UQParams* p) { return uq_workspace_bytes(*p); }
+int uqb_has_sm90(void) { return 0; }
+
+int uqb_decode_launch(const UQParams* p, int nwarps, int stages, void* stream) {
+  if (!p) return (int)cudaErrorInvalidValue;
+  return (int)uq_decode_launch(*p, nwarps, stages, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uqb_decode_launch_ws(const UQParams* p, void* workspace, int nwarps, int stages, void* stream) {
+  if (!p) return (int)cudaErrorInvalidValue;
+  return (int)uq_decode_launch_ws(*p, workspace, nwarps, stages, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value, const int64_t* slots,
+                      int T, int HKV, int D, int PAGE, int dtype, void* stream) {
+  cudaError_t e = uq_append_dispatch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && T > 0) g_launches += 1;
+  return (int)e;
+}
+
+int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, float* o_part, float* lse2_part, void* stream) {
+  if (!p || !o_part || !lse2_part) return (int)cudaErrorInvalidValue;
+  return (int)run(*p, pos_offset, o_part, lse2_part, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16, void* stream) {
+  cudaError_t e = uq_merge_dispatch(o_parts, lse2_parts, R, rows, D, out_bf16, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && rows > 0) g_launches += 1;
+  return (int)e;
+}
+
+int uqb_last_status(uint32_t out4[4]) {
+  if (!out4) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemcpyFromSymbol(out4, g_uq_status, 4 * sizeof(unsigned int));
+  if (e != cudaSuccess) return (int)e;
+  const unsigned int zero[4] = {0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(g_uq_status, zero, sizeof(zero));
+}
+
+int uqb_last_path(void) { return t_last_path; }
+void uqb_debug_events(void* before, void* after) {
+  t_ev_before = reinterpret_cast<cudaEvent_t>(before);
+  t_ev_after = reinterpret_cast<cudaEvent_t>(after);
+}
+unsigned long long uqb_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

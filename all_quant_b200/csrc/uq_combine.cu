@@ -1,0 +1,112 @@
+// Log-sum-exp combine of split-KV partials (the reference's uq_reduce_kernel, reference
+// cuda/uq_decode.cu:353-388, restated): per query row,
+//   mx = max_s lse_s;  w_s = 2^(lse_s - mx);  out = sum_s w_s * o_s / sum_s w_s;  all -inf -> zeros.
+// One warp per output row; lanes stride the head dimension.  Three outputs are served by the same
+// arithmetic: bf16 [B,K,Hq,D] (the op's result), fp32 partial + lse (one shard of a context split), and
+// the merge of R shards' partials into bf16.
+#include "uq_common.cuh"
+
+namespace {
+
+// Partials of (b, hk) live in scratch slots s = 0..ns_eff-1, rows r = j*G + g with stride BM.
+template <bool kPartialOut>
+__global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const UQLaunch x, float* __restrict__ o_part,
+                                                         float* __restrict__ lse_part) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);   // over [B, K, HQ]
+  const int lane = threadIdx.x & 31;
+  const int total = p.B * p.K * p.HQ;
+  if (row >= total) return;
+  const int h = row % p.HQ, j = (row / p.HQ) % p.K, b = row / (p.HQ * p.K);
+  const int hk = h / x.G, r = j * x.G + (h % x.G);
+  const int D = p.D;
+  const size_t slot0 = uq_slot(p, b, hk, 0);
+  float mx = -INFINITY;
+  for (int s = 0; s < x.ns_eff; s++) mx = fmaxf(mx, p.ml[(slot0 + s) * x.BM + r]);
+  float acc[8];   // D <= 256: 8 channels per lane
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  float den = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < x.ns_eff; s++) {
+      const float lse = p.ml[(slot0 + s) * x.BM + r];
+      if (lse == -INFINITY) continue;   // an empty split never wrote its o
+      const float w = exp2f(lse - mx);
+      den += w;
+      const float* o = p.mo + ((slot0 + s) * x.BM + r) * (size_t)D;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < D) acc[i] = fmaf(w, o[d], acc[i]);
+      }
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  if (kPartialOut) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int d = lane + 32 * i;
+      if (d < D) o_part[(size_t)row * D + d] = acc[i] * inv;
+    }
+    if (lane == 0) lse_part[row] = den > 0.f ? mx + log2f(den) : -INFINITY;
+  } else {
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * D;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int d = lane + 32 * i;
+      if (d < D) out[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+  }
+}
+
+// Merge of R shards: o [R, rows, D], lse2 [R, rows] -> bf16 [rows, D].
+__global__ void __launch_bounds__(128) uq_merge_kernel(const float* __restrict__ o, const float* __restrict__ lse, int R, size_t rows, int D,
+                                                       __nv_bfloat16* __restrict__ out) {
+  const size_t row = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float mx = -INFINITY;
+  for (int r = 0; r < R; r++) mx = fmaxf(mx, lse[(size_t)r * rows + row]);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  float den = 0.f;
+  if (mx != -INFINITY) {
+    for (int r = 0; r < R; r++) {
+      const float l = lse[(size_t)r * rows + row];
+      if (l == -INFINITY) continue;
+      const float w = exp2f(l - mx);
+      den += w;
+      const float* src = o + ((size_t)r * rows + row) * D;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < D) acc[i] = fmaf(w, src[d], acc[i]);
+      }
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int d = lane + 32 * i;
+    if (d < D) out[row * D + d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+}  // namespace
+
+cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_part, float* lse_part, cudaStream_t s) {
+  const int rows = p.B * p.K * p.HQ;
+  if (rows == 0) return cudaSuccess;
+  if (o_part)
+    uq_combine_kernel<true><<<(rows + 3) / 4, 128, 0, s>>>(p, x, o_part, lse_part);
+  else
+    uq_combine_kernel<false><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t uq_merge_dispatch(const float* o, const float* lse, int R, size_t rows, int D, void* out, cudaStream_t s) {
+  if (!o || !lse || !out || R < 1 || D < 32 || D > 256 || D % 32) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, lse, R, rows, D, reinterpret_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError();
+}

@@ -1,0 +1,59 @@
+// Shared device/host helpers of libuq_b200: the FP4 codec arithmetic, the partial-slot layout of the
+// caller's scratch, and the status record that bounded waits write to.
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "uq_params.h"
+
+#define UQ_DEV __device__ __forceinline__
+
+// ---- what the host adds to UQParams for one launch -------------------------------------------------
+struct UQLaunch {
+  const int32_t* pos_offset;  // [B] global position of shard-local key 0 (nullptr = 0)
+  int ns_eff;                 // partial slots actually used per (sequence, kv head): <= p.nsplit
+  int G;                      // Hq / Hkv
+  int rows;                   // K * G query rows per (sequence, kv head)
+  int BM;                     // row stride of the scratch (uq_block_m)
+  float sc2;                  // sm_scale * log2(e): scores live in the exp2 domain
+  unsigned int* status;       // this device's status record (4 words), see uq_report
+};
+
+// Scratch slot (b, hk, s): rows are r = j * G + g (draft j, head g of the group), row stride BM.
+UQ_DEV size_t uq_slot(const UQParams& p, int b, int hk, int s) { return ((size_t)b * p.HKV + hk) * p.nsplit + s; }
+
+// Keys of sequence b held by this cache (whole context, or one shard of it).
+UQ_DEV int uq_n_local(const UQParams& p, const UQLaunch& x, int b, int* off_out) {
+  const int n = p.seq_lens[b];
+  const int off = x.pos_offset ? x.pos_offset[b] : 0;
+  *off_out = off;
+  long long cap = (long long)p.max_pages * p.PAGE;
+  long long nl = (long long)n - off;
+  nl = nl < 0 ? 0 : (nl > cap ? cap : nl);
+  return (int)nl;
+}
+
+// ---- status record ------------------------------------------------------------------------------------
+// [0] code (0 none, 1 barrier wait ran out), [1] block, [2] barrier id, [3] tile.  First writer wins.
+UQ_DEV void uq_report(unsigned int* status, unsigned code, unsigned bar, unsigned tile) {
+  if (atomicCAS(&status[0], 0u, code) == 0u) {
+    status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    status[2] = bar;
+    status[3] = tile;
+  }
+}
+
+// ---- codec ------------------------------------------------------------------------------------------
+// UE8M0 byte -> fp32 2^(s-127).  s = 0 gives the denormal 2^-127; s = 255 gives 2^128 = +inf in fp32
+// (the reference's torch.exp2 does the same).
+UQ_DEV float uq_scale_f32(unsigned s) {
+  return s == 0 ? __int_as_float(0x00400000) : (s == 255 ? __int_as_float(0x7f800000) : __int_as_float((int)(s << 23)));
+}
+
+// e2m1 nibble -> exact fp32 value: (sign | code3 << 22) read as fp32 is value * 2^-126 (a denormal for
+// 0.5, zero for 0), and one multiply by 2^126 normalises it without rounding.
+UQ_DEV float uq_e2m1_f32(unsigned nib) {
+  return __int_as_float((int)(((nib & 8u) << 28) | ((nib & 7u) << 22))) * 8.507059173023462e37f;
+}

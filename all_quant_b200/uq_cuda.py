@@ -1,0 +1,289 @@
+"""Python API of the B200 UltraQuant verify/decode attention, mirroring the reference's
+`cuda/uq_cuda.py` (reference cuda/uq_cuda.py:10-66): `ext`, `auto_nsplit`, `uq_decode_cuda`,
+`workspace_floats`, plus the append hooks `append_kv` (reference uqmt/vllm_adapter.py:48-59) and
+`quantize_on_write` (reference uqmt/quant.py:197-206) and the context-split pair
+`uq_decode_partial` / `uq_merge`, which the reference does not have.
+
+Everything goes through the C ABI of libuq_b200.so (include/uq_b200.h) with raw device pointers and
+the current CUDA stream; torch only owns the memory.  There is no CPU or eager fallback: if the
+library is missing or the device is not CUDA, the call raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libuq_b200.so")
+_lib = None
+_ext = None
+
+cudaErrorInvalidValue = 1
+
+
+class UQParams(ctypes.Structure):
+    """ctypes mirror of `struct UQParams` (include/uq_params.h; reference cuda/uq_decode.h:11-30)."""
+    _fields_ = [("q", ctypes.c_void_p), ("kc", ctypes.c_void_p), ("ks", ctypes.c_void_p), ("vc", ctypes.c_void_p),
+                ("vs", ctypes.c_void_p), ("block_table", ctypes.c_void_p), ("seq_lens", ctypes.c_void_p),
+                ("mo", ctypes.c_void_p), ("ml", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("B", ctypes.c_int), ("K", ctypes.c_int), ("HQ", ctypes.c_int), ("HKV", ctypes.c_int), ("D", ctypes.c_int),
+                ("PAGE", ctypes.c_int), ("max_pages", ctypes.c_int), ("nsplit", ctypes.c_int), ("sm_scale", ctypes.c_float),
+                ("variant", ctypes.c_int), ("mb", ctypes.c_int), ("fmt", ctypes.c_int), ("k_ts", ctypes.c_float),
+                ("v_ts", ctypes.c_float)]
+
+
+EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_merge_launch", "uqb_last_status",
+           "uqb_last_path", "uqb_launch_count", "uqb_debug_events")
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built (python -m all_quant_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(f"{_LIB_PATH} is missing: build it with `python -m all_quant_b200.build` (there is no fallback path)")
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+        pp = ctypes.POINTER(UQParams)
+        L.uqb_block_m.argtypes = [i, i, i]
+        for n in ("uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes"):
+            getattr(L, n).argtypes = [pp]
+            getattr(L, n).restype = sz
+        L.uqb_decode_launch.argtypes = [pp, i, i, vp]
+        L.uqb_decode_launch_ws.argtypes = [pp, vp, i, i, vp]
+        L.uqb_append_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
+        L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
+        L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
+        L.uqb_last_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+        L.uqb_launch_count.restype = ctypes.c_ulonglong
+        L.uqb_debug_events.argtypes = [vp, vp]
+        L.uqb_debug_events.restype = None
+        _lib = L
+    return _lib
+
+
+def _check(err, what):
+    if err != 0:
+        name = {1: "cudaErrorInvalidValue (shape not served / bad argument)"}.get(err, f"cudaError {err}")
+        raise RuntimeError(f"{what} failed: {name}")
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("uq_cuda: tensors must live on a CUDA device (no CPU path in this library)")
+
+
+def _params(q, kc, ks, vc, vs, bt, sl, nsplit, sm_scale, variant=0, mb=0, fmt=0, k_ts=1.0, v_ts=1.0):
+    B, K, HQ, D = q.shape
+    p = UQParams()
+    p.q, p.kc, p.ks, p.vc, p.vs = q.data_ptr(), kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr()
+    p.block_table, p.seq_lens = bt.data_ptr(), sl.data_ptr()
+    p.B, p.K, p.HQ, p.D = B, K, HQ, D
+    p.HKV, p.PAGE, p.max_pages, p.nsplit = kc.shape[1], kc.shape[2], bt.shape[1], int(nsplit)
+    p.sm_scale, p.variant, p.mb, p.fmt, p.k_ts, p.v_ts = float(sm_scale), int(variant), int(mb), int(fmt), float(k_ts), float(v_ts)
+    return p
+
+
+class _Ext:
+    """Stand-in for the reference's pybind module `uq_cuda_ext` (reference cuda/uq_ext.cpp:6-37): same
+    four functions, same positional arguments, same checks and messages."""
+
+    @staticmethod
+    def block_m(K, HQ, HKV):
+        return int(lib().uqb_block_m(int(K), int(HQ), int(HKV)))
+
+    @staticmethod
+    def has_sm90():
+        return 0
+
+    @staticmethod
+    def workspace_floats(B, K, HQ, HKV, D, nsplit):
+        p = UQParams()
+        p.B, p.K, p.HQ, p.HKV, p.D, p.nsplit = int(B), int(K), int(HQ), int(HKV), int(D), int(nsplit)
+        return int(lib().uqb_mo_elems(ctypes.byref(p)) + lib().uqb_ml_elems(ctypes.byref(p)))
+
+    @staticmethod
+    def decode(q, kc, ks, vc, vs, bt, sl, nsplit, nwarps, stages, variant, mb, sm_scale, mo=None, ml=None, out=None,
+               fmt=0, k_ts=1.0, v_ts=1.0):
+        if not (q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous()):
+            raise RuntimeError("q must be contiguous bf16 cuda")
+        if bt.dtype != torch.int32 or sl.dtype != torch.int32:
+            raise RuntimeError("bt/sl must be int32")
+        _need_cuda(kc, ks, vc, vs, bt, sl)
+        p = _params(q, kc, ks, vc, vs, bt, sl, nsplit, sm_scale, variant, mb, fmt, k_ts, v_ts)
+        L = lib()
+        n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
+        if mo is None:
+            mo = torch.empty(n_mo, dtype=torch.float32, device=q.device)
+        if ml is None:
+            ml = torch.empty(n_ml, dtype=torch.float32, device=q.device)
+        if out is None:
+            out = torch.empty_like(q)
+        if mo.numel() < n_mo or ml.numel() < n_ml:
+            raise RuntimeError("scratch too small")
+        p.mo, p.ml, p.out = mo.data_ptr(), ml.data_ptr(), out.data_ptr()
+        with torch.cuda.device(q.device):
+            err = L.uqb_decode_launch(ctypes.byref(p), int(nwarps), int(stages), _stream(q))
+        _check(err, "uq_decode_launch")
+        return out
+
+
+def ext(verbose=False):
+    """The op module (reference cuda/uq_cuda.py:10-31 JIT-builds a pybind extension; here it is a thin
+    object over the prebuilt C-ABI library)."""
+    global _ext
+    if _ext is None:
+        lib()
+        _ext = _Ext()
+    return _ext
+
+
+def auto_nsplit(B, HKV, n_pages, sms, K=1, G=8):
+    """Default number of partial slots (reference cuda/uq_cuda.py:34-37): 4 CTAs per SM, at most one per page, at most 128."""
+    target = 4 * sms
+    want = max(1, target // max(1, B * HKV))
+    return max(1, min(want, n_pages, 128))
+
+
+def workspace_floats(B, K, HQ, HKV, D, nsplit):
+    """fp32 element count of the scratch (mo then ml) for uq_decode_cuda(..., workspace=...) (reference cuda/uq_cuda.py:64-66)."""
+    return ext().workspace_floats(B, K, HQ, HKV, D, nsplit)
+
+
+def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nsplit=None, nwarps=0, stages=0, variant=0, mb=0,
+                   sm_scale=None, out=None, fmt=0, k_ts=1.0, v_ts=1.0, workspace=None):
+    """Fused K-query verify attention over the paged FP4 cache (reference cuda/uq_cuda.py:40-61).
+
+    q bf16 [B,K,Hq,D]; kc/vc uint8 [pages,Hkv,PAGE,D/2]; ks/vs uint8 [pages,Hkv,PAGE,D/32]; block_table
+    int [B,max_pages]; seq_lens int [B] including the K draft tokens.  Returns bf16 [B,K,Hq,D].
+    fused=False is the reference's no-sharing mode: K independent single-query problems over B*K
+    pseudo-sequences (the cache is read K times)."""
+    _need_cuda(q, kc, ks, vc, vs, block_table, seq_lens)
+    B, K, HQ, D = q.shape
+    HKV = kc.shape[1]
+    sm_scale = sm_scale if sm_scale is not None else D ** -0.5
+    if seq_lens.dtype != torch.int32:
+        seq_lens = seq_lens.to(torch.int32)
+    block_table = block_table.to(torch.int32)
+    q = q.contiguous()
+    if nsplit is None:
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+    e = ext()
+    mo = ml = None
+    if workspace is not None:   # caller-owned fp32 scratch, nothing is allocated inside
+        nm = e.workspace_floats(B, K, HQ, HKV, D, nsplit)
+        BM = e.block_m(K, HQ, HKV)
+        mo = workspace[: nm - B * HKV * nsplit * BM].view(-1)
+        ml = workspace[nm - B * HKV * nsplit * BM: nm]
+    if fused or K == 1:
+        return e.decode(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, nwarps, stages, variant, mb, sm_scale, mo, ml, out, fmt, k_ts, v_ts)
+    qs = q.reshape(B * K, 1, HQ, D)
+    bt = block_table.repeat_interleave(K, 0)
+    sl = (seq_lens.repeat_interleave(K) - K + torch.arange(K, device=q.device).repeat(B) + 1).to(torch.int32)
+    return e.decode(qs, kc, ks, vc, vs, bt, sl, nsplit, nwarps, stages, variant, mb, sm_scale, None, None, None, fmt, k_ts, v_ts).reshape(B, K, HQ, D)
+
+
+_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def append_kv(kc, ks, vc, vs, key, value, slot_mapping):
+    """Quantize new key/value [T,Hkv,D] and write them at flat slots (slot = physical_page * PAGE + offset):
+    the cache-append hook of an engine (reference uqmt/vllm_adapter.py:48-59).  One kernel launch for both streams;
+    bytes identical to the reference encoder.  Negative slots are skipped."""
+    _need_cuda(kc, ks, vc, vs, key, value, slot_mapping)
+    if key.dtype not in _DTYPE or value.dtype != key.dtype:
+        raise RuntimeError("key/value must both be fp32, bf16 or fp16")
+    T, HKV, D = key.shape
+    key, value = key.contiguous(), value.contiguous()
+    slots = slot_mapping.to(torch.int64).contiguous()
+    for t in (kc, ks, vc, vs):
+        if not t.is_contiguous() or t.dtype != torch.uint8:
+            raise RuntimeError("cache tensors must be contiguous uint8")
+    with torch.cuda.device(key.device):
+        err = lib().uqb_append_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                      slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], _stream(key))
+    _check(err, "uq_append_launch")
+
+
+def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):
+    """Quantize x [N,Hkv,D] and scatter into `code` [pages,Hkv,PAGE,D/2] / `scale` [pages,Hkv,PAGE,D/32] at flat
+    slots [N] (reference uqmt/quant.py:197-206).  Only the reference's default rule "ceil" (the cache's own
+    encoder) is served."""
+    if rule != "ceil":
+        raise NotImplementedError("only rule='ceil' (the UltraQuant cache encoder) is served")
+    _need_cuda(x, code, scale, slots)
+    if x.dtype not in _DTYPE:
+        raise RuntimeError("x must be fp32, bf16 or fp16")
+    N, HKV, D = x.shape
+    x = x.contiguous()
+    sl = slots.to(torch.int64).contiguous()
+    with torch.cuda.device(x.device):
+        err = lib().uqb_append_launch(code.data_ptr(), scale.data_ptr(), None, None, x.data_ptr(), None, sl.data_ptr(),
+                                      N, HKV, D, code.shape[2], _DTYPE[x.dtype], _stream(x))
+    _check(err, "uq_append_launch")
+
+
+def uq_decode_partial(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset=None, *, nsplit=None, sm_scale=None, workspace=None):
+    """Attention over one context shard (the cache and block_table hold only this shard's pages; shard-local key 0 of
+    sequence b is global position pos_offset[b]; seq_lens are global).  Returns (o fp32 [B,K,Hq,D] normalised,
+    lse2 fp32 [B,K,Hq] in the log2 domain, -inf for rows that see nothing here).  Not in the reference."""
+    _need_cuda(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset)
+    B, K, HQ, D = q.shape
+    HKV = kc.shape[1]
+    sm_scale = sm_scale if sm_scale is not None else D ** -0.5
+    seq_lens = seq_lens.to(torch.int32)
+    block_table = block_table.to(torch.int32).contiguous()
+    q = q.contiguous()
+    if nsplit is None:
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+    p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale)
+    L = lib()
+    n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
+    if workspace is None:
+        workspace = torch.empty(n_mo + n_ml, dtype=torch.float32, device=q.device)
+    if workspace.numel() < n_mo + n_ml:
+        raise RuntimeError("scratch too small")
+    p.mo, p.ml = workspace.data_ptr(), workspace.data_ptr() + 4 * n_mo
+    o = torch.empty(B, K, HQ, D, dtype=torch.float32, device=q.device)
+    lse = torch.empty(B, K, HQ, dtype=torch.float32, device=q.device)
+    po = None if pos_offset is None else pos_offset.to(torch.int32).contiguous()
+    with torch.cuda.device(q.device):
+        err = L.uqb_decode_partial_launch(ctypes.byref(p), None if po is None else po.data_ptr(), o.data_ptr(), lse.data_ptr(), _stream(q))
+    _check(err, "uq_decode_partial_launch")
+    return o, lse
+
+
+def uq_merge(o_parts, lse2_parts, out=None):
+    """Merge R shards' partials: o_parts fp32 [R,...,D], lse2_parts fp32 [R,...] -> bf16 [...,D].  Not in the reference."""
+    _need_cuda(o_parts, lse2_parts)
+    o_parts, lse2_parts = o_parts.contiguous(), lse2_parts.contiguous()
+    R, D = o_parts.shape[0], o_parts.shape[-1]
+    rows = lse2_parts[0].numel()
+    if out is None:
+        out = torch.empty(o_parts.shape[1:], dtype=torch.bfloat16, device=o_parts.device)
+    with torch.cuda.device(o_parts.device):
+        err = lib().uqb_merge_launch(o_parts.data_ptr(), lse2_parts.data_ptr(), R, rows, D, out.data_ptr(), _stream(o_parts))
+    _check(err, "uq_merge_launch")
+    return out
+
+
+def last_status():
+    """(code, block, barrier, tile) of the first device-side wait that ran out since the last call; code 0 = none."""
+    a = (ctypes.c_uint32 * 4)()
+    _check(lib().uqb_last_status(a), "uq_last_status")
+    return tuple(int(v) for v in a)
+
+
+def last_path():
+    """1 = CUDA-core kernel, 2 = tcgen05 kernel (the last decode call of this thread)."""
+    return int(lib().uqb_last_path())
+
+
+def launch_count():
+    return int(lib().uqb_launch_count())

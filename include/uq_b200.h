@@ -1,0 +1,81 @@
+/* C ABI of libuq_b200.so: paged UltraQuant FP4 verify/decode attention and KV append for NVIDIA B200
+ * (sm_100a).  Plain pointers and sizes only; every function returns a cudaError_t value as int
+ * (0 = success, 1 = cudaErrorInvalidValue = "this shape is not served", nothing was enqueued).
+ * All launches are asynchronous on `stream` (a cudaStream_t passed as void*), allocate nothing and
+ * never read device memory on the host.  Pointers are caller-owned device memory.
+ *
+ * Each function names the reference interface it stands in for (reference file:line), or says that
+ * the reference has no counterpart. */
+#ifndef UQ_B200_H_
+#define UQ_B200_H_
+#include <stddef.h>
+#include <stdint.h>
+
+#include "uq_params.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- the reference's surface, C linkage ------------------------------------------------------ */
+
+/* uq_block_m (reference cuda/uq_decode.h:33, cuda/uq_decode.cu:398) */
+int uqb_block_m(int K, int HQ, int HKV);
+/* uq_mo_elems / uq_ml_elems / uq_workspace_bytes (reference cuda/uq_decode.h:34-35,41) */
+size_t uqb_mo_elems(const UQParams* p);
+size_t uqb_ml_elems(const UQParams* p);
+size_t uqb_workspace_bytes(const UQParams* p);
+/* uq_decode_launch (reference cuda/uq_decode.h:39, cuda/uq_decode.cu:602-626) */
+int uqb_decode_launch(const UQParams* p, int nwarps, int stages, void* stream);
+/* uq_decode_launch_ws (reference cuda/uq_decode.h:42, cuda/uq_decode.cu:629-632): workspace = mo then ml */
+int uqb_decode_launch_ws(const UQParams* p, void* workspace, int nwarps, int stages, void* stream);
+/* uq_has_sm90 (reference cuda/uq_decode.h:43): always 0 here */
+int uqb_has_sm90(void);
+
+/* ---- KV append-quantize ---------------------------------------------------------------------- */
+
+/* Quantize T new tokens and scatter them into the paged cache; bit-exact with the reference encoder.
+ * Stands in for uqmt.vllm_adapter.append_kv (reference uqmt/vllm_adapter.py:48-59) and for
+ * uqmt.quant.quantize_on_write, rule "ceil" (reference uqmt/quant.py:157-206); the reference has no
+ * native entry point for it.
+ *   key, value   [T, HKV, D] contiguous; dtype 0 = fp32, 1 = bf16, 2 = fp16.  value may be NULL with
+ *                vc/vs NULL to write only one stream (the quantize_on_write form).
+ *   slots        int64 [T]: physical_page * PAGE + offset; a negative slot is skipped (padding).
+ * D in {64,128,256}; PAGE any positive value. */
+int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
+                      const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, void* stream);
+
+/* ---- context-split partials and their merge (no counterpart in the reference) ---------------- */
+
+/* Attention of all queries over ONE SHARD of each sequence's context.  The cache and block_table in
+ * `p` hold only this shard's pages; shard-local key t of sequence b is global position
+ * pos_offset[b] + t and the shard holds n_local = clamp(seq_len - pos_offset, 0, max_pages*PAGE)
+ * keys.  seq_lens stay global.  Writes, per query row, the normalised partial output
+ * o_part fp32 [B,K,Hq,D] and lse2_part fp32 [B,K,Hq] = log2 of the sum of 2^(score*log2 e) over the
+ * shard (-inf and zeros when the row sees no key of this shard).  p->out is not used.
+ * pos_offset == NULL means offset 0 (the shard is the whole context). */
+int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, float* o_part, float* lse2_part,
+                              void* stream);
+/* Log-sum-exp merge of R shards' partials: o_parts fp32 [R,rows,D], lse2_parts fp32 [R,rows]
+ * -> out bf16 [rows,D]  (same arithmetic as the reference's in-GPU combine, cuda/uq_decode.cu:353-388). */
+int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16,
+                     void* stream);
+
+/* ---- diagnostics (no counterpart in the reference) ------------------------------------------- */
+
+/* Every device-side wait in this library is bounded; a wait that runs out records what it was
+ * waiting for and the kernel returns.  Reads (and clears) the current device's record:
+ * out4[0] = code (0 = none), out4[1] = block, out4[2] = barrier id, out4[3] = tile.  Synchronises the device. */
+int uqb_last_status(uint32_t out4[4]);
+/* Which kernel the last uqb_decode_* call on this thread chose: 1 = CUDA-core path, 2 = tcgen05 path. */
+int uqb_last_path(void);
+/* Timing aid for benchmarks: while both are non-NULL (cudaEvent_t passed as void*), every uqb_decode_* call of
+ * this thread records `before` and `after` on the launch stream around its attention kernel (not the combine). */
+void uqb_debug_events(void* before, void* after);
+/* Kernels launched by this library in this process (all threads). */
+unsigned long long uqb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,89 @@
+"""KV append-quantize kernel: bytes identical to the reference encoder (fixtures made by the reference's
+quantize_fp4 / append_kv) and to the CPU oracle on seeded inputs.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+from all_quant_b200 import uq_cuda
+from oracle import uq_oracle as O
+from tests.cases import load
+
+pytestmark = pytest.mark.gpu
+
+
+def encode_on_gpu(x, dtype=torch.float32):
+    """x fp32 numpy [N, D] -> (packed, scales) via quantize_on_write into a fresh one-head cache."""
+    N, D = x.shape
+    PAGE = 64
+    pages = (N + PAGE - 1) // PAGE
+    code = torch.zeros(pages, 1, PAGE, D // 2, dtype=torch.uint8, device="cuda")
+    scale = torch.zeros(pages, 1, PAGE, D // 32, dtype=torch.uint8, device="cuda")
+    xt = torch.from_numpy(x).cuda().to(dtype).reshape(N, 1, D)
+    uq_cuda.quantize_on_write(xt, code, scale, torch.arange(N, device="cuda"))
+    torch.cuda.synchronize()
+    return code.reshape(-1, D // 2)[:N].cpu().numpy(), scale.reshape(-1, D // 32)[:N].cpu().numpy()
+
+
+@pytest.mark.parametrize("name,dtype", [("wide", torch.float32), ("bf16in", torch.float32), ("bf16in", torch.bfloat16),
+                                        ("fp16in", torch.float32), ("fp16in", torch.float16)])
+def test_encoder_bit_exact_with_reference_fixture(name, dtype):
+    z = load("gen_codec")
+    p, s = encode_on_gpu(z[f"{name}_x"], dtype)
+    assert np.array_equal(s, z[f"{name}_scales"])
+    assert np.array_equal(p, z[f"{name}_packed"])
+
+
+def test_encoder_ties_specials_and_every_scale_boundary():
+    z = load("gen_codec")
+    x = z["g32_x"]                                   # [n, 32] single groups
+    n = x.shape[0] // 2 * 2
+    p, s = encode_on_gpu(x[:n].reshape(n // 2, 64))  # two groups per row of a D=64 cache
+    assert np.array_equal(s.reshape(-1), z["g32_scales"][:n].reshape(-1))
+    assert np.array_equal(p.reshape(n, 16), z["g32_packed"][:n])
+
+
+def test_append_kv_matches_reference_fixture():
+    z = load("gen_append")
+    kc, ks, vc, vs = (torch.from_numpy(z[n].copy()).cuda() for n in ("kc0", "ks0", "vc0", "vs0"))
+    key = torch.from_numpy(z["key"].view(np.int16)).cuda().view(torch.bfloat16)
+    val = torch.from_numpy(z["value"].view(np.int16)).cuda().view(torch.bfloat16)
+    uq_cuda.append_kv(kc, ks, vc, vs, key, val, torch.from_numpy(z["slots"]).cuda())
+    torch.cuda.synchronize()
+    for got, name in ((kc, "kc1"), (ks, "ks1"), (vc, "vc1"), (vs, "vs1")):
+        assert np.array_equal(got.cpu().numpy(), z[name]), name
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_cache_build_bit_exact_with_oracle_on_seeded_kv(D):
+    """The benchmark's cache is built by this kernel: lognormal-channel K, N(0,1) V, fp32 in."""
+    g = torch.Generator(device="cuda").manual_seed(1000 + D)
+    T, HKV, PAGE = 4096, 2, 64
+    chan = torch.exp(0.5 * torch.randn(1, HKV, D, generator=g, device="cuda"))
+    k = torch.randn(T, HKV, D, generator=g, device="cuda") * chan
+    v = torch.randn(T, HKV, D, generator=g, device="cuda")
+    pages = T // PAGE
+    kc = torch.zeros(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device="cuda")
+    ks = torch.zeros(pages, HKV, PAGE, D // 32, dtype=torch.uint8, device="cuda")
+    vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
+    slots = torch.randperm(T, generator=g, device="cuda")
+    uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots)
+    torch.cuda.synchronize()
+    rkc, rks, rvc, rvs = (np.zeros_like(t.cpu().numpy()) for t in (kc, ks, vc, vs))
+    O.append_kv(rkc, rks, rvc, rvs, k.cpu().numpy(), v.cpu().numpy(), slots.cpu().numpy())
+    for got, ref in ((kc, rkc), (ks, rks), (vc, rvc), (vs, rvs)):
+        assert np.array_equal(got.cpu().numpy(), ref)
+
+
+def test_negative_slots_are_skipped_and_empty_append_is_a_no_op():
+    kc = torch.full((2, 1, 16, 64), 7, dtype=torch.uint8, device="cuda")
+    ks = torch.full((2, 1, 16, 4), 9, dtype=torch.uint8, device="cuda")
+    vc, vs = kc.clone(), ks.clone()
+    x = torch.randn(3, 1, 128, device="cuda")
+    uq_cuda.append_kv(kc, ks, vc, vs, x, x, torch.tensor([-1, 5, -1], device="cuda"))
+    uq_cuda.append_kv(kc, ks, vc, vs, x[:0], x[:0], torch.zeros(0, dtype=torch.long, device="cuda"))
+    torch.cuda.synchronize()
+    untouched = torch.ones(32, dtype=torch.bool)
+    untouched[5] = False
+    assert (kc.reshape(32, 64)[untouched.cuda()] == 7).all() and (ks.reshape(32, 4)[untouched.cuda()] == 9).all()
+    p, s = O.quantize_fp4(x[1].cpu().numpy())
+    assert np.array_equal(kc.reshape(32, 64)[5].cpu().numpy(), p[0]) and np.array_equal(vs.reshape(32, 4)[5].cpu().numpy(), s[0])

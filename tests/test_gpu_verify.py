@@ -1,0 +1,146 @@
+"""Parity of the CUDA verify/decode attention with the reference's known answers and with the CPU oracle,
+through the C ABI (all_quant_b200.uq_cuda -> libuq_b200.so).  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+from all_quant_b200 import uq_cuda
+from oracle import uq_oracle as O
+from tests.cases import check_close, check_harness_rule, load_cases
+
+pytestmark = pytest.mark.gpu
+CASES = load_cases()
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.view(dtype)
+
+
+def run_case(c, **kw):
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    out = uq_cuda.uq_decode_cuda(q, dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt), dev(c.sl), sm_scale=c.sm_scale, **kw)
+    torch.cuda.synchronize()
+    assert uq_cuda.last_status()[0] == 0
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("c", CASES, ids=repr)
+def test_known_answers(c):
+    got = run_case(c)
+    check_close(got, c.ref, c.name)
+    check_harness_rule(got, c.ref, c.name)
+    for b in range(c.B):            # rows that see no key are exact zeros
+        for j in range(c.K):
+            if c.sl[b] - c.K + j + 1 <= 0:
+                assert not got[b, j].any()
+
+
+@pytest.mark.parametrize("c", [x for x in CASES if x.name in ("ref_cuda_main_K8", "gen_k8g8_K8", "ref_cuda_p16_g4_K3", "gen_d256_K8")], ids=repr)
+@pytest.mark.parametrize("nsplit", [1, 2, 3, 7, 16])
+def test_nsplit_invariance(c, nsplit):
+    check_close(run_case(c, nsplit=nsplit), c.ref, f"{c.name} nsplit={nsplit}")
+
+
+@pytest.mark.parametrize("c", [x for x in CASES if x.name in ("ref_cuda_main_K4", "gen_cfg0_K4", "gen_g7_K3")], ids=repr)
+def test_fused_equals_no_sharing(c):
+    a = run_case(c, fused=True)
+    b = run_case(c, fused=False)
+    check_close(b, c.ref, c.name + " no-sharing")
+    assert np.abs(a - b).max() <= 2e-2 * max(1.0, np.abs(c.ref).max())
+
+
+@pytest.mark.parametrize("path", ["fma", "tc"])
+def test_both_kernels_on_the_same_case(path, monkeypatch):
+    c = [x for x in CASES if x.name == "ref_cuda_main_K8"][0]
+    monkeypatch.setenv("UQ_B200_CFG", f"path={path}")
+    try:
+        got = run_case(c)
+    except RuntimeError as e:   # a forced kernel that does not serve the shape answers invalid value, never garbage
+        assert "InvalidValue" in str(e)
+        pytest.skip(f"{path} kernel does not serve this shape")
+    assert uq_cuda.last_path() == (1 if path == "fma" else 2)
+    check_close(got, c.ref, f"{c.name} {path}")
+
+
+def test_caller_workspace_int64_tables_and_out_argument():
+    c = [x for x in CASES if x.name == "ref_cuda_main_K4"][0]
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    ns = 5
+    ws = torch.full((uq_cuda.workspace_floats(c.B, c.K, c.HQ, c.HKV, c.D, ns),), float("nan"), device="cuda")
+    out = torch.full_like(q, float("nan"))
+    r = uq_cuda.uq_decode_cuda(q, dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt).long(), dev(c.sl).long(), nsplit=ns,
+                               workspace=ws, out=out)
+    assert r.data_ptr() == out.data_ptr()
+    check_close(out.float().cpu().numpy(), c.ref, "workspace")
+
+
+def test_poisoned_tail_and_unused_table_entries():
+    """Bytes after seq_len in the last page and page-table entries past the sequence may hold anything."""
+    c = [x for x in CASES if x.name == "gen_cfg0_K4"][0]
+    kc, ks, vc, vs, bt = (a.copy() for a in (c.kc, c.ks, c.vc, c.vs, c.bt))
+    for b in range(c.B):
+        n = int(c.sl[b])
+        last = bt[b, (n - 1) // c.PAGE]
+        t = n % c.PAGE
+        if t:
+            for a in (kc, ks, vc, vs):
+                a[last, :, t:] = 0xFF
+        bt[b, (n + c.PAGE - 1) // c.PAGE:] = -1
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    out = uq_cuda.uq_decode_cuda(q, dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(c.sl))
+    check_close(out.float().cpu().numpy(), c.ref, "poisoned tail")
+
+
+def test_scale_extremes():
+    """Scale bytes far from 127 (2^+-20): outputs follow the oracle on the same bytes."""
+    c = [x for x in CASES if x.name == "ref_cuda_main_K2"][0]
+    ks = (c.ks.astype(np.int32) - 20).clip(0, 255).astype(np.uint8)
+    vs = (c.vs.astype(np.int32) + 20).clip(0, 255).astype(np.uint8)
+    ref = O.reference(c.q, c.kc, ks, c.vc, vs, c.bt, c.sl, c.sm_scale)
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    out = uq_cuda.uq_decode_cuda(q, dev(c.kc), dev(ks), dev(c.vc), dev(vs), dev(c.bt), dev(c.sl))
+    check_close(out.float().cpu().numpy(), ref, "scale extremes")
+
+
+def test_unserved_shapes_answer_invalid_value_before_any_work():
+    c = [x for x in CASES if x.name == "ref_cuda_main_K1"][0]
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    args = (dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt), dev(c.sl))
+    with pytest.raises(RuntimeError, match="InvalidValue"):
+        uq_cuda.uq_decode_cuda(q, *args, fmt=1)
+    with pytest.raises(RuntimeError, match="InvalidValue"):
+        uq_cuda.uq_decode_cuda(q, *args, nsplit=129)
+    with pytest.raises(RuntimeError, match="InvalidValue"):
+        uq_cuda.uq_decode_cuda(q, *args, nsplit=0)
+    with pytest.raises(RuntimeError, match="bf16"):
+        uq_cuda.uq_decode_cuda(q.float(), *args)
+    # the tuning hints of the reference's kernels are accepted and ignored
+    out = uq_cuda.uq_decode_cuda(q, *args, variant=4, mb=2, nwarps=8, stages=4)
+    check_close(out.float().cpu().numpy(), c.ref, "hints")
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_context_split_partials_merge_to_the_unsplit_answer(R):
+    c = [x for x in CASES if x.name == "gen_d256_K8"][0]
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    per = -(-c.max_pages // R)
+    os_, ls_ = [], []
+    for r in range(R):
+        lo, hi = min(r * per, c.max_pages), min((r + 1) * per, c.max_pages)
+        bt = np.zeros((c.B, max(per, 1)), np.int32)
+        bt[:, : hi - lo] = c.bt[:, lo:hi]
+        off = np.full(c.B, lo * c.PAGE, np.int32)
+        o, l = uq_cuda.uq_decode_partial(q, dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(bt), dev(c.sl), dev(off))
+        # each shard's partial against the oracle's partial on the same shard
+        nloc = np.clip(c.sl - lo * c.PAGE, 0, (hi - lo) * c.PAGE).astype(np.int32)
+        ro, rl = O.reference(c.q, c.kc, c.ks, c.vc, c.vs, bt, c.sl, pos_offset=off, n_local=nloc, return_lse=True)
+        check_close(o.cpu().numpy(), ro, f"shard {r} o")
+        lse = l.cpu().numpy() * np.log(2.0)
+        fin = np.isfinite(rl)
+        assert np.array_equal(np.isfinite(lse), fin)
+        assert np.abs(lse[fin] - rl[fin]).max(initial=0) <= 2e-3
+        os_.append(o)
+        ls_.append(l)
+    out = uq_cuda.uq_merge(torch.stack(os_), torch.stack(ls_))
+    check_close(out.float().cpu().numpy(), c.ref, f"merge R={R}")
