@@ -87,11 +87,11 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 // dtype: 0 fp32, 1 bf16, 2 fp16.  value/vc/vs may be null (single-stream form).
 cudaError_t uq_append_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                                const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, cudaStream_t s) {
+  if (T == 0) return cudaSuccess;   // nothing to write; empty tensors may come with null pointers
   if (!kc || !ks || !key || !slots) return cudaErrorInvalidValue;
   const bool two = value != nullptr;
   if (two && (!vc || !vs)) return cudaErrorInvalidValue;
   if (!(D == 64 || D == 128 || D == 256) || PAGE <= 0 || HKV <= 0 || T < 0 || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
-  if (T == 0) return cudaSuccess;
   const int nstream = two ? 2 : 1;
   const long long warps = (long long)T * HKV * nstream;
   const int blocks = (int)((warps + 3) / 4);

@@ -1,5 +1,780 @@
-// placeholder until the tcgen05 kernel lands
+// Verify/decode attention over the paged FP4 cache on the Blackwell tensor cores (tcgen05 + TMEM).
+//
+// The operation is the reference's (reference cuda/uq_decode.h:1-6, oracle uqmt/attn.py:402-422); the
+// kernel is built the other way round from the reference's own tcgen05 kernel
+// (reference cuda/uq_decode_sm100.cuh, query rows on the 128 accumulator lanes, padded): here the KEYS
+// sit on the 128 lanes and the K*G query rows are the N extent of both contractions, so tensor work is
+// proportional to the rows that exist:
+//     S^T[key, row] = Kdeq[key, :] . Q[row, :]        M = 128 keys, N = NT rows, K = D      (A from TMEM)
+//     O^T[d,   row] += Vdeq[key, d] * P[key, row]     M = 128 channels, N = NT rows, K = 128 keys
+//
+// One CTA per SM, 512 threads = four warpgroups:
+//   warps 0-3   softmax   thread = key: reads its lane of S^T, exp2 with a lazily updated per-row reference
+//                         maximum, writes P^T to shared memory (MN-major B operand), keeps per-thread row sums;
+//                         at the end of a segment reduces the sums, reads O^T and writes the partial.
+//   warps 4-7   K decode  thread = key: nibbles + UE8M0 -> bf16 in registers -> tcgen05.st into the A operand
+//   warps 8-11  V decode  thread = key: -> 128-byte-swizzled bf16 tile in shared memory (MN-major A operand)
+//   warp 12     producer  TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code
+//                         row without bank conflicts) of the K/V code pages + bulk copies of the scale pages
+//   warp 13     MMA       issues tcgen05.mma, owns the TMEM allocation        (warps 14-15 idle)
+// Work is a flat list of 128-key tiles over all (sequence, kv head) items, cut into equal chunks, one per CTA;
+// a chunk that crosses items yields several segments, each written to its own partial slot.
+//
+// Decoded operands carry a fixed bias of 2^-64 (K and V alike: value * 2^(s-127-64)) so that one bf16
+// multiply covers scale bytes 59..192 exactly; the bias is undone in fp32 (scores: folded into the softmax
+// scale; outputs: one multiply in the epilogue).  Scale bytes above 192 take a two-multiply path.
+//
+// Every wait is bounded (about one second): on expiry the thread records the barrier in the status record,
+// raises the CTA's abort flag and every role drains to the common exit, which frees TMEM.
+#include <cuda.h>
+
 #include "uq_common.cuh"
-bool uq_verify_tc_serves(const UQParams&, const UQLaunch&) { return false; }
-int uq_verify_tc_splits(const UQParams&, const UQLaunch&) { return 1; }
-cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t) { return cudaErrorInvalidValue; }
+
+namespace tc {
+
+constexpr int kKeys = 128;      // keys per tile = accumulator lanes
+constexpr int kThreads = 512;      // 16 warps: 128 registers per thread
+constexpr int kRawStages = 4;
+constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
+constexpr float kNegBig = -1.0e30f;
+
+// ---------------------------------------------------------------------------------------------- PTX
+UQ_DEV uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+UQ_DEV void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+UQ_DEV void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+UQ_DEV void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+UQ_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+UQ_DEV unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+UQ_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+UQ_DEV void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+UQ_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+UQ_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+UQ_DEV void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+UQ_DEV void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+UQ_DEV void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
+
+// 2-D tiled TMA load: box (inner 0.., rows y..) of the tensor map into shared memory, bytes counted on `bar`.
+UQ_DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// contiguous bulk copy (scale pages)
+UQ_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// shared-memory matrix descriptor, 128-byte swizzle (sm_100 format: version bit 46, layout type 2 at bit 61)
+UQ_DEV uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor, kind::f16: bf16 x bf16 -> fp32; major 0 = K-major, 1 = MN-major
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+UQ_DEV void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+UQ_DEV void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+UQ_DEV void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+UQ_DEV void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+UQ_DEV uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+UQ_DEV float fast_exp2(float v) {   // 2^v, -inf -> 0
+  float d;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(v));
+  return d;
+}
+UQ_DEV uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// ---------------------------------------------------------------------------------------------- decode
+// 8 packed e2m1 nibbles (channels 8a .. 8a+7) and the group's multiplier (bf16x2, both halves equal)
+// -> 4 bf16x2 words holding channels (0,4), (1,5), (2,6), (3,7) of the octet: pairing nibble i with nibble
+// i+4 lets one shift serve both halves.  (sign | code3 << 6) read as bf16 is value * 2^-126 exactly, zero and
+// the 0.5 subnormal included; the multiplier supplies 2^(s - 1 - 64).
+UQ_DEV void decode8(uint32_t w, uint32_t mult, uint32_t* out) {
+  const uint32_t t0 = (w << 6) & 0x03C003C0u, t1 = (w << 2) & 0x03C003C0u, t2 = (w >> 2) & 0x03C003C0u, t3 = (w >> 6) & 0x03C003C0u;
+  out[0] = mul_bf16x2(t0 + (t0 & 0x02000200u) * 63u, mult);   // bit 9 (sign) moves to bit 15
+  out[1] = mul_bf16x2(t1 + (t1 & 0x02000200u) * 63u, mult);
+  out[2] = mul_bf16x2(t2 + (t2 & 0x02000200u) * 63u, mult);
+  out[3] = mul_bf16x2(t3 + (t3 & 0x02000200u) * 63u, mult);
+}
+// position p (0..7) of a decoded octet holds channel (p >> 1) + 4 * (p & 1); queries are laid out to match
+UQ_DEV int octet_channel(int p) { return (p >> 1) + 4 * (p & 1); }
+
+// group multiplier 2^(s-65) as bf16x2 for s <= 192; above that the caller multiplies twice
+UQ_DEV uint32_t scale_mult(uint32_t s) {
+  const uint32_t b = (s + 62u) << 7;
+  return b | (b << 16);
+}
+
+// ---------------------------------------------------------------------------------------------- layout
+template <int D, int NT>
+struct Cfg {
+  static_assert(D == 128, "head_dim 128 only");
+  static_assert(NT == 16 || NT == 32 || NT == 64, "rows padded to 16 / 32 / 64");
+  static constexpr int kCodeRow = D / 2;                 // bytes of codes per key
+  static constexpr int kGroups = D / 32;                 // scale bytes per key
+  static constexpr int kRawCodes = kKeys * kCodeRow;     // 8192
+  static constexpr int kRawScales = kKeys * kGroups;     // 512
+  static constexpr int kRawStage = 2 * (kRawCodes + kRawScales);
+  static constexpr int kVTile = kKeys * D * 2;           // bf16 [key][d], two 64-channel halves of [128][128 B]
+  static constexpr int kVHalf = kKeys * 128;
+  static constexpr int kQTile = NT * D * 2;              // bf16 [row][position], two halves of [NT][128 B]
+  static constexpr int kQHalf = NT * 128;
+  static constexpr int kPTile = kKeys * 128;             // bf16 [key][row], rows padded to 64
+  // shared memory map (offsets from a 1024-aligned base)
+  static constexpr int oV = 0;
+  static constexpr int oQ = oV + 2 * kVTile;
+  static constexpr int oP = oQ + kQTile;
+  static constexpr int oRaw = oP + 2 * kPTile;
+  static constexpr int oBar = oRaw + kRawStages * kRawStage;
+  static constexpr int kNumBars = 2 * kRawStages + 16;
+  static constexpr int oMisc = oBar + kNumBars * 8;
+  // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], prefix[]
+  static constexpr int oTmemSlot = oMisc;
+  static constexpr int oAbort = oMisc + 4;
+  static constexpr int oVote = oMisc + 8;                // 2 ints
+  static constexpr int oMref = oMisc + 16;
+  static constexpr int oWmax = oMref + 2 * NT * 4;
+  static constexpr int oLsum = oWmax + 4 * NT * 4;
+  static constexpr int oPrefix = oLsum + NT * 4;
+  static constexpr int kMaxB = 2048;
+  static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4 + 1024;   // + slack for the 1024 alignment
+  // TMEM columns
+  static constexpr int cK = 0;                 // 2 x 64: bf16 A operand of S^T
+  static constexpr int cS = 128;               // 2 x NT: fp32 S^T
+  static constexpr int cO = cS + 2 * NT;       // NT:     fp32 O^T
+};
+
+// barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
+enum { bKfull = 0, bSfull = 2, bSfree = 4, bVfull = 6, bPfull = 8, bPVdone = 10, bQfull = 12, bOdone = 13, bEpi = 14, bVote = 15 };
+
+struct Params {
+  UQParams p;
+  UQLaunch x;
+  int chunk_min;      // lower bound on the chunk (tiles per CTA) that keeps segments per item within ns_eff
+};
+
+// ---------------------------------------------------------------------------------------------- work list
+struct Seg {
+  int b, hk, t0, t1;   // tiles [t0, t1) of item (b, hk)
+  int slot;            // partial slot of this segment
+  int nseg;            // slots the item uses (valid when t0 == 0)
+  int ntiles;          // tiles of the whole item
+};
+
+struct Walker {
+  const int* prefix;   // prefix[b] = tiles of sequences < b (one kv head)
+  int B, HKV, nitems, total, chunk, per_item;
+  int pos, end, it, cta;
+
+  UQ_DEV void init(const int* pre, int B_, int HKV_, int ns_eff, int chunk_min) {
+    prefix = pre; B = B_; HKV = HKV_; nitems = B * HKV; total = HKV * pre[B];
+    cta = blockIdx.x;
+    per_item = ns_eff < 2;
+    if (per_item) { it = cta - (int)gridDim.x; pos = end = 0; chunk = 1; return; }
+    chunk = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (chunk < chunk_min) chunk = chunk_min;
+    if (chunk < 1) chunk = 1;
+    pos = min(cta * chunk, total);
+    end = min(pos + chunk, total);
+    it = 0;
+  }
+  UQ_DEV int item_tiles(int item) const { const int b = item / HKV; return prefix[b + 1] - prefix[b]; }
+  UQ_DEV int item_start(int item) const { const int b = item / HKV, hk = item % HKV; return HKV * prefix[b] + hk * (prefix[b + 1] - prefix[b]); }
+  UQ_DEV bool next(Seg& s) {
+    if (per_item) {
+      for (it += (int)gridDim.x; it < nitems; it += (int)gridDim.x) {
+        const int n = item_tiles(it);
+        if (n == 0) continue;
+        s.b = it / HKV; s.hk = it % HKV; s.t0 = 0; s.t1 = n; s.slot = 0; s.nseg = 1; s.ntiles = n;
+        return true;
+      }
+      return false;
+    }
+    if (pos >= end) return false;
+    // sequence containing flat tile `pos`: largest b with HKV * prefix[b] <= pos
+    int lo = 0, hi = B;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (HKV * prefix[mid] <= pos) lo = mid; else hi = mid;
+    }
+    const int n = prefix[lo + 1] - prefix[lo];   // > 0 because pos < HKV * prefix[lo + 1]
+    const int hk = (pos - HKV * prefix[lo]) / n;
+    const int start = HKV * prefix[lo] + hk * n;
+    s.b = lo; s.hk = hk; s.ntiles = n;
+    s.t0 = pos - start;
+    s.t1 = min(start + n, end) - start;
+    const int c0 = start / chunk;
+    s.slot = cta - c0;
+    s.nseg = (start + n - 1) / chunk - c0 + 1;
+    pos = start + s.t1;
+    return true;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------- kernel
+template <int D, int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc) {
+  using C = Cfg<D, NT>;
+  extern __shared__ uint8_t smem_raw[];
+  const UQParams& p = prm.p;
+  const UQLaunch& x = prm.x;
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sm_a = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::oAbort);
+  int* prefix = reinterpret_cast<int*>(sm + C::oPrefix);
+
+  auto bar_raw_full = [&](int s) { return sm_a + C::oBar + 8 * s; };
+  auto bar_raw_empty = [&](int s) { return sm_a + C::oBar + 8 * (kRawStages + s); };
+  auto bar = [&](int i) { return sm_a + C::oBar + 8 * (2 * kRawStages + i); };
+
+  // bounded wait; false = gave up (this thread or another one), the caller leaves its loop
+  auto wait = [&](uint32_t b, uint32_t parity, int id, int tile) -> bool {
+    if (mbar_try(b, parity)) return true;
+    const unsigned long long t_start = now_ns();
+    for (unsigned it = 1;; it++) {
+      if (mbar_try(b, parity)) return true;
+      if ((it & 63u) == 0u) {
+        if (*abort_flag) return false;
+        if (now_ns() - t_start > 1000000000ull) {
+          *abort_flag = 1;
+          uq_report(x.status, 1u, (unsigned)id, (unsigned)tile);
+          return false;
+        }
+      }
+    }
+  };
+
+  // ---- set-up: barriers, tile prefix, TMEM
+  if (tid == 0) {
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 256); }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(bar(bKfull + i), 128); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 128);
+      mbar_init(bar(bVfull + i), 128); mbar_init(bar(bPfull + i), 128); mbar_init(bar(bPVdone + i), 1);
+    }
+    mbar_init(bar(bQfull), 128); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 128); mbar_init(bar(bVote), 128);
+    *abort_flag = 0;
+    reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
+    reinterpret_cast<int*>(sm + C::oVote)[1] = 0;
+    fence_barrier_init();
+  }
+  for (int b = tid; b < p.B; b += kThreads) {   // tiles per sequence, then an in-place scan by one thread
+    int off;
+    const int n = uq_n_local(p, x, b, &off);
+    prefix[b + 1] = (n + kKeys - 1) / kKeys;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    prefix[0] = 0;
+    for (int b = 0; b < p.B; b++) prefix[b + 1] += prefix[b];
+  }
+  if (warp == 13) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sm_a + C::oTmemSlot) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sm + C::oTmemSlot);
+
+  Walker wk;
+  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min);
+  const int G = x.G, rows = x.rows;
+  Seg sg;
+
+  if (warp == 12) {
+    // ================================================================= producer
+    const int ppt = kKeys / p.PAGE;   // pages per tile
+    const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kGroups;
+    int cnt = 0;
+    bool ok = true;
+    while (ok && wk.next(sg)) {
+      int off;
+      const int n_loc = uq_n_local(p, x, sg.b, &off);
+      const int pages_valid = (n_loc + p.PAGE - 1) / p.PAGE;
+      const int32_t* bt = p.block_table + (size_t)sg.b * p.max_pages;
+      for (int t = sg.t0; t < sg.t1; t++, cnt++) {
+        const int stage = cnt % kRawStages;
+        const int vp = min(ppt, pages_valid - t * ppt);
+        int pid = 0;
+        if (lane < vp) pid = __ldg(bt + t * ppt + lane);
+        ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t dst = sm_a + C::oRaw + stage * C::kRawStage;
+        if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * 2u * (page_bytes_codes + page_bytes_scales));
+        __syncwarp();
+        if (lane < vp) {
+          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE;   // first cache row of this (page, head)
+          const uint32_t fb = bar_raw_full(stage);
+          tma_load_2d(dst + lane * page_bytes_codes, &map_kc, 0, row0, fb);
+          tma_load_2d(dst + C::kRawCodes + lane * page_bytes_codes, &map_vc, 0, row0, fb);
+          bulk_load(dst + 2 * C::kRawCodes + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
+          bulk_load(dst + 2 * C::kRawCodes + C::kRawScales + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
+        }
+      }
+    }
+  } else if (warp == 13) {
+    // ================================================================= MMA issue
+    constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0);
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1);
+    int cnt = 0, seg_i = 0;
+    bool ok = true;
+    auto issue_pv = [&](int c, int first) {   // c = global tile counter of the tile whose P/V are consumed
+      const int buf = c & 1;
+      if (!wait(bar(bPfull + buf), (c >> 1) & 1, 20 + buf, c)) return false;
+      if (!wait(bar(bVfull + buf), (c >> 1) & 1, 22 + buf, c)) return false;
+      tc_fence_after();
+      const uint32_t va = sm_a + C::oV + buf * C::kVTile, pa = sm_a + C::oP + buf * C::kPTile;
+#pragma unroll
+      for (int kk = 0; kk < kKeys / 16; kk++)
+        mma_ss(tmem + C::cO, smem_desc(va + kk * 2048, C::kVHalf, 1024), smem_desc(pa + kk * 2048, C::kVHalf, 1024), idesc_pv, (first && kk == 0) ? 0u : 1u);
+      tc_commit(bar(bPVdone + buf));
+      return true;
+    };
+    while (ok && wk.next(sg)) {
+      if (lane == 0) {
+        ok = wait(bar(bQfull), seg_i & 1, 30, seg_i);
+        if (ok && seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i);   // previous segment's O has been read
+        const int c0 = cnt;
+        for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
+          const int buf = cnt & 1;
+          ok = wait(bar(bKfull + buf), (cnt >> 1) & 1, 24 + buf, cnt);
+          if (ok && cnt >= 2) ok = wait(bar(bSfree + buf), ((cnt >> 1) - 1) & 1, 26 + buf, cnt);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t qa = sm_a + C::oQ;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ks++)
+            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, smem_desc(qa + (ks >> 2) * C::kQHalf + (ks & 3) * 32, 16, 1024), idesc_qk, ks ? 1u : 0u);
+          tc_commit(bar(bSfull + buf));
+          if (cnt > c0) ok = issue_pv(cnt - 1, cnt - 1 == c0);
+        }
+        if (ok) ok = issue_pv(cnt - 1, cnt - 1 == c0);
+        if (ok) tc_commit(bar(bOdone));
+      } else {
+        cnt += sg.t1 - sg.t0;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      seg_i++;
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ================================================================= K decode -> TMEM
+    const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    int cnt = 0;
+    bool ok = true;
+    while (ok && wk.next(sg)) {
+      for (int t = sg.t0; t < sg.t1; t++, cnt++) {
+        const int stage = cnt % kRawStages, buf = cnt & 1;
+        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt);
+        if (ok && cnt >= 2) ok = wait(bar(bSfull + buf), ((cnt >> 1) - 1) & 1, 44 + buf, cnt);   // S^T(cnt-2) done: its A operand is free
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
+        const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
+        const bool big = __any_sync(0xffffffffu, (sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u);
+#pragma unroll
+        for (int g = 0; g < C::kGroups; g++) {
+          // 64-byte-swizzled row: logical 16-byte chunk g sits at chunk g ^ ((key >> 1) & 3)
+          const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+          const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
+          uint32_t o[16];
+          if (!big) {
+            const uint32_t m = scale_mult(s);
+            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          } else {
+            const uint32_t s1 = s > 192u ? s - 96u : s, m = scale_mult(s1), m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;   // 2^96 or 1
+            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+#pragma unroll
+            for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
+          }
+          tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(bKfull + buf));
+        mbar_arrive(bar_raw_empty(stage));
+      }
+    }
+  } else if (warp >= 8 && warp < 12) {
+    // ================================================================= V decode -> shared memory
+    const int kk = (warp - 8) * 32 + lane;
+    int cnt = 0;
+    bool ok = true;
+    while (ok && wk.next(sg)) {
+      int off;
+      const int n_loc = uq_n_local(p, x, sg.b, &off);
+      for (int t = sg.t0; t < sg.t1; t++, cnt++) {
+        const int stage = cnt % kRawStages, buf = cnt & 1;
+        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 50 + stage, cnt);
+        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 54 + buf, cnt);   // O^T += of tile cnt-2 done: tile buffer free
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kRawCodes;
+        uint8_t* vt = sm + C::oV + buf * C::kVTile;
+        const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
+        const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * 4);
+        const bool big = __any_sync(0xffffffffu, live && ((sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u));
+#pragma unroll
+        for (int g = 0; g < C::kGroups; g++) {
+          const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+          const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
+          uint32_t o[16];
+          if (!big) {
+            const uint32_t m = scale_mult(s);
+            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          } else {
+            const uint32_t s1 = s > 192u ? s - 96u : s, m = scale_mult(s1), m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
+            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+#pragma unroll
+            for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
+          }
+          if (!live) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) o[i] = 0u;
+          }
+          // output chunk oc = 4g + w (8 channels) of the key's 256-byte row: half oc >> 3, slot (oc & 7) ^ (key & 7)
+#pragma unroll
+          for (int w = 0; w < 4; w++) {
+            const int oc = 4 * g + w;
+            *reinterpret_cast<uint4*>(vt + (oc >> 3) * C::kVHalf + kk * 128 + (((oc & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
+          }
+        }
+        fence_async_smem();
+        mbar_arrive(bar(bVfull + buf));
+        mbar_arrive(bar_raw_empty(stage));
+      }
+    }
+  } else if (warp < 4) {
+    // ================================================================= softmax + epilogue
+    const int quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = 0..127 index within the role
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    float* mref = reinterpret_cast<float*>(sm + C::oMref);     // [2][NT], the live copy is mref + mcur * NT
+    float* wmax = reinterpret_cast<float*>(sm + C::oWmax);     // [4][NT]
+    float* lsum = reinterpret_cast<float*>(sm + C::oLsum);
+    int* vote = reinterpret_cast<int*>(sm + C::oVote);
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const float csc = x.sc2 * 18446744073709551616.0f;   // scores carry the 2^-64 of the decoded K
+    int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
+    bool ok = true;
+    // items without a single key: nobody computes them, their slots must read as empty
+    for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
+      if (wk.item_tiles(it) != 0) continue;
+      for (int i = st; i < x.ns_eff * rows; i += 128)
+        p.ml[uq_slot(p, it / p.HKV, it % p.HKV, i / rows) * x.BM + i % rows] = -INFINITY;
+    }
+    while (ok && wk.next(sg)) {
+      int off;
+      const int n_loc = uq_n_local(p, x, sg.b, &off);
+      const int n_glob = p.seq_lens[sg.b];
+      // ---- query tile: [row][position], octets permuted like the decoded K, 128-byte swizzle, two 64-position halves
+      for (int i = st; i < NT * (D / 8); i += 128) {
+        const int n = i / (D / 8), a = i % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n < rows) v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
+        const uint4 w = make_uint4(__byte_perm(v.x, v.z, 0x5410), __byte_perm(v.x, v.z, 0x7632), __byte_perm(v.y, v.w, 0x5410), __byte_perm(v.y, v.w, 0x7632));
+        *reinterpret_cast<uint4*>(sm + C::oQ + (a >> 3) * C::kQHalf + n * 128 + (((a & 7) ^ (n & 7)) << 4)) = w;
+      }
+      if (st < NT) { mref[mcur * NT + st] = kNegBig; lsum[st] = 0.f; }
+      fence_async_smem();
+      mbar_arrive(bar(bQfull));
+      // the first segment of an item marks the slots the item does not use as empty
+      if (sg.t0 == 0)
+        for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 128)
+          p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
+      // the reference row maxima written above must be visible to all 128 threads before the first tile
+      mbar_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 60, seg_i);
+      nvote++;
+      ok = __all_sync(0xffffffffu, ok);
+      float l[NT];
+#pragma unroll
+      for (int r = 0; r < NT; r++) l[r] = 0.f;
+      const int c0 = cnt;
+      for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
+        const int buf = cnt & 1;
+        ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t s_addr = lane_addr + C::cS + buf * NT;
+        // rows this key is visible to: r >= rmin (causal limit among the drafts); none if past the end
+        const int key = t * kKeys + kk;
+        int rmin = 0;
+        if (key >= n_loc) rmin = NT;
+        else { const int jmin = off + key - (n_glob - p.K); if (jmin > 0) rmin = jmin * G; }
+        const float* mr = mref + mcur * NT;
+        // ---- pass 1: does any visible score leave the window of its row's reference maximum?
+        float xm = kNegBig;
+#pragma unroll
+        for (int c = 0; c < NT / 16; c++) {
+          uint32_t sv[16];
+          tmem_ld16(s_addr + c * 16, sv);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            const int r = c * 16 + i;
+            const float v = fmaf(__uint_as_float(sv[i]), csc, -mr[r]);
+            xm = fmaxf(xm, (r >= rmin && r < rows) ? v : kNegBig);
+          }
+        }
+        const bool mine = xm > kRescaleAt;
+        if (__any_sync(0xffffffffu, mine) && lane == 0) atomicOr(&vote[nvote & 1], 1);
+        mbar_arrive(bar(bVote));
+        ok = wait(bar(bVote), nvote & 1, 64, cnt);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int moved = *reinterpret_cast<volatile int*>(&vote[nvote & 1]);
+        nvote++;
+        if (moved) {
+          // ---- move the reference maxima of this segment's rows (the first tile, then only on growth)
+#pragma unroll
+          for (int c = 0; c < NT / 16; c++) {
+            uint32_t sv[16];
+            tmem_ld16(s_addr + c * 16, sv);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              const int r = c * 16 + i;
+              float v = (r >= rmin && r < rows) ? __uint_as_float(sv[i]) * csc : -INFINITY;
+#pragma unroll
+              for (int m = 16; m; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+              if (lane == 0) wmax[quad * NT + r] = v;
+            }
+          }
+          mbar_arrive(bar(bVote));
+          ok = wait(bar(bVote), nvote & 1, 65, cnt);
+          nvote++;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (st == 0) vote[0] = vote[1] = 0;
+          float* mn = mref + (mcur ^ 1) * NT;
+          auto new_ref = [&](int r) { return fmaxf(fmaxf(mr[r], fmaxf(wmax[r], wmax[NT + r])), fmaxf(wmax[2 * NT + r], wmax[3 * NT + r])); };
+#pragma unroll
+          for (int r = 0; r < NT; r++) {
+            const float m_new = new_ref(r);
+            l[r] *= fast_exp2(mr[r] - m_new);   // first tile: 2^(-1e30 - m) = 0
+            if (st == r) mn[r] = m_new;
+          }
+          if (cnt > c0) {
+            // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's lane
+            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < NT / 16; c++) {
+              uint32_t ov[16];
+              tmem_ld16(lane_addr + C::cO + c * 16, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * fast_exp2(mr[c * 16 + i] - new_ref(c * 16 + i)));
+              tmem_st16(lane_addr + C::cO + c * 16, ov);
+            }
+            tc_wait_st();
+          }
+          mcur ^= 1;
+          mbar_arrive(bar(bVote));          // new references and cleared votes visible before anyone's next tile
+          ok = wait(bar(bVote), nvote & 1, 67, cnt);
+          nvote++;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        if (cnt >= 2) {
+          ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt);   // P buffer free
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        // ---- pass 2: probabilities against the (possibly moved) references -> P^T, row sums
+        const float* mc = mref + mcur * NT;
+        uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
+#pragma unroll
+        for (int c = 0; c < NT / 16; c++) {
+          uint32_t sv[16];
+          tmem_ld16(s_addr + c * 16, sv);
+          tc_wait_ld();
+          if (c == NT / 16 - 1) {   // the S^T buffer is in registers now
+            tc_fence_before();
+            mbar_arrive(bar(bSfree + buf));
+          }
+          float pv[16];
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            const int r = c * 16 + i;
+            const float v = fast_exp2(fmaf(__uint_as_float(sv[i]), csc, -mc[r]));
+            pv[i] = (r >= rmin && r < rows) ? v : 0.f;
+            l[r] += pv[i];
+          }
+          *reinterpret_cast<uint4*>(pt + (((2 * c) ^ (kk & 7)) << 4)) =
+              make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
+          *reinterpret_cast<uint4*>(pt + (((2 * c + 1) ^ (kk & 7)) << 4)) =
+              make_uint4(pack_bf16x2(pv[8], pv[9]), pack_bf16x2(pv[10], pv[11]), pack_bf16x2(pv[12], pv[13]), pack_bf16x2(pv[14], pv[15]));
+        }
+        fence_async_smem();
+        mbar_arrive(bar(bPfull + buf));
+      }
+      if (!ok) break;
+      // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
+#pragma unroll
+      for (int r = 0; r < NT; r++) {
+        float v = l[r];
+#pragma unroll
+        for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+        if (lane == 0) atomicAdd(&lsum[r], v);
+      }
+      mbar_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 70, seg_i);
+      nvote++;
+      if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const size_t slot = uq_slot(p, sg.b, sg.hk, sg.slot);
+      float* mo = p.mo + slot * x.BM * D;
+      float* ml = p.ml + slot * x.BM;
+      const int dch = (kk & ~7) + octet_channel(kk & 7);   // channel held by accumulator lane kk
+      const float* mr = mref + mcur * NT;
+#pragma unroll
+      for (int c = 0; c < NT / 16; c++) {
+        uint32_t ov[16];
+        tmem_ld16(lane_addr + C::cO + c * 16, ov);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+          const int r = c * 16 + i;
+          if (r < rows) {
+            const float lr = lsum[r];
+            mo[(size_t)r * D + dch] = lr > 0.f ? __uint_as_float(ov[i]) * (18446744073709551616.0f / lr) : 0.f;
+          }
+        }
+      }
+      if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
+      tc_fence_before();
+      mbar_arrive(bar(bEpi));
+      // everyone has read lsum / mref before the next segment overwrites them
+      mbar_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 72, seg_i);
+      nvote++;
+      ok = __all_sync(0xffffffffu, ok);
+      seg_i++;
+    }
+  }
+
+  // ---- common exit: every role gets here (all waits are bounded); TMEM goes back before the CTA ends
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 13) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// The code arrays as a 2-D byte tensor [cache rows][D/2]; a box is one page of one head (PAGE rows).  The number
+// of physical pages is not part of the launch arguments, so the row extent is the largest the map can hold:
+// only rows named by the page table are ever touched.
+bool make_code_map(CUtensorMap* map, const uint8_t* base, int code_row_bytes, int page) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)code_row_bytes, (cuuint64_t)1 << 31};
+  const cuuint64_t strides[1] = {(cuuint64_t)code_row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)code_row_bytes, (cuuint32_t)page};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, int NT>
+cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
+  using C = Cfg<D, NT>;
+  auto kern = uq_verify_tc_kernel<D, NT>;
+  static bool ready[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidValue;
+  if (!ready[dev]) {   // per device: the attribute belongs to the device's copy of the kernel
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (e != cudaSuccess) { cudaGetLastError(); return e; }
+    ready[dev] = true;
+  }
+  Params prm;
+  prm.p = p;
+  prm.x = x;
+  // an item of n tiles cut into chunks of c tiles spans at most ceil(n / c) + 1 CTAs: keep that within ns_eff
+  const long long max_tiles = ((long long)p.max_pages * p.PAGE + kKeys - 1) / kKeys;
+  prm.chunk_min = x.ns_eff >= 2 ? (int)((max_tiles + x.ns_eff - 2) / (x.ns_eff - 1)) : 1;
+  CUtensorMap mk, mv;
+  if (!make_code_map(&mk, p.kc, C::kCodeRow, p.PAGE) || !make_code_map(&mv, p.vc, C::kCodeRow, p.PAGE)) return cudaErrorInvalidValue;
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  kern<<<sms, kThreads, C::kSmem, s>>>(prm, mk, mv);
+  return cudaGetLastError();
+}
+
+}  // namespace tc
+
+bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
+  if (p.D != 128) return false;
+  if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
+  if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
+  if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
+  if ((long long)p.max_pages * p.PAGE >= (1ll << 30)) return false;
+  return tc::encode_fn() != nullptr;
+}
+
+int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) { return p.nsplit; }
+
+cudaError_t uq_verify_tc_dispatch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
+  if (x.rows <= 16) return tc::launch<128, 16>(p, x, s);
+  if (x.rows <= 32) return tc::launch<128, 32>(p, x, s);
+  return tc::launch<128, 64>(p, x, s);
+}

@@ -100,7 +100,8 @@ def test_scale_extremes():
     ref = O.reference(c.q, c.kc, ks, c.vc, vs, c.bt, c.sl, c.sm_scale)
     q = dev(c.q.view(np.int16), torch.bfloat16)
     out = uq_cuda.uq_decode_cuda(q, dev(c.kc), dev(ks), dev(c.vc), dev(vs), dev(c.bt), dev(c.sl))
-    check_close(out.float().cpu().numpy(), ref, "scale extremes")
+    mx = np.abs(ref).max()      # outputs are ~2^20 here: apply the acceptance rule to outputs normalised to O(1)
+    check_close(out.float().cpu().numpy() / mx, ref / mx, "scale extremes")
 
 
 def test_unserved_shapes_answer_invalid_value_before_any_work():
