@@ -32,6 +32,24 @@
 
 namespace tc {
 
+#ifdef UQ_TC_PROF
+// per-role cycle counters (profiling build only): [role][0..5] cycles spent in the role's wait sites, [6] event count, [7] total cycles
+__device__ unsigned long long g_tc_prof[5][8];
+#define UQ_PROF_DECL unsigned long long pw[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long pt0 = clock64();
+#define UQ_PROF_FLUSH(role, leader) if (leader) { pw[7] = clock64() - pt0; for (int i = 0; i < 8; i++) atomicAdd(&g_tc_prof[role][i], pw[i]); }
+#define UQ_PROF_SITE(n) , &pw[n]
+#define UQ_PROF_COUNT(n) pw[n]++;
+#define UQ_PROF_T0 const long long ps0 = clock64();
+#define UQ_PROF_T1(n) pw[n] += clock64() - ps0;
+#else
+#define UQ_PROF_DECL
+#define UQ_PROF_FLUSH(role, leader)
+#define UQ_PROF_SITE(n) , nullptr
+#define UQ_PROF_COUNT(n)
+#define UQ_PROF_T0
+#define UQ_PROF_T1(n)
+#endif
+
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 constexpr int kThreads = 512;      // 16 warps: 128 registers per thread
 constexpr int kRawStages = 4;
@@ -112,6 +130,35 @@ UQ_DEV uint32_t pack_bf16x2(float lo, float hi) {
   return d;
 }
 
+// Wait for phase `parity` of an mbarrier, for about one second at most.  false = gave up (this thread's wait ran
+// out, or another thread of the CTA raised the abort flag): the caller leaves its loop and falls through to the exit.
+__device__ __noinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, int id, int tile,
+                                          unsigned long long* site) {
+#ifdef UQ_TC_PROF
+  const long long c_start = clock64();
+  if (mbar_try(bar, parity)) { if (site) *site += clock64() - c_start; return true; }
+#else
+  if (mbar_try(bar, parity)) return true;
+#endif
+  const unsigned long long t_start = now_ns();
+  for (unsigned it = 1;; it++) {
+    if (mbar_try(bar, parity)) {
+#ifdef UQ_TC_PROF
+      if (site) *site += clock64() - c_start;
+#endif
+      return true;
+    }
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (now_ns() - t_start > 1000000000ull) {
+        *abort_flag = 1;
+        uq_report(status, 1u, (unsigned)id, (unsigned)tile);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- decode
 // 8 packed e2m1 nibbles (channels 8a .. 8a+7) and the group's multiplier (bf16x2, both halves equal)
 // -> 4 bf16x2 words holding channels (0,4), (1,5), (2,6), (3,7) of the octet: pairing nibble i with nibble
@@ -156,14 +203,15 @@ struct Cfg {
   static constexpr int oBar = oRaw + kRawStages * kRawStage;
   static constexpr int kNumBars = 2 * kRawStages + 16;
   static constexpr int oMisc = oBar + kNumBars * 8;
-  // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], prefix[]
+  // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], fac[NT], prefix[]
   static constexpr int oTmemSlot = oMisc;
   static constexpr int oAbort = oMisc + 4;
   static constexpr int oVote = oMisc + 8;                // 2 ints
   static constexpr int oMref = oMisc + 16;
   static constexpr int oWmax = oMref + 2 * NT * 4;
   static constexpr int oLsum = oWmax + 4 * NT * 4;
-  static constexpr int oPrefix = oLsum + NT * 4;
+  static constexpr int oFac = oLsum + NT * 4;
+  static constexpr int oPrefix = oFac + NT * 4;
   static constexpr int kMaxB = 2048;
   static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4 + 1024;   // + slack for the 1024 alignment
   // TMEM columns
@@ -208,7 +256,7 @@ struct Walker {
   }
   UQ_DEV int item_tiles(int item) const { const int b = item / HKV; return prefix[b + 1] - prefix[b]; }
   UQ_DEV int item_start(int item) const { const int b = item / HKV, hk = item % HKV; return HKV * prefix[b] + hk * (prefix[b + 1] - prefix[b]); }
-  UQ_DEV bool next(Seg& s) {
+  __device__ __noinline__ bool next(Seg& s) {
     if (per_item) {
       for (it += (int)gridDim.x; it < nitems; it += (int)gridDim.x) {
         const int n = item_tiles(it);
@@ -257,31 +305,27 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   auto bar_raw_empty = [&](int s) { return sm_a + C::oBar + 8 * (kRawStages + s); };
   auto bar = [&](int i) { return sm_a + C::oBar + 8 * (2 * kRawStages + i); };
 
-  // bounded wait; false = gave up (this thread or another one), the caller leaves its loop
-  auto wait = [&](uint32_t b, uint32_t parity, int id, int tile) -> bool {
-    if (mbar_try(b, parity)) return true;
-    const unsigned long long t_start = now_ns();
-    for (unsigned it = 1;; it++) {
-      if (mbar_try(b, parity)) return true;
-      if ((it & 63u) == 0u) {
-        if (*abort_flag) return false;
-        if (now_ns() - t_start > 1000000000ull) {
-          *abort_flag = 1;
-          uq_report(x.status, 1u, (unsigned)id, (unsigned)tile);
-          return false;
-        }
-      }
-    }
+  // bounded wait (out of line: it is called from ~25 sites and the kernel's speed depends on its code staying in the instruction cache)
+  auto wait = [&](uint32_t b, uint32_t parity, int id, int tile, unsigned long long* site) -> bool {
+    return bounded_wait(b, parity, abort_flag, x.status, id, tile, site);
+  };
+
+  // one arrival per warp: every lane's earlier writes are ordered before it by the warp barrier
+  auto warp_arrive = [&](uint32_t b) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(b);
   };
 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 256); }
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 8); }
     for (int i = 0; i < 2; i++) {
-      mbar_init(bar(bKfull + i), 128); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 128);
-      mbar_init(bar(bVfull + i), 128); mbar_init(bar(bPfull + i), 128); mbar_init(bar(bPVdone + i), 1);
+      // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
+      // barrier serialise in the shared-memory unit and cost more than the work they order
+      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 4);
+      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 4); mbar_init(bar(bPVdone + i), 1);
     }
-    mbar_init(bar(bQfull), 128); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 128); mbar_init(bar(bVote), 128);
+    mbar_init(bar(bQfull), 4); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4); mbar_init(bar(bVote), 4);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
     reinterpret_cast<int*>(sm + C::oVote)[1] = 0;
@@ -314,6 +358,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   if (warp == 12) {
     // ================================================================= producer
     const int ppt = kKeys / p.PAGE;   // pages per tile
+    UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kGroups;
     int cnt = 0;
     bool ok = true;
@@ -327,7 +372,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const int vp = min(ppt, pages_valid - t * ppt);
         int pid = 0;
         if (lane < vp) pid = __ldg(bt + t * ppt + lane);
-        ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t);
+        ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t dst = sm_a + C::oRaw + stage * C::kRawStage;
@@ -343,16 +388,18 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         }
       }
     }
+    UQ_PROF_FLUSH(0, lane == 0)
   } else if (warp == 13) {
     // ================================================================= MMA issue
     constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0);
     constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1);
     int cnt = 0, seg_i = 0;
     bool ok = true;
+    UQ_PROF_DECL
     auto issue_pv = [&](int c, int first) {   // c = global tile counter of the tile whose P/V are consumed
       const int buf = c & 1;
-      if (!wait(bar(bPfull + buf), (c >> 1) & 1, 20 + buf, c)) return false;
-      if (!wait(bar(bVfull + buf), (c >> 1) & 1, 22 + buf, c)) return false;
+      if (!wait(bar(bPfull + buf), (c >> 1) & 1, 20 + buf, c UQ_PROF_SITE(4))) return false;
+      if (!wait(bar(bVfull + buf), (c >> 1) & 1, 22 + buf, c UQ_PROF_SITE(5))) return false;
       tc_fence_after();
       const uint32_t va = sm_a + C::oV + buf * C::kVTile, pa = sm_a + C::oP + buf * C::kPTile;
 #pragma unroll
@@ -363,13 +410,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     };
     while (ok && wk.next(sg)) {
       if (lane == 0) {
-        ok = wait(bar(bQfull), seg_i & 1, 30, seg_i);
-        if (ok && seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i);   // previous segment's O has been read
+        ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
+        if (ok && seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i UQ_PROF_SITE(1));   // previous segment's O has been read
         const int c0 = cnt;
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
           const int buf = cnt & 1;
-          ok = wait(bar(bKfull + buf), (cnt >> 1) & 1, 24 + buf, cnt);
-          if (ok && cnt >= 2) ok = wait(bar(bSfree + buf), ((cnt >> 1) - 1) & 1, 26 + buf, cnt);
+          ok = wait(bar(bKfull + buf), (cnt >> 1) & 1, 24 + buf, cnt UQ_PROF_SITE(2));
+          if (ok && cnt >= 2) ok = wait(bar(bSfree + buf), ((cnt >> 1) - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
           if (!ok) break;
           tc_fence_after();
           const uint32_t qa = sm_a + C::oQ;
@@ -387,95 +434,97 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       seg_i++;
     }
+    UQ_PROF_FLUSH(1, lane == 0)
   } else if (warp >= 4 && warp < 8) {
     // ================================================================= K decode -> TMEM
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     int cnt = 0;
     bool ok = true;
+    UQ_PROF_DECL
     while (ok && wk.next(sg)) {
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
         const int stage = cnt % kRawStages, buf = cnt & 1;
-        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt);
-        if (ok && cnt >= 2) ok = wait(bar(bSfull + buf), ((cnt >> 1) - 1) & 1, 44 + buf, cnt);   // S^T(cnt-2) done: its A operand is free
+        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= 2) ok = wait(bar(bSfull + buf), ((cnt >> 1) - 1) & 1, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T(cnt-2) done: its A operand is free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
         const bool big = __any_sync(0xffffffffu, (sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u);
-#pragma unroll
+#pragma unroll 1
         for (int g = 0; g < C::kGroups; g++) {
           // 64-byte-swizzled row: logical 16-byte chunk g sits at chunk g ^ ((key >> 1) & 3)
           const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
           const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
           uint32_t o[16];
-          if (!big) {
-            const uint32_t m = scale_mult(s);
-            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
-          } else {
-            const uint32_t s1 = s > 192u ? s - 96u : s, m = scale_mult(s1), m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;   // 2^96 or 1
-            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          const uint32_t m = scale_mult(s > 192u ? s - 96u : s);
+          decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          if (big) {   // some scale byte of this warp's keys is above 192: second multiply by 2^96 (or 1)
+            const uint32_t m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
 #pragma unroll
             for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
           }
           tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
         }
+        UQ_PROF_T1(2)
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(bar(bKfull + buf));
-        mbar_arrive(bar_raw_empty(stage));
+        warp_arrive(bar(bKfull + buf));
+        warp_arrive(bar_raw_empty(stage));
+        UQ_PROF_T1(3)
       }
     }
+    UQ_PROF_FLUSH(2, kk == 0)
   } else if (warp >= 8 && warp < 12) {
     // ================================================================= V decode -> shared memory
     const int kk = (warp - 8) * 32 + lane;
     int cnt = 0;
     bool ok = true;
+    UQ_PROF_DECL
     while (ok && wk.next(sg)) {
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
         const int stage = cnt % kRawStages, buf = cnt & 1;
-        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 50 + stage, cnt);
-        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 54 + buf, cnt);   // O^T += of tile cnt-2 done: tile buffer free
+        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 50 + stage, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of tile cnt-2 done: tile buffer free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kRawCodes;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * 4);
         const bool big = __any_sync(0xffffffffu, live && ((sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u));
-#pragma unroll
+#pragma unroll 1
         for (int g = 0; g < C::kGroups; g++) {
           const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
           const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
           uint32_t o[16];
-          if (!big) {
-            const uint32_t m = scale_mult(s);
-            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
-          } else {
-            const uint32_t s1 = s > 192u ? s - 96u : s, m = scale_mult(s1), m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
-            decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          const uint32_t m = live ? scale_mult(s > 192u ? s - 96u : s) : 0u;   // multiplier 0: keys past the end decode to zeros
+          decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
+          if (big) {
+            const uint32_t m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
 #pragma unroll
             for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
           }
-          if (!live) {
-#pragma unroll
-            for (int i = 0; i < 16; i++) o[i] = 0u;
-          }
           // output chunk oc = 4g + w (8 channels) of the key's 256-byte row: half oc >> 3, slot (oc & 7) ^ (key & 7)
+          uint8_t* vrow = vt + (g >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
-          for (int w = 0; w < 4; w++) {
-            const int oc = 4 * g + w;
-            *reinterpret_cast<uint4*>(vt + (oc >> 3) * C::kVHalf + kk * 128 + (((oc & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
-          }
+          for (int w = 0; w < 4; w++)
+            *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
         }
+        UQ_PROF_T1(2)
         fence_async_smem();
-        mbar_arrive(bar(bVfull + buf));
-        mbar_arrive(bar_raw_empty(stage));
+        warp_arrive(bar(bVfull + buf));
+        warp_arrive(bar_raw_empty(stage));
+        UQ_PROF_T1(3)
       }
     }
+    UQ_PROF_FLUSH(3, kk == 0)
   } else if (warp < 4) {
     // ================================================================= softmax + epilogue
     const int quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = 0..127 index within the role
@@ -483,11 +532,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     float* mref = reinterpret_cast<float*>(sm + C::oMref);     // [2][NT], the live copy is mref + mcur * NT
     float* wmax = reinterpret_cast<float*>(sm + C::oWmax);     // [4][NT]
     float* lsum = reinterpret_cast<float*>(sm + C::oLsum);
+    float* fac_s = reinterpret_cast<float*>(sm + C::oFac);      // per-row rescale factors of a reference move
     int* vote = reinterpret_cast<int*>(sm + C::oVote);
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
     const float csc = x.sc2 * 18446744073709551616.0f;   // scores carry the 2^-64 of the decoded K
     int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
     bool ok = true;
+    UQ_PROF_DECL
     // items without a single key: nobody computes them, their slots must read as empty
     for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
@@ -508,14 +559,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       if (st < NT) { mref[mcur * NT + st] = kNegBig; lsum[st] = 0.f; }
       fence_async_smem();
-      mbar_arrive(bar(bQfull));
+      warp_arrive(bar(bQfull));
       // the first segment of an item marks the slots the item does not use as empty
       if (sg.t0 == 0)
         for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 128)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
       // the reference row maxima written above must be visible to all 128 threads before the first tile
-      mbar_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 60, seg_i);
+      warp_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 60, seg_i UQ_PROF_SITE(5));
       nvote++;
       ok = __all_sync(0xffffffffu, ok);
       float l[NT];
@@ -524,7 +575,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       const int c0 = cnt;
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
         const int buf = cnt & 1;
-        ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt);
+        ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -537,7 +588,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const float* mr = mref + mcur * NT;
         // ---- pass 1: does any visible score leave the window of its row's reference maximum?
         float xm = kNegBig;
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < NT / 16; c++) {
           uint32_t sv[16];
           tmem_ld16(s_addr + c * 16, sv);
@@ -551,15 +602,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         }
         const bool mine = xm > kRescaleAt;
         if (__any_sync(0xffffffffu, mine) && lane == 0) atomicOr(&vote[nvote & 1], 1);
-        mbar_arrive(bar(bVote));
-        ok = wait(bar(bVote), nvote & 1, 64, cnt);
+        warp_arrive(bar(bVote));
+        ok = wait(bar(bVote), nvote & 1, 64, cnt UQ_PROF_SITE(1));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const int moved = *reinterpret_cast<volatile int*>(&vote[nvote & 1]);
         nvote++;
         if (moved) {
+          UQ_PROF_COUNT(6)
           // ---- move the reference maxima of this segment's rows (the first tile, then only on growth)
-#pragma unroll
+#pragma unroll 1
           for (int c = 0; c < NT / 16; c++) {
             uint32_t sv[16];
             tmem_ld16(s_addr + c * 16, sv);
@@ -573,46 +625,46 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
               if (lane == 0) wmax[quad * NT + r] = v;
             }
           }
-          mbar_arrive(bar(bVote));
-          ok = wait(bar(bVote), nvote & 1, 65, cnt);
+          warp_arrive(bar(bVote));
+          ok = wait(bar(bVote), nvote & 1, 65, cnt UQ_PROF_SITE(2));
           nvote++;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (st == 0) vote[0] = vote[1] = 0;
-          float* mn = mref + (mcur ^ 1) * NT;
-          auto new_ref = [&](int r) { return fmaxf(fmaxf(mr[r], fmaxf(wmax[r], wmax[NT + r])), fmaxf(wmax[2 * NT + r], wmax[3 * NT + r])); };
-#pragma unroll
-          for (int r = 0; r < NT; r++) {
-            const float m_new = new_ref(r);
-            l[r] *= fast_exp2(mr[r] - m_new);   // first tile: 2^(-1e30 - m) = 0
-            if (st == r) mn[r] = m_new;
+          if (st < NT) {   // thread r owns row r: new reference, and the factor everything accumulated so far shrinks by
+            const float m_old = mr[st];
+            const float m_new = fmaxf(fmaxf(m_old, fmaxf(wmax[st], wmax[NT + st])), fmaxf(wmax[2 * NT + st], wmax[3 * NT + st]));
+            mref[(mcur ^ 1) * NT + st] = m_new;
+            fac_s[st] = fast_exp2(m_old - m_new);   // first tile: 2^(-1e30 - m) = 0
           }
+          warp_arrive(bar(bVote));
+          ok = wait(bar(bVote), nvote & 1, 67, cnt UQ_PROF_SITE(2));
+          nvote++;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+#pragma unroll
+          for (int r = 0; r < NT; r++) l[r] *= fac_s[r];
           if (cnt > c0) {
             // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's lane
-            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt);
+            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt UQ_PROF_SITE(2));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-#pragma unroll
+#pragma unroll 1
             for (int c = 0; c < NT / 16; c++) {
               uint32_t ov[16];
               tmem_ld16(lane_addr + C::cO + c * 16, ov);
               tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * fast_exp2(mr[c * 16 + i] - new_ref(c * 16 + i)));
+              for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * fac_s[c * 16 + i]);
               tmem_st16(lane_addr + C::cO + c * 16, ov);
             }
             tc_wait_st();
           }
-          mcur ^= 1;
-          mbar_arrive(bar(bVote));          // new references and cleared votes visible before anyone's next tile
-          ok = wait(bar(bVote), nvote & 1, 67, cnt);
-          nvote++;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
+          mcur ^= 1;   // the next tile's vote rendezvous keeps fac_s / wmax from being overwritten while still read
         }
         if (cnt >= 2) {
-          ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt);   // P buffer free
+          ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(3));   // P buffer free
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
@@ -626,7 +678,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           tc_wait_ld();
           if (c == NT / 16 - 1) {   // the S^T buffer is in registers now
             tc_fence_before();
-            mbar_arrive(bar(bSfree + buf));
+            warp_arrive(bar(bSfree + buf));
           }
           float pv[16];
 #pragma unroll
@@ -642,7 +694,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
               make_uint4(pack_bf16x2(pv[8], pv[9]), pack_bf16x2(pv[10], pv[11]), pack_bf16x2(pv[12], pv[13]), pack_bf16x2(pv[14], pv[15]));
         }
         fence_async_smem();
-        mbar_arrive(bar(bPfull + buf));
+        warp_arrive(bar(bPfull + buf));
       }
       if (!ok) break;
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
@@ -653,10 +705,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
         if (lane == 0) atomicAdd(&lsum[r], v);
       }
-      mbar_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 70, seg_i);
+      warp_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 70, seg_i UQ_PROF_SITE(5));
       nvote++;
-      if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i);
+      if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(4));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -681,14 +733,15 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       tc_fence_before();
-      mbar_arrive(bar(bEpi));
+      warp_arrive(bar(bEpi));
       // everyone has read lsum / mref before the next segment overwrites them
-      mbar_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 72, seg_i);
+      warp_arrive(bar(bVote));
+      ok = wait(bar(bVote), nvote & 1, 72, seg_i UQ_PROF_SITE(5));
       nvote++;
       ok = __all_sync(0xffffffffu, ok);
       seg_i++;
     }
+    UQ_PROF_FLUSH(4, st == 0)
   }
 
   // ---- common exit: every role gets here (all waits are bounded); TMEM goes back before the CTA ends
@@ -761,6 +814,17 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
 }
 
 }  // namespace tc
+
+#ifdef UQ_TC_PROF
+// profiling build only: read and clear the per-role cycle counters (5 roles x 8 counters)
+extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out40, tc::g_tc_prof, sizeof(unsigned long long) * 40);
+  static const unsigned long long zero[40] = {0};
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(tc::g_tc_prof, zero, sizeof(zero));
+  return (int)e;
+}
+#endif
 
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
   if (p.D != 128) return false;
