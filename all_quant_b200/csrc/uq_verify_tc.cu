@@ -94,8 +94,8 @@ UQ_DEV uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // instruction descriptor, kind::f16: bf16 x bf16 -> fp32; major 0 = K-major, 1 = MN-major
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major, int a_bf16 = 1, int b_bf16 = 1) {
+  return (1u << 4) | ((uint32_t)a_bf16 << 7) | ((uint32_t)b_bf16 << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 UQ_DEV void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
@@ -122,6 +122,11 @@ UQ_DEV uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
 UQ_DEV float fast_exp2(float v) {   // 2^v, -inf -> 0
   float d;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(v));
+  return d;
+}
+UQ_DEV uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
   return d;
 }
 UQ_DEV uint32_t pack_bf16x2(float lo, float hi) {
@@ -174,6 +179,36 @@ UQ_DEV void decode8(uint32_t w, uint32_t mult, uint32_t* out) {
 // position p (0..7) of a decoded octet holds channel (p >> 1) + 4 * (p & 1); queries are laid out to match
 UQ_DEV int octet_channel(int p) { return (p >> 1) + 4 * (p & 1); }
 
+// ---- second decode path: hardware e2m1 -> fp16 conversion (UQ_TC_BF16_DECODE selects the integer/bf16 path above instead)
+// One cvt per byte gives the two channels of the byte as an exact fp16 pair in natural order (low nibble = even
+// channel), zero and sign included; one fp16 multiply applies the group scale RELATIVE to the key's largest group
+// scale, 2^(s_g - ref) <= 1 (exact down to 2^-24, zero below: such a group is < 2^-24 of the key's largest).  The key's
+// reference 2^(ref - 127) is applied in fp32 by the softmax thread that owns the key: to the score (K) and to the
+// probability (V).  Operands: K and V fp16, Q and P bf16, accumulators fp32.
+// Both operands of one tcgen05.mma kind::f16 must have the same 16-bit format on this hardware (an fp16 A with a bf16 B
+// raised "illegal instruction"), so the switch is per contraction: kF16K = K and Q in fp16, kF16V = V and P in fp16.
+#ifdef UQ_TC_BF16_DECODE
+constexpr bool kF16K = false;
+#else
+constexpr bool kF16K = true;
+#endif
+constexpr bool kF16V = false;
+UQ_DEV void decode8_f16(uint32_t w, uint32_t mult, uint32_t* out) {
+  uint32_t a, b, c, d;
+  asm("{\n .reg .b8 t0, t1, t2, t3;\n mov.b32 {t0, t1, t2, t3}, %4;\n cvt.rn.f16x2.e2m1x2 %0, t0;\n cvt.rn.f16x2.e2m1x2 %1, t1;\n"
+      " cvt.rn.f16x2.e2m1x2 %2, t2;\n cvt.rn.f16x2.e2m1x2 %3, t3;\n}" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(w));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[0]) : "r"(a), "r"(mult));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[1]) : "r"(b), "r"(mult));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[2]) : "r"(c), "r"(mult));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[3]) : "r"(d), "r"(mult));
+}
+// 2^e (e <= 0) as an fp16 pair: normal down to 2^-14, subnormal down to 2^-24, zero below
+UQ_DEV uint32_t pow2_f16x2(int e) {
+  const uint32_t b = e >= -14 ? (uint32_t)(e + 15) << 10 : (e >= -24 ? 1u << (e + 24) : 0u);
+  return b | (b << 16);
+}
+UQ_DEV uint32_t max_byte(uint32_t v) { return max(max(v & 0xFFu, (v >> 8) & 0xFFu), max((v >> 16) & 0xFFu, v >> 24)); }
+
 // group multiplier 2^(s-65) as bf16x2 for s <= 192; above that the caller multiplies twice
 UQ_DEV uint32_t scale_mult(uint32_t s) {
   const uint32_t b = (s + 62u) << 7;
@@ -211,7 +246,9 @@ struct Cfg {
   static constexpr int oWmax = oMref + 2 * NT * 4;
   static constexpr int oLsum = oWmax + 4 * NT * 4;
   static constexpr int oFac = oLsum + NT * 4;
-  static constexpr int oPrefix = oFac + NT * 4;
+  static constexpr int oRef = oFac + NT * 4;          // [4][128] uint16: K reference byte | V reference byte << 8 of the last four tiles (a slot is rewritten only
+                                                      // after the S^T buffer two tiles back was released, i.e. after its reader is done)
+  static constexpr int oPrefix = oRef + 4 * kKeys * 2;
   static constexpr int kMaxB = 2048;
   static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4 + 1024;   // + slack for the 1024 alignment
   // TMEM columns
@@ -391,8 +428,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     UQ_PROF_FLUSH(0, lane == 0)
   } else if (warp == 13) {
     // ================================================================= MMA issue
-    constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0);
-    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1);
+    constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, kF16K ? 0 : 1, kF16K ? 0 : 1);   // A = K, B = Q: both fp16 or both bf16
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, kF16V ? 0 : 1, kF16V ? 0 : 1);   // A = V, B = P: both fp16 or both bf16
     int cnt = 0, seg_i = 0;
     bool ok = true;
     UQ_PROF_DECL
@@ -453,6 +490,21 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
+        if (kF16K) {
+          const uint32_t kref = max_byte(sc4);
+          const uint32_t vref = max_byte(*reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + C::kRawScales + kk * 4));
+          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax thread of this key
+          uint4 c4[C::kGroups];
+#pragma unroll
+          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+#pragma unroll
+          for (int g = 0; g < C::kGroups; g++) {
+            const uint32_t m = pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - (int)kref);
+            uint32_t o[16];
+            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
+            tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
+          }
+        } else {
         const bool big = __any_sync(0xffffffffu, (sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u);
 #pragma unroll 1
         for (int g = 0; g < C::kGroups; g++) {
@@ -468,6 +520,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
           }
           tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
+        }
         }
         UQ_PROF_T1(2)
         tc_wait_st();
@@ -498,6 +551,22 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * 4);
+        if (kF16V) {
+          const int vref = (int)max_byte(sc4);
+          uint4 c4[C::kGroups];
+#pragma unroll
+          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+#pragma unroll
+          for (int g = 0; g < C::kGroups; g++) {
+            const uint32_t m = live ? pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - vref) : 0u;   // multiplier 0: keys past the end decode to zeros
+            uint32_t o[16];
+            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
+            uint8_t* vrow = vt + (g >> 1) * C::kVHalf + kk * 128;
+#pragma unroll
+            for (int w = 0; w < 4; w++)
+              *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
+          }
+        } else {
         const bool big = __any_sync(0xffffffffu, live && ((sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u));
 #pragma unroll 1
         for (int g = 0; g < C::kGroups; g++) {
@@ -517,6 +586,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           for (int w = 0; w < 4; w++)
             *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
         }
+        }
         UQ_PROF_T1(2)
         fence_async_smem();
         warp_arrive(bar(bVfull + buf));
@@ -535,7 +605,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     float* fac_s = reinterpret_cast<float*>(sm + C::oFac);      // per-row rescale factors of a reference move
     int* vote = reinterpret_cast<int*>(sm + C::oVote);
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
-    const float csc = x.sc2 * 18446744073709551616.0f;   // scores carry the 2^-64 of the decoded K
+    float csc0 = x.sc2 * 18446744073709551616.0f;   // bf16 K path: scores carry the 2^-64 of the decoded K
     int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
     bool ok = true;
     UQ_PROF_DECL
@@ -549,6 +619,44 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int n_glob = p.seq_lens[sg.b];
+      if (kF16K) {
+        // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
+        // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
+        // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
+        uint32_t amax = 0;   // bf16 magnitudes compare as integers
+        for (int i = st; i < rows * (D / 8); i += 128) {
+          const int n = i / (D / 8), a = i % (D / 8);
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) amax = max(amax, max(w4[j] & 0x7FFFu, (w4[j] >> 16) & 0x7FFFu));
+        }
+        amax = __reduce_max_sync(0xffffffffu, amax);
+        if (lane == 0) reinterpret_cast<uint32_t*>(wmax)[quad] = amax;
+        warp_arrive(bar(bVote));
+        ok = wait(bar(bVote), nvote & 1, 59, seg_i UQ_PROF_SITE(5));
+        nvote++;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t* wq = reinterpret_cast<const uint32_t*>(wmax);
+        amax = max(max(wq[0], wq[1]), max(wq[2], wq[3]));
+        int eq = amax ? (int)(amax >> 7) - 127 : 0;
+        eq = min(max(eq, -126), 126);
+        const float qf = __int_as_float((127 - eq) << 23);
+        csc0 = x.sc2 * __int_as_float((127 + eq) << 23);
+        for (int i = st; i < NT * (D / 8); i += 128) {
+          const int n = i / (D / 8), a = i % (D / 8);
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (n < rows) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
+            w.x = pack_f16x2(__uint_as_float(v.x << 16) * qf, __uint_as_float(v.x & 0xFFFF0000u) * qf);
+            w.y = pack_f16x2(__uint_as_float(v.y << 16) * qf, __uint_as_float(v.y & 0xFFFF0000u) * qf);
+            w.z = pack_f16x2(__uint_as_float(v.z << 16) * qf, __uint_as_float(v.z & 0xFFFF0000u) * qf);
+            w.w = pack_f16x2(__uint_as_float(v.w << 16) * qf, __uint_as_float(v.w & 0xFFFF0000u) * qf);
+          }
+          *reinterpret_cast<uint4*>(sm + C::oQ + (a >> 3) * C::kQHalf + n * 128 + (((a & 7) ^ (n & 7)) << 4)) = w;
+        }
+      } else {
       // ---- query tile: [row][position], octets permuted like the decoded K, 128-byte swizzle, two 64-position halves
       for (int i = st; i < NT * (D / 8); i += 128) {
         const int n = i / (D / 8), a = i % (D / 8);
@@ -556,6 +664,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (n < rows) v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
         const uint4 w = make_uint4(__byte_perm(v.x, v.z, 0x5410), __byte_perm(v.x, v.z, 0x7632), __byte_perm(v.y, v.w, 0x5410), __byte_perm(v.y, v.w, 0x7632));
         *reinterpret_cast<uint4*>(sm + C::oQ + (a >> 3) * C::kQHalf + n * 128 + (((a & 7) ^ (n & 7)) << 4)) = w;
+      }
       }
       if (st < NT) { mref[mcur * NT + st] = kNegBig; lsum[st] = 0.f; }
       fence_async_smem();
@@ -580,6 +689,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (!ok) break;
         tc_fence_after();
         const uint32_t s_addr = lane_addr + C::cS + buf * NT;
+        // this key's reference scales (fp16 path): K's multiplies the score, V's multiplies the probability
+        float csc = csc0, vfac = 1.f;
+        if (kF16K || kF16V) {
+          const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk];
+          if (kF16K) csc = csc0 * uq_scale_f32(rf & 0xFFu);
+          if (kF16V) vfac = t * kKeys + kk < n_loc ? uq_scale_f32(rf >> 8) : 0.f;   // past the end the bytes are arbitrary: keep 0 * vfac finite
+        }
         // rows this key is visible to: r >= rmin (causal limit among the drafts); none if past the end
         const int key = t * kKeys + kk;
         int rmin = 0;
@@ -688,6 +804,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             pv[i] = (r >= rmin && r < rows) ? v : 0.f;
             l[r] += pv[i];
           }
+          if (kF16V) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) pv[i] *= vfac;
+          }
           *reinterpret_cast<uint4*>(pt + (((2 * c) ^ (kk & 7)) << 4)) =
               make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
           *reinterpret_cast<uint4*>(pt + (((2 * c + 1) ^ (kk & 7)) << 4)) =
@@ -715,7 +835,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       const size_t slot = uq_slot(p, sg.b, sg.hk, sg.slot);
       float* mo = p.mo + slot * x.BM * D;
       float* ml = p.ml + slot * x.BM;
-      const int dch = (kk & ~7) + octet_channel(kk & 7);   // channel held by accumulator lane kk
+      const int dch = kF16V ? kk : (kk & ~7) + octet_channel(kk & 7);   // channel held by accumulator lane kk
       const float* mr = mref + mcur * NT;
 #pragma unroll
       for (int c = 0; c < NT / 16; c++) {
@@ -727,7 +847,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           const int r = c * 16 + i;
           if (r < rows) {
             const float lr = lsum[r];
-            mo[(size_t)r * D + dch] = lr > 0.f ? __uint_as_float(ov[i]) * (18446744073709551616.0f / lr) : 0.f;
+            mo[(size_t)r * D + dch] = lr > 0.f ? __uint_as_float(ov[i]) * ((kF16V ? 1.0f : 18446744073709551616.0f) / lr) : 0.f;
           }
         }
       }
