@@ -137,22 +137,10 @@ UQ_DEV uint32_t pack_bf16x2(float lo, float hi) {
 
 // Wait for phase `parity` of an mbarrier, for about one second at most.  false = gave up (this thread's wait ran
 // out, or another thread of the CTA raised the abort flag): the caller leaves its loop and falls through to the exit.
-__device__ __noinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, int id, int tile,
-                                          unsigned long long* site) {
-#ifdef UQ_TC_PROF
-  const long long c_start = clock64();
-  if (mbar_try(bar, parity)) { if (site) *site += clock64() - c_start; return true; }
-#else
-  if (mbar_try(bar, parity)) return true;
-#endif
+__device__ __noinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, int id, int tile) {
   const unsigned long long t_start = now_ns();
   for (unsigned it = 1;; it++) {
-    if (mbar_try(bar, parity)) {
-#ifdef UQ_TC_PROF
-      if (site) *site += clock64() - c_start;
-#endif
-      return true;
-    }
+    if (mbar_try(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
       if (now_ns() - t_start > 1000000000ull) {
@@ -342,9 +330,19 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   auto bar_raw_empty = [&](int s) { return sm_a + C::oBar + 8 * (kRawStages + s); };
   auto bar = [&](int i) { return sm_a + C::oBar + 8 * (2 * kRawStages + i); };
 
-  // bounded wait (out of line: it is called from ~25 sites and the kernel's speed depends on its code staying in the instruction cache)
+  // Wait on an mbarrier: two blocking tries inline (try_wait itself suspends the thread for a while, so these almost always
+  // suffice), then the out-of-line bounded wait.  The call sits on the rare path so that the registers live across it
+  // are not saved and restored on every tile.
   auto wait = [&](uint32_t b, uint32_t parity, int id, int tile, unsigned long long* site) -> bool {
-    return bounded_wait(b, parity, abort_flag, x.status, id, tile, site);
+#ifdef UQ_TC_PROF
+    const long long c_start = clock64();
+#endif
+    bool r = mbar_try(b, parity) || mbar_try(b, parity);
+    if (!r) r = bounded_wait(b, parity, abort_flag, x.status, id, tile);
+#ifdef UQ_TC_PROF
+    if (site) *site += clock64() - c_start;
+#endif
+    return r;
   };
 
   // one arrival per warp: every lane's earlier writes are ordered before it by the warp barrier
@@ -429,19 +427,27 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   } else if (warp == 13) {
     // ================================================================= MMA issue
     constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, kF16K ? 0 : 1, kF16K ? 0 : 1);   // A = K, B = Q: both fp16 or both bf16
-    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, kF16V ? 0 : 1, kF16V ? 0 : 1);   // A = V, B = P: both fp16 or both bf16
+    #ifdef UQ_TC_EXP_KMAJOR_PV   // timing experiment only (wrong results): declare the P.V operands K-major
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 0, 0, kF16V ? 0 : 1, kF16V ? 0 : 1);
+#else
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, kF16V ? 0 : 1, kF16V ? 0 : 1);
+#endif
+      // A = V, B = P: both fp16 or both bf16
     int cnt = 0, seg_i = 0;
     bool ok = true;
     UQ_PROF_DECL
+    // descriptors differ between instructions only in the start-address field (bits 0-13, units of 16 bytes)
+    const uint64_t q_desc = smem_desc(sm_a + C::oQ, 16, 1024);
+    const uint64_t v_desc = smem_desc(sm_a + C::oV, C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
     auto issue_pv = [&](int c, int first) {   // c = global tile counter of the tile whose P/V are consumed
       const int buf = c & 1;
       if (!wait(bar(bPfull + buf), (c >> 1) & 1, 20 + buf, c UQ_PROF_SITE(4))) return false;
       if (!wait(bar(bVfull + buf), (c >> 1) & 1, 22 + buf, c UQ_PROF_SITE(5))) return false;
       tc_fence_after();
-      const uint32_t va = sm_a + C::oV + buf * C::kVTile, pa = sm_a + C::oP + buf * C::kPTile;
+      const uint64_t va = v_desc + (uint64_t)(buf * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; kk++)
-        mma_ss(tmem + C::cO, smem_desc(va + kk * 2048, C::kVHalf, 1024), smem_desc(pa + kk * 2048, C::kVHalf, 1024), idesc_pv, (first && kk == 0) ? 0u : 1u);
+        mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (first && kk == 0) ? 0u : 1u);
       tc_commit(bar(bPVdone + buf));
       return true;
     };
@@ -456,11 +462,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (ok && cnt >= 2) ok = wait(bar(bSfree + buf), ((cnt >> 1) - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
           if (!ok) break;
           tc_fence_after();
-          const uint32_t qa = sm_a + C::oQ;
+          UQ_PROF_T0
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++)
-            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, smem_desc(qa + (ks >> 2) * C::kQHalf + (ks & 3) * 32, 16, 1024), idesc_qk, ks ? 1u : 0u);
+            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
           tc_commit(bar(bSfull + buf));
+          UQ_PROF_T1(6)
           if (cnt > c0) ok = issue_pv(cnt - 1, cnt - 1 == c0);
         }
         if (ok) ok = issue_pv(cnt - 1, cnt - 1 == c0);
