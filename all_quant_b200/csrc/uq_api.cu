@@ -18,6 +18,12 @@
 
 __device__ unsigned int g_uq_status[4];
 
+// Built-in scratch of uqb_decode_launch_static: 24 MiB of fp32 partials, resident on every device that loads the
+// library from the moment the module is loaded until the process exits.  In host code this name is only a handle
+// for the runtime, never an address a kernel can use: the device address comes from cudaGetSymbolAddress.
+constexpr size_t kStaticScratchFloats = (size_t)24 * 1024 * 1024 / sizeof(float);
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
 cudaError_t uq_append_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, cudaStream_t);
 cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
@@ -178,6 +184,31 @@ int uqb_last_status(uint32_t out4[4]) {
   if (e != cudaSuccess) return (int)e;
   const unsigned int zero[4] = {0, 0, 0, 0};
   return (int)cudaMemcpyToSymbol(g_uq_status, zero, sizeof(zero));
+}
+
+size_t uqb_static_scratch_bytes(void) { return kStaticScratchFloats * sizeof(float); }
+
+int uqb_decode_launch_static(const UQParams* p, int nwarps, int stages, void* stream) {
+  if (!p) return (int)cudaErrorInvalidValue;
+  if (p->nsplit < 1 || p->nsplit > 128 || p->B < 0 || p->K < 1 || p->HKV < 1 || p->HQ < 1 || p->D < 1) return (int)cudaErrorInvalidValue;
+  // the partials of this call must fit the built-in array: refuse, before anything is enqueued, a call that needs more
+  if (uq_mo_elems(*p) + uq_ml_elems(*p) > kStaticScratchFloats) return (int)cudaErrorInvalidValue;
+  // once per device, with that device current: ask the runtime where the array lives on this device
+  static float* base[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    base[dev] = reinterpret_cast<float*>(ptr);
+  }
+  UQParams q = *p;
+  q.mo = base[dev];
+  q.ml = base[dev] + uq_mo_elems(q);
+  return (int)uq_decode_launch(q, nwarps, stages, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int uqb_last_path(void) { return t_last_path; }

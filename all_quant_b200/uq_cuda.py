@@ -34,7 +34,8 @@ class UQParams(ctypes.Structure):
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
            "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_merge_launch", "uqb_last_status",
-           "uqb_last_path", "uqb_launch_count", "uqb_debug_events")
+           "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
+           "uqb_decode_launch_static", "uqb_static_scratch_bytes")
 
 
 def lib():
@@ -59,6 +60,8 @@ def lib():
         L.uqb_launch_count.restype = ctypes.c_ulonglong
         L.uqb_debug_events.argtypes = [vp, vp]
         L.uqb_debug_events.restype = None
+        L.uqb_decode_launch_static.argtypes = [pp, i, i, vp]
+        L.uqb_static_scratch_bytes.restype = sz
         _lib = L
     return _lib
 
@@ -187,6 +190,32 @@ def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nspl
     bt = block_table.repeat_interleave(K, 0)
     sl = (seq_lens.repeat_interleave(K) - K + torch.arange(K, device=q.device).repeat(B) + 1).to(torch.int32)
     return e.decode(qs, kc, ks, vc, vs, bt, sl, nsplit, nwarps, stages, variant, mb, sm_scale, None, None, None, fmt, k_ts, v_ts).reshape(B, K, HQ, D)
+
+
+def uq_decode_static(q, kc, ks, vc, vs, block_table, seq_lens, out, *, nsplit=None, sm_scale=None):
+    """uq_decode_cuda for hosts that may not allocate device memory around the call: the split-KV partials go to the
+    24 MiB array built into the library instead of a torch allocation, and `out` (bf16, shape of q) must be supplied.
+    block_table / seq_lens must already be int32 and q contiguous, so that nothing is converted (and allocated) here.
+    Raises if the call's partials do not fit the built-in array; calls sharing a device must not overlap on the GPU."""
+    _need_cuda(q, kc, ks, vc, vs, block_table, seq_lens, out)
+    if not (q.dtype == torch.bfloat16 and q.is_contiguous() and out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == q.shape):
+        raise RuntimeError("q and out must be contiguous bf16 of the same shape")
+    if block_table.dtype != torch.int32 or seq_lens.dtype != torch.int32 or not block_table.is_contiguous():
+        raise RuntimeError("bt/sl must be int32 (contiguous)")
+    B, K, HQ, D = q.shape
+    HKV = kc.shape[1]
+    if nsplit is None:
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+    p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale if sm_scale is not None else D ** -0.5)
+    p.out = out.data_ptr()
+    L = lib()
+    need, have = int(L.uqb_workspace_bytes(ctypes.byref(p))), int(L.uqb_static_scratch_bytes())
+    if need > have:
+        raise RuntimeError(f"this call needs {need} bytes of partials, the built-in scratch holds {have}: lower nsplit or pass a workspace to uq_decode_cuda")
+    with torch.cuda.device(q.device):
+        err = L.uqb_decode_launch_static(ctypes.byref(p), 0, 0, _stream(q))
+    _check(err, "uq_decode_launch_static")
+    return out
 
 
 _DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}

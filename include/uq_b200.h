@@ -61,6 +61,26 @@ int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, floa
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16,
                      void* stream);
 
+/* ---- the launch for callers that may not allocate (no counterpart in the reference) ---------- */
+
+/* uqb_decode_launch without caller-owned scratch: p->mo and p->ml are ignored and the split-KV partials go to a
+ * 24 MiB array that is part of the library image (uqb_static_scratch_bytes() bytes; every device that loads the
+ * library carries it until the process ends).  It is meant for hosts where this call cannot be preceded by a
+ * device allocation: an engine that has already handed all device memory to its own pool, a plugin whose host
+ * framework forbids cudaMalloc once inference has begun, a latency-critical thread that cannot take the
+ * device-wide stall cudaMalloc/cudaFree may cause.  Queries, cache, page table, lengths and `out` are still the
+ * caller's.  The function itself never allocates or frees (no cudaMalloc/cudaFree, no library allocator).
+ *   - A call whose partials need more than the array (uqb_workspace_bytes(p) > uqb_static_scratch_bytes(), e.g.
+ *     a very large B*Hkv*nsplit*rows*D) is refused with cudaErrorInvalidValue before anything is enqueued:
+ *     lower p->nsplit or use uqb_decode_launch_ws.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on one device share the array and it keeps the previous call's partials.  Nothing in it has to
+ *     start at zero (each call writes every slot it later reads), but two such calls that overlap on the GPU
+ *     (different streams, no ordering between them) race on it: order them, or give one of them its own workspace. */
+int uqb_decode_launch_static(const UQParams* p, int nwarps, int stages, void* stream);
+size_t uqb_static_scratch_bytes(void);
+
 /* ---- diagnostics (no counterpart in the reference) ------------------------------------------- */
 
 /* Every device-side wait in this library is bounded; a wait that runs out records what it was
