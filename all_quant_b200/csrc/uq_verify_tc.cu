@@ -51,7 +51,8 @@ __device__ unsigned long long g_tc_prof[5][8];
 #endif
 
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
-constexpr int kThreads = 512;      // 16 warps: 128 registers per thread
+constexpr int kThreads = 640;      // 20 warps (5 per SM sub-partition): 96 registers per thread
+constexpr int kWarpSmB = 4, kWarpK = 8, kWarpV = 12, kWarpProd = 16, kWarpMma = 17;   // first warp of each role; softmax A = 0
 constexpr int kRawStages = 4;
 constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
 constexpr float kNegBig = -1.0e30f;
@@ -109,15 +110,18 @@ UQ_DEV void tmem_ld16(uint32_t taddr, uint32_t* r) {
                  "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                : "r"(taddr) : "memory");
 }
+UQ_DEV void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+UQ_DEV void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
 UQ_DEV void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
                  "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-UQ_DEV uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
 }
 UQ_DEV float fast_exp2(float v) {   // 2^v, -inf -> 0
   float d;
@@ -153,34 +157,12 @@ __device__ __noinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // ---------------------------------------------------------------------------------------------- decode
-// 8 packed e2m1 nibbles (channels 8a .. 8a+7) and the group's multiplier (bf16x2, both halves equal)
-// -> 4 bf16x2 words holding channels (0,4), (1,5), (2,6), (3,7) of the octet: pairing nibble i with nibble
-// i+4 lets one shift serve both halves.  (sign | code3 << 6) read as bf16 is value * 2^-126 exactly, zero and
-// the 0.5 subnormal included; the multiplier supplies 2^(s - 1 - 64).
-UQ_DEV void decode8(uint32_t w, uint32_t mult, uint32_t* out) {
-  const uint32_t t0 = (w << 6) & 0x03C003C0u, t1 = (w << 2) & 0x03C003C0u, t2 = (w >> 2) & 0x03C003C0u, t3 = (w >> 6) & 0x03C003C0u;
-  out[0] = mul_bf16x2(t0 + (t0 & 0x02000200u) * 63u, mult);   // bit 9 (sign) moves to bit 15
-  out[1] = mul_bf16x2(t1 + (t1 & 0x02000200u) * 63u, mult);
-  out[2] = mul_bf16x2(t2 + (t2 & 0x02000200u) * 63u, mult);
-  out[3] = mul_bf16x2(t3 + (t3 & 0x02000200u) * 63u, mult);
-}
-// position p (0..7) of a decoded octet holds channel (p >> 1) + 4 * (p & 1); queries are laid out to match
-UQ_DEV int octet_channel(int p) { return (p >> 1) + 4 * (p & 1); }
-
-// ---- second decode path: hardware e2m1 -> fp16 conversion (UQ_TC_BF16_DECODE selects the integer/bf16 path above instead)
-// One cvt per byte gives the two channels of the byte as an exact fp16 pair in natural order (low nibble = even
-// channel), zero and sign included; one fp16 multiply applies the group scale RELATIVE to the key's largest group
-// scale, 2^(s_g - ref) <= 1 (exact down to 2^-24, zero below: such a group is < 2^-24 of the key's largest).  The key's
-// reference 2^(ref - 127) is applied in fp32 by the softmax thread that owns the key: to the score (K) and to the
-// probability (V).  Operands: K and V fp16, Q and P bf16, accumulators fp32.
-// Both operands of one tcgen05.mma kind::f16 must have the same 16-bit format on this hardware (an fp16 A with a bf16 B
-// raised "illegal instruction"), so the switch is per contraction: kF16K = K and Q in fp16, kF16V = V and P in fp16.
-#ifdef UQ_TC_BF16_DECODE
-constexpr bool kF16K = false;
-#else
-constexpr bool kF16K = true;
-#endif
-constexpr bool kF16V = false;
+// One cvt per code byte gives the byte's two channels as an exact fp16 pair in natural order (low nibble = even channel),
+// zero and sign included; one fp16 multiply applies the group scale RELATIVE to the key's largest group scale,
+// 2^(s_g - ref) <= 1 (exact down to 2^-24, zero below: such a group is under 2^-24 of the key's largest).  The key's
+// reference 2^(ref - 127) is applied in fp32 by the softmax threads that own the key: K's to the score, V's to the
+// probability.  Both operands of a tcgen05.mma kind::f16 must have the same 16-bit format on this hardware (an fp16 A
+// with a bf16 B raised "illegal instruction"), so Q and P are fp16 as well; accumulators are fp32.
 UQ_DEV void decode8_f16(uint32_t w, uint32_t mult, uint32_t* out) {
   uint32_t a, b, c, d;
   asm("{\n .reg .b8 t0, t1, t2, t3;\n mov.b32 {t0, t1, t2, t3}, %4;\n cvt.rn.f16x2.e2m1x2 %0, t0;\n cvt.rn.f16x2.e2m1x2 %1, t1;\n"
@@ -196,11 +178,10 @@ UQ_DEV uint32_t pow2_f16x2(int e) {
   return b | (b << 16);
 }
 UQ_DEV uint32_t max_byte(uint32_t v) { return max(max(v & 0xFFu, (v >> 8) & 0xFFu), max((v >> 16) & 0xFFu, v >> 24)); }
-
-// group multiplier 2^(s-65) as bf16x2 for s <= 192; above that the caller multiplies twice
-UQ_DEV uint32_t scale_mult(uint32_t s) {
-  const uint32_t b = (s + 62u) << 7;
-  return b | (b << 16);
+// 2^e as fp32 for any integer e (clamped to the finite range; e <= -127 uses the denormal / zero)
+UQ_DEV float pow2_f32(int e) {
+  e = min(e, 127);
+  return e >= -126 ? __int_as_float((e + 127) << 23) : (e >= -149 ? __int_as_float(1 << (e + 149)) : 0.f);
 }
 
 // ---------------------------------------------------------------------------------------------- layout
@@ -226,7 +207,7 @@ struct Cfg {
   static constexpr int oBar = oRaw + kRawStages * kRawStage;
   static constexpr int kNumBars = 2 * kRawStages + 16;
   static constexpr int oMisc = oBar + kNumBars * 8;
-  // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], fac[NT], prefix[]
+  // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], fac[NT], facO[NT], wr[8], ref side band, prefix[]
   static constexpr int oTmemSlot = oMisc;
   static constexpr int oAbort = oMisc + 4;
   static constexpr int oVote = oMisc + 8;                // 2 ints
@@ -234,7 +215,9 @@ struct Cfg {
   static constexpr int oWmax = oMref + 2 * NT * 4;
   static constexpr int oLsum = oWmax + 4 * NT * 4;
   static constexpr int oFac = oLsum + NT * 4;
-  static constexpr int oRef = oFac + NT * 4;          // [4][128] uint16: K reference byte | V reference byte << 8 of the last four tiles (a slot is rewritten only
+  static constexpr int oFacO = oFac + NT * 4;         // per-row factor for O^T (row factor x V-reference factor)
+  static constexpr int oWr = oFacO + NT * 4;          // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
+  static constexpr int oRef = oWr + 32;          // [4][128] uint16: K reference byte | V reference byte << 8 of the last four tiles (a slot is rewritten only
                                                       // after the S^T buffer two tiles back was released, i.e. after its reader is done)
   static constexpr int oPrefix = oRef + 4 * kKeys * 2;
   static constexpr int kMaxB = 2048;
@@ -357,10 +340,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     for (int i = 0; i < 2; i++) {
       // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
       // barrier serialise in the shared-memory unit and cost more than the work they order
-      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 4);
-      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 4); mbar_init(bar(bPVdone + i), 1);
+      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 8);
+      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 8); mbar_init(bar(bPVdone + i), 1);
     }
-    mbar_init(bar(bQfull), 4); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4); mbar_init(bar(bVote), 4);
+    mbar_init(bar(bQfull), 8); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 8); mbar_init(bar(bVote), 8);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
     reinterpret_cast<int*>(sm + C::oVote)[1] = 0;
@@ -376,7 +359,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     prefix[0] = 0;
     for (int b = 0; b < p.B; b++) prefix[b + 1] += prefix[b];
   }
-  if (warp == 13) {
+  if (warp == kWarpMma) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sm_a + C::oTmemSlot) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -390,7 +373,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   const int G = x.G, rows = x.rows;
   Seg sg;
 
-  if (warp == 12) {
+  if (warp == kWarpProd) {
     // ================================================================= producer
     const int ppt = kKeys / p.PAGE;   // pages per tile
     UQ_PROF_DECL
@@ -424,15 +407,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
     }
     UQ_PROF_FLUSH(0, lane == 0)
-  } else if (warp == 13) {
+  } else if (warp == kWarpMma) {
     // ================================================================= MMA issue
-    constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, kF16K ? 0 : 1, kF16K ? 0 : 1);   // A = K, B = Q: both fp16 or both bf16
-    #ifdef UQ_TC_EXP_KMAJOR_PV   // timing experiment only (wrong results): declare the P.V operands K-major
-    constexpr uint32_t idesc_pv = instr_desc(128, NT, 0, 0, kF16V ? 0 : 1, kF16V ? 0 : 1);
-#else
-    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, kF16V ? 0 : 1, kF16V ? 0 : 1);
-#endif
-      // A = V, B = P: both fp16 or both bf16
+    constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, 0, 0);   // A = K, B = Q, both fp16 (mixed 16-bit formats are not legal)
+        constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
     int cnt = 0, seg_i = 0;
     bool ok = true;
     UQ_PROF_DECL
@@ -479,7 +457,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       seg_i++;
     }
     UQ_PROF_FLUSH(1, lane == 0)
-  } else if (warp >= 4 && warp < 8) {
+  } else if (warp >= kWarpK && warp < kWarpK + 4) {
     // ================================================================= K decode -> TMEM
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
@@ -497,13 +475,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
-        if (kF16K) {
+        {
           const uint32_t kref = max_byte(sc4);
           const uint32_t vref = max_byte(*reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + C::kRawScales + kk * 4));
-          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax thread of this key
+          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
           uint4 c4[C::kGroups];
 #pragma unroll
-          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));   // 64-byte swizzle
 #pragma unroll
           for (int g = 0; g < C::kGroups; g++) {
             const uint32_t m = pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - (int)kref);
@@ -511,23 +489,6 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
             tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
           }
-        } else {
-        const bool big = __any_sync(0xffffffffu, (sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u);
-#pragma unroll 1
-        for (int g = 0; g < C::kGroups; g++) {
-          // 64-byte-swizzled row: logical 16-byte chunk g sits at chunk g ^ ((key >> 1) & 3)
-          const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
-          const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
-          uint32_t o[16];
-          const uint32_t m = scale_mult(s > 192u ? s - 96u : s);
-          decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
-          if (big) {   // some scale byte of this warp's keys is above 192: second multiply by 2^96 (or 1)
-            const uint32_t m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
-#pragma unroll
-            for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
-          }
-          tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
-        }
         }
         UQ_PROF_T1(2)
         tc_wait_st();
@@ -538,9 +499,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
     }
     UQ_PROF_FLUSH(2, kk == 0)
-  } else if (warp >= 8 && warp < 12) {
+  } else if (warp >= kWarpV && warp < kWarpV + 4) {
     // ================================================================= V decode -> shared memory
-    const int kk = (warp - 8) * 32 + lane;
+    const int kk = (warp - kWarpV) * 32 + lane;
     int cnt = 0;
     bool ok = true;
     UQ_PROF_DECL
@@ -558,7 +519,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * 4);
-        if (kF16V) {
+        {
           const int vref = (int)max_byte(sc4);
           uint4 c4[C::kGroups];
 #pragma unroll
@@ -568,31 +529,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             const uint32_t m = live ? pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - vref) : 0u;   // multiplier 0: keys past the end decode to zeros
             uint32_t o[16];
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
+            // output chunk 4g + w (8 channels) of the key's 256-byte row: half (4g + w) >> 3, slot ((4g + w) & 7) ^ (key & 7)
             uint8_t* vrow = vt + (g >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
             for (int w = 0; w < 4; w++)
               *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
           }
-        } else {
-        const bool big = __any_sync(0xffffffffu, live && ((sc4 & 0xFFu) > 192u || ((sc4 >> 8) & 0xFFu) > 192u || ((sc4 >> 16) & 0xFFu) > 192u || (sc4 >> 24) > 192u));
-#pragma unroll 1
-        for (int g = 0; g < C::kGroups; g++) {
-          const uint4 c4 = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
-          const uint32_t s = (sc4 >> (8 * g)) & 0xFFu;
-          uint32_t o[16];
-          const uint32_t m = live ? scale_mult(s > 192u ? s - 96u : s) : 0u;   // multiplier 0: keys past the end decode to zeros
-          decode8(c4.x, m, o); decode8(c4.y, m, o + 4); decode8(c4.z, m, o + 8); decode8(c4.w, m, o + 12);
-          if (big) {
-            const uint32_t m2 = s > 192u ? 0x6F806F80u : 0x3F803F80u;
-#pragma unroll
-            for (int i = 0; i < 16; i++) o[i] = mul_bf16x2(o[i], m2);
-          }
-          // output chunk oc = 4g + w (8 channels) of the key's 256-byte row: half oc >> 3, slot (oc & 7) ^ (key & 7)
-          uint8_t* vrow = vt + (g >> 1) * C::kVHalf + kk * 128;
-#pragma unroll
-          for (int w = 0; w < 4; w++)
-            *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
-        }
         }
         UQ_PROF_T1(2)
         fence_async_smem();
@@ -602,36 +544,54 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
     }
     UQ_PROF_FLUSH(3, kk == 0)
-  } else if (warp < 4) {
-    // ================================================================= softmax + epilogue
-    const int quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = 0..127 index within the role
+  } else if (warp < 8) {
+    // ================================================================= softmax + epilogue: two warpgroups, half the rows each
+    constexpr int HW = NT / 2;                          // rows (columns of S^T) per thread
+    const int grp = warp >> 2, quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = 0..255 within the role
+    const int r0 = grp * HW;                            // first row of this thread
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    float* mref = reinterpret_cast<float*>(sm + C::oMref);     // [2][NT], the live copy is mref + mcur * NT
-    float* wmax = reinterpret_cast<float*>(sm + C::oWmax);     // [4][NT]
+    float* mref = reinterpret_cast<float*>(sm + C::oMref);     // [2][NT] per-row reference maxima, live copy = mref + mcur * NT
+    float* wmax = reinterpret_cast<float*>(sm + C::oWmax);     // [4][NT] per-warp row maxima of a tile (reference move only)
     float* lsum = reinterpret_cast<float*>(sm + C::oLsum);
-    float* fac_s = reinterpret_cast<float*>(sm + C::oFac);      // per-row rescale factors of a reference move
+    float* fac_s = reinterpret_cast<float*>(sm + C::oFac);     // per-row factor of a reference move, for the row sums
+    float* facO_s = reinterpret_cast<float*>(sm + C::oFacO);   // the same times the V-reference factor, for O^T
+    uint32_t* wr = reinterpret_cast<uint32_t*>(sm + C::oWr);   // [0..3] per-warp maxima of V reference bytes, [4 + mcur] the segment's V reference byte
     int* vote = reinterpret_cast<int*>(sm + C::oVote);
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
-    float csc0 = x.sc2 * 18446744073709551616.0f;   // bf16 K path: scores carry the 2^-64 of the decoded K
+    float csc0 = x.sc2;
     int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
     bool ok = true;
     UQ_PROF_DECL
+    auto rendezvous = [&](int id, int tile) -> bool {   // all 256 threads of the role; orders their shared-memory traffic
+      warp_arrive(bar(bVote));
+      const bool r = wait(bar(bVote), nvote & 1, id, tile UQ_PROF_SITE(1));
+      nvote++;
+      return __all_sync(0xffffffffu, r);
+    };
+    auto load_scores = [&](uint32_t addr, float* dst) {
+      if constexpr (HW == 8) tmem_ld8(addr, reinterpret_cast<uint32_t*>(dst));
+      else {
+#pragma unroll
+        for (int c = 0; c < HW / 16; c++) tmem_ld16(addr + c * 16, reinterpret_cast<uint32_t*>(dst) + c * 16);
+      }
+      tc_wait_ld();
+    };
     // items without a single key: nobody computes them, their slots must read as empty
     for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
-      for (int i = st; i < x.ns_eff * rows; i += 128)
+      for (int i = st; i < x.ns_eff * rows; i += 256)
         p.ml[uq_slot(p, it / p.HKV, it % p.HKV, i / rows) * x.BM + i % rows] = -INFINITY;
     }
     while (ok && wk.next(sg)) {
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int n_glob = p.seq_lens[sg.b];
-      if (kF16K) {
-        // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
-        // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
-        // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
+      // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
+      // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
+      // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
+      {
         uint32_t amax = 0;   // bf16 magnitudes compare as integers
-        for (int i = st; i < rows * (D / 8); i += 128) {
+        for (int i = st; i < rows * (D / 8); i += 256) {
           const int n = i / (D / 8), a = i % (D / 8);
           const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
           const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
@@ -639,19 +599,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           for (int j = 0; j < 4; j++) amax = max(amax, max(w4[j] & 0x7FFFu, (w4[j] >> 16) & 0x7FFFu));
         }
         amax = __reduce_max_sync(0xffffffffu, amax);
-        if (lane == 0) reinterpret_cast<uint32_t*>(wmax)[quad] = amax;
-        warp_arrive(bar(bVote));
-        ok = wait(bar(bVote), nvote & 1, 59, seg_i UQ_PROF_SITE(5));
-        nvote++;
-        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) reinterpret_cast<uint32_t*>(wmax)[warp] = amax;
+        ok = rendezvous(59, seg_i);
         if (!ok) break;
         const uint32_t* wq = reinterpret_cast<const uint32_t*>(wmax);
-        amax = max(max(wq[0], wq[1]), max(wq[2], wq[3]));
+        amax = max(max(max(wq[0], wq[1]), max(wq[2], wq[3])), max(max(wq[4], wq[5]), max(wq[6], wq[7])));
         int eq = amax ? (int)(amax >> 7) - 127 : 0;
         eq = min(max(eq, -126), 126);
         const float qf = __int_as_float((127 - eq) << 23);
         csc0 = x.sc2 * __int_as_float((127 + eq) << 23);
-        for (int i = st; i < NT * (D / 8); i += 128) {
+        for (int i = st; i < NT * (D / 8); i += 256) {
           const int n = i / (D / 8), a = i % (D / 8);
           uint4 w = make_uint4(0, 0, 0, 0);
           if (n < rows) {
@@ -663,209 +620,170 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           *reinterpret_cast<uint4*>(sm + C::oQ + (a >> 3) * C::kQHalf + n * 128 + (((a & 7) ^ (n & 7)) << 4)) = w;
         }
-      } else {
-      // ---- query tile: [row][position], octets permuted like the decoded K, 128-byte swizzle, two 64-position halves
-      for (int i = st; i < NT * (D / 8); i += 128) {
-        const int n = i / (D / 8), a = i % (D / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (n < rows) v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
-        const uint4 w = make_uint4(__byte_perm(v.x, v.z, 0x5410), __byte_perm(v.x, v.z, 0x7632), __byte_perm(v.y, v.w, 0x5410), __byte_perm(v.y, v.w, 0x7632));
-        *reinterpret_cast<uint4*>(sm + C::oQ + (a >> 3) * C::kQHalf + n * 128 + (((a & 7) ^ (n & 7)) << 4)) = w;
       }
-      }
-      if (st < NT) { mref[mcur * NT + st] = kNegBig; lsum[st] = 0.f; }
+      // padding rows (no query behind them) get a reference of +1e30: their probabilities are 2^-inf = 0 without a select
+      if (st < NT) { mref[mcur * NT + st] = st < rows ? kNegBig : 1.0e30f; lsum[st] = 0.f; }
+      if (st == 0) wr[4 + mcur] = 0u;
       fence_async_smem();
       warp_arrive(bar(bQfull));
       // the first segment of an item marks the slots the item does not use as empty
       if (sg.t0 == 0)
-        for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 128)
+        for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 256)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
-      // the reference row maxima written above must be visible to all 128 threads before the first tile
-      warp_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 60, seg_i UQ_PROF_SITE(5));
-      nvote++;
-      ok = __all_sync(0xffffffffu, ok);
-      float l[NT];
+      ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
+      float l[HW];
 #pragma unroll
-      for (int r = 0; r < NT; r++) l[r] = 0.f;
+      for (int i = 0; i < HW; i++) l[i] = 0.f;
       const int c0 = cnt;
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
         const int buf = cnt & 1;
         ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(3));   // P buffer free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t s_addr = lane_addr + C::cS + buf * NT;
-        // this key's reference scales (fp16 path): K's multiplies the score, V's multiplies the probability
-        float csc = csc0, vfac = 1.f;
-        if (kF16K || kF16V) {
-          const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk];
-          if (kF16K) csc = csc0 * uq_scale_f32(rf & 0xFFu);
-          if (kF16V) vfac = t * kKeys + kk < n_loc ? uq_scale_f32(rf >> 8) : 0.f;   // past the end the bytes are arbitrary: keep 0 * vfac finite
-        }
-        // rows this key is visible to: r >= rmin (causal limit among the drafts); none if past the end
+        const uint32_t s_addr = lane_addr + C::cS + buf * NT + r0;
+        // this key: reference scale bytes, position, visibility
+        const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk];
+        const int vref = (int)(rf >> 8);
+        const float ck = csc0 * uq_scale_f32(rf & 0xFFu);
         const int key = t * kKeys + kk;
-        int rmin = 0;
-        if (key >= n_loc) rmin = NT;
+        const bool live = key < n_loc;
+        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 > n_glob - p.K;   // same for every thread
+        int rmin = 0;   // rows r >= rmin see this key (causal limit among the drafts); none if past the end
+        if (!live) rmin = NT;
         else { const int jmin = off + key - (n_glob - p.K); if (jmin > 0) rmin = jmin * G; }
-        const float* mr = mref + mcur * NT;
-        // ---- pass 1: does any visible score leave the window of its row's reference maximum?
-        float xm = kNegBig;
-#pragma unroll 1
-        for (int c = 0; c < NT / 16; c++) {
-          uint32_t sv[16];
-          tmem_ld16(s_addr + c * 16, sv);
-          tc_wait_ld();
+        uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
+        float pv[HW];
+        // scores -> probabilities against the references `mrow`, in place; returns the largest exponent seen
+        auto probabilities = [&](const float* mrow) -> float {
+          float xm = kNegBig;
 #pragma unroll
-          for (int i = 0; i < 16; i++) {
-            const int r = c * 16 + i;
-            const float v = fmaf(__uint_as_float(sv[i]), csc, -mr[r]);
-            xm = fmaxf(xm, (r >= rmin && r < rows) ? v : kNegBig);
+          for (int i = 0; i < HW; i++) {
+            float xv = fmaf(pv[i], ck, -mrow[r0 + i]);
+            if (need_mask) xv = (r0 + i >= rmin) ? xv : -INFINITY;
+            xm = fmaxf(xm, xv);
+            pv[i] = fast_exp2(xv);
           }
-        }
-        const bool mine = xm > kRescaleAt;
-        if (__any_sync(0xffffffffu, mine) && lane == 0) atomicOr(&vote[nvote & 1], 1);
-        warp_arrive(bar(bVote));
-        ok = wait(bar(bVote), nvote & 1, 64, cnt UQ_PROF_SITE(1));
-        ok = __all_sync(0xffffffffu, ok);
+          return xm;
+        };
+        // P^T row of this key: probabilities times the key's V reference relative to the segment's, fp16
+        auto write_p = [&](int rbyte) {
+          const float vf = live ? pow2_f32(vref - rbyte) : 0.f;   // past the end the bytes are arbitrary: keep 0 * vf finite
+#pragma unroll
+          for (int c = 0; c < HW / 8; c++)
+            *reinterpret_cast<uint4*>(pt + (((r0 / 8 + c) ^ (kk & 7)) << 4)) =
+                make_uint4(pack_f16x2(pv[8 * c] * vf, pv[8 * c + 1] * vf), pack_f16x2(pv[8 * c + 2] * vf, pv[8 * c + 3] * vf),
+                           pack_f16x2(pv[8 * c + 4] * vf, pv[8 * c + 5] * vf), pack_f16x2(pv[8 * c + 6] * vf, pv[8 * c + 7] * vf));
+        };
+        load_scores(s_addr, pv);
+        const int rbyte = (int)wr[4 + mcur];
+        const float xm = probabilities(mref + mcur * NT);
+        write_p(rbyte);
+        // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
+        const int vslot = nvote & 1;
+        if (__any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte)) && lane == 0) atomicOr(&vote[vslot], 1);
+        ok = rendezvous(64, cnt);
         if (!ok) break;
-        const int moved = *reinterpret_cast<volatile int*>(&vote[nvote & 1]);
-        nvote++;
-        if (moved) {
+        if (*reinterpret_cast<volatile int*>(&vote[vslot])) {
           UQ_PROF_COUNT(6)
-          // ---- move the reference maxima of this segment's rows (the first tile, then only on growth)
-#pragma unroll 1
-          for (int c = 0; c < NT / 16; c++) {
-            uint32_t sv[16];
-            tmem_ld16(s_addr + c * 16, sv);
-            tc_wait_ld();
+          // ---- move the references (the first tile of a segment, then only on growth), rescale what was accumulated,
+          // and redo this tile against the new references
+          const float* mr = mref + mcur * NT;
+          load_scores(s_addr, pv);
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-              const int r = c * 16 + i;
-              float v = (r >= rmin && r < rows) ? __uint_as_float(sv[i]) * csc : -INFINITY;
+          for (int i = 0; i < HW; i++) {
+            float v = (!need_mask || r0 + i >= rmin) ? pv[i] * ck : -INFINITY;
 #pragma unroll
-              for (int m = 16; m; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
-              if (lane == 0) wmax[quad * NT + r] = v;
-            }
+            for (int m = 16; m; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+            if (lane == 0) wmax[quad * NT + r0 + i] = v;
           }
-          warp_arrive(bar(bVote));
-          ok = wait(bar(bVote), nvote & 1, 65, cnt UQ_PROF_SITE(2));
-          nvote++;
-          ok = __all_sync(0xffffffffu, ok);
+          if (grp == 0) {
+            const uint32_t vr = __reduce_max_sync(0xffffffffu, live ? (uint32_t)vref : 0u);
+            if (lane == 0) wr[quad] = vr;
+          }
+          ok = rendezvous(65, cnt);
           if (!ok) break;
           if (st == 0) vote[0] = vote[1] = 0;
-          if (st < NT) {   // thread r owns row r: new reference, and the factor everything accumulated so far shrinks by
+          if (st < NT) {   // thread r owns row r
             const float m_old = mr[st];
             const float m_new = fmaxf(fmaxf(m_old, fmaxf(wmax[st], wmax[NT + st])), fmaxf(wmax[2 * NT + st], wmax[3 * NT + st]));
+            const int r_old = (int)wr[4 + mcur];
+            const int r_new = max(max(r_old, (int)max(wr[0], wr[1])), (int)max(wr[2], wr[3]));
+            const float f = fast_exp2(m_old - m_new);   // first tile: 2^(-1e30 - m) = 0
             mref[(mcur ^ 1) * NT + st] = m_new;
-            fac_s[st] = fast_exp2(m_old - m_new);   // first tile: 2^(-1e30 - m) = 0
+            fac_s[st] = f;
+            facO_s[st] = f * pow2_f32(r_old - r_new);
+            if (st == 0) wr[4 + (mcur ^ 1)] = (uint32_t)r_new;
           }
-          warp_arrive(bar(bVote));
-          ok = wait(bar(bVote), nvote & 1, 67, cnt UQ_PROF_SITE(2));
-          nvote++;
-          ok = __all_sync(0xffffffffu, ok);
+          ok = rendezvous(67, cnt);
           if (!ok) break;
 #pragma unroll
-          for (int r = 0; r < NT; r++) l[r] *= fac_s[r];
+          for (int i = 0; i < HW; i++) l[i] *= fac_s[r0 + i];
           if (cnt > c0) {
-            // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's lane
+            // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's part
             ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt UQ_PROF_SITE(2));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < NT / 16; c++) {
-              uint32_t ov[16];
-              tmem_ld16(lane_addr + C::cO + c * 16, ov);
-              tc_wait_ld();
+            float ov[HW];
+            load_scores(lane_addr + C::cO + r0, ov);
 #pragma unroll
-              for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * fac_s[c * 16 + i]);
-              tmem_st16(lane_addr + C::cO + c * 16, ov);
+            for (int i = 0; i < HW; i++) ov[i] *= facO_s[r0 + i];
+            if constexpr (HW == 8) tmem_st8(lane_addr + C::cO + r0, reinterpret_cast<uint32_t*>(ov));
+            else {
+#pragma unroll
+              for (int c = 0; c < HW / 16; c++) tmem_st16(lane_addr + C::cO + r0 + c * 16, reinterpret_cast<uint32_t*>(ov) + c * 16);
             }
             tc_wait_st();
           }
-          mcur ^= 1;   // the next tile's vote rendezvous keeps fac_s / wmax from being overwritten while still read
+          mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
+          load_scores(s_addr, pv);
+          probabilities(mref + mcur * NT);
+          write_p((int)wr[4 + mcur]);
         }
-        if (cnt >= 2) {
-          ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(3));   // P buffer free
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
-        // ---- pass 2: probabilities against the (possibly moved) references -> P^T, row sums
-        const float* mc = mref + mcur * NT;
-        uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
 #pragma unroll
-        for (int c = 0; c < NT / 16; c++) {
-          uint32_t sv[16];
-          tmem_ld16(s_addr + c * 16, sv);
-          tc_wait_ld();
-          if (c == NT / 16 - 1) {   // the S^T buffer is in registers now
-            tc_fence_before();
-            warp_arrive(bar(bSfree + buf));
-          }
-          float pv[16];
-#pragma unroll
-          for (int i = 0; i < 16; i++) {
-            const int r = c * 16 + i;
-            const float v = fast_exp2(fmaf(__uint_as_float(sv[i]), csc, -mc[r]));
-            pv[i] = (r >= rmin && r < rows) ? v : 0.f;
-            l[r] += pv[i];
-          }
-          if (kF16V) {
-#pragma unroll
-            for (int i = 0; i < 16; i++) pv[i] *= vfac;
-          }
-          *reinterpret_cast<uint4*>(pt + (((2 * c) ^ (kk & 7)) << 4)) =
-              make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
-          *reinterpret_cast<uint4*>(pt + (((2 * c + 1) ^ (kk & 7)) << 4)) =
-              make_uint4(pack_bf16x2(pv[8], pv[9]), pack_bf16x2(pv[10], pv[11]), pack_bf16x2(pv[12], pv[13]), pack_bf16x2(pv[14], pv[15]));
-        }
+        for (int i = 0; i < HW; i++) l[i] += pv[i];
+        tc_fence_before();
+        warp_arrive(bar(bSfree + buf));   // the scores are consumed
         fence_async_smem();
         warp_arrive(bar(bPfull + buf));
       }
       if (!ok) break;
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
 #pragma unroll
-      for (int r = 0; r < NT; r++) {
-        float v = l[r];
+      for (int i = 0; i < HW; i++) {
+        float v = l[i];
 #pragma unroll
         for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-        if (lane == 0) atomicAdd(&lsum[r], v);
+        if (lane == 0) atomicAdd(&lsum[r0 + i], v);
       }
-      warp_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 70, seg_i UQ_PROF_SITE(5));
-      nvote++;
+      ok = rendezvous(70, seg_i);
       if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(4));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const size_t slot = uq_slot(p, sg.b, sg.hk, sg.slot);
-      float* mo = p.mo + slot * x.BM * D;
-      float* ml = p.ml + slot * x.BM;
-      const int dch = kF16V ? kk : (kk & ~7) + octet_channel(kk & 7);   // channel held by accumulator lane kk
-      const float* mr = mref + mcur * NT;
+      {
+        const size_t slot = uq_slot(p, sg.b, sg.hk, sg.slot);
+        float* mo = p.mo + slot * x.BM * D;
+        float* ml = p.ml + slot * x.BM;
+        const float* mr = mref + mcur * NT;
+        const float osc = pow2_f32((int)wr[4 + mcur] - 127);   // O^T was accumulated relative to the segment's V reference
+        float ov[HW];
+        load_scores(lane_addr + C::cO + r0, ov);   // accumulator lane kk = channel kk
 #pragma unroll
-      for (int c = 0; c < NT / 16; c++) {
-        uint32_t ov[16];
-        tmem_ld16(lane_addr + C::cO + c * 16, ov);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-          const int r = c * 16 + i;
+        for (int i = 0; i < HW; i++) {
+          const int r = r0 + i;
           if (r < rows) {
             const float lr = lsum[r];
-            mo[(size_t)r * D + dch] = lr > 0.f ? __uint_as_float(ov[i]) * ((kF16V ? 1.0f : 18446744073709551616.0f) / lr) : 0.f;
+            mo[(size_t)r * D + kk] = lr > 0.f ? ov[i] * (osc / lr) : 0.f;
           }
         }
+        if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       }
-      if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       tc_fence_before();
       warp_arrive(bar(bEpi));
-      // everyone has read lsum / mref before the next segment overwrites them
-      warp_arrive(bar(bVote));
-      ok = wait(bar(bVote), nvote & 1, 72, seg_i UQ_PROF_SITE(5));
-      nvote++;
-      ok = __all_sync(0xffffffffu, ok);
+      ok = rendezvous(72, seg_i);   // everyone has read the sums and references before the next segment overwrites them
       seg_i++;
     }
     UQ_PROF_FLUSH(4, st == 0)
@@ -874,7 +792,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // ---- common exit: every role gets here (all waits are bounded); TMEM goes back before the CTA ends
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == kWarpMma) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
   }
