@@ -50,6 +50,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_T1(n)
 #endif
 
+#ifndef UQ_ABL
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no per-tile rendezvous
+#endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 constexpr int kThreads = 640;      // 20 warps (5 per SM sub-partition): 96 registers per thread
 constexpr int kWarpSmB = 4, kWarpK = 8, kWarpV = 12, kWarpProd = 16, kWarpMma = 17;   // first warp of each role; softmax A = 0
@@ -408,32 +411,18 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     }
     UQ_PROF_FLUSH(0, lane == 0)
   } else if (warp == kWarpMma) {
-    // ================================================================= MMA issue
+    // ================================================================= MMA issue, S^T = K.Q^T (one thread).  The two contractions are
+    // issued by two warps: an instruction occupies its issuing thread for as long as the tensor pipe takes to accept it
+    // (about 70 cycles), so one thread doing both spends its waits and commits on the pipe's critical path.
     constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, 0, 0);   // A = K, B = Q, both fp16 (mixed 16-bit formats are not legal)
-        constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
     int cnt = 0, seg_i = 0;
     bool ok = true;
     UQ_PROF_DECL
     // descriptors differ between instructions only in the start-address field (bits 0-13, units of 16 bytes)
     const uint64_t q_desc = smem_desc(sm_a + C::oQ, 16, 1024);
-    const uint64_t v_desc = smem_desc(sm_a + C::oV, C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
-    auto issue_pv = [&](int c, int first) {   // c = global tile counter of the tile whose P/V are consumed
-      const int buf = c & 1;
-      if (!wait(bar(bPfull + buf), (c >> 1) & 1, 20 + buf, c UQ_PROF_SITE(4))) return false;
-      if (!wait(bar(bVfull + buf), (c >> 1) & 1, 22 + buf, c UQ_PROF_SITE(5))) return false;
-      tc_fence_after();
-      const uint64_t va = v_desc + (uint64_t)(buf * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
-#pragma unroll
-      for (int kk = 0; kk < kKeys / 16; kk++)
-        mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (first && kk == 0) ? 0u : 1u);
-      tc_commit(bar(bPVdone + buf));
-      return true;
-    };
     while (ok && wk.next(sg)) {
       if (lane == 0) {
         ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
-        if (ok && seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i UQ_PROF_SITE(1));   // previous segment's O has been read
-        const int c0 = cnt;
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
           const int buf = cnt & 1;
           ok = wait(bar(bKfull + buf), (cnt >> 1) & 1, 24 + buf, cnt UQ_PROF_SITE(2));
@@ -446,10 +435,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
           tc_commit(bar(bSfull + buf));
           UQ_PROF_T1(6)
-          if (cnt > c0) ok = issue_pv(cnt - 1, cnt - 1 == c0);
         }
-        if (ok) ok = issue_pv(cnt - 1, cnt - 1 == c0);
-        if (ok) tc_commit(bar(bOdone));
       } else {
         cnt += sg.t1 - sg.t0;
       }
@@ -457,6 +443,35 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       seg_i++;
     }
     UQ_PROF_FLUSH(1, lane == 0)
+  } else if (warp == kWarpMma + 1) {
+    // ================================================================= MMA issue, O^T += V^T.P^T (one thread)
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
+    int cnt = 0, seg_i = 0;
+    bool ok = true;
+    const uint64_t v_desc = smem_desc(sm_a + C::oV, C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
+    while (ok && wk.next(sg)) {
+      if (lane == 0) {
+        if (seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
+        const int c0 = cnt;
+        for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
+          const int buf = cnt & 1;
+          ok = wait(bar(bPfull + buf), (cnt >> 1) & 1, 20 + buf, cnt, nullptr);
+          if (ok) ok = wait(bar(bVfull + buf), (cnt >> 1) & 1, 22 + buf, cnt, nullptr);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t va = v_desc + (uint64_t)(buf * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
+#pragma unroll
+          for (int kk = 0; kk < kKeys / 16; kk++)
+            mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
+          tc_commit(bar(bPVdone + buf));
+        }
+        if (ok) tc_commit(bar(bOdone));
+      } else {
+        cnt += sg.t1 - sg.t0;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      seg_i++;
+    }
   } else if (warp >= kWarpK && warp < kWarpK + 4) {
     // ================================================================= K decode -> TMEM
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
@@ -660,10 +675,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           float xm = kNegBig;
 #pragma unroll
           for (int i = 0; i < HW; i++) {
-            float xv = fmaf(pv[i], ck, -mrow[r0 + i]);
+            float xv = fmaf(pv[i], ck, (UQ_ABL & 4) ? -1.0f : -mrow[r0 + i]);
             if (need_mask) xv = (r0 + i >= rmin) ? xv : -INFINITY;
             xm = fmaxf(xm, xv);
-            pv[i] = fast_exp2(xv);
+            pv[i] = (UQ_ABL & 1) ? xv * 0.001f : fast_exp2(xv);
           }
           return xm;
         };
@@ -676,16 +691,20 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
                 make_uint4(pack_f16x2(pv[8 * c] * vf, pv[8 * c + 1] * vf), pack_f16x2(pv[8 * c + 2] * vf, pv[8 * c + 3] * vf),
                            pack_f16x2(pv[8 * c + 4] * vf, pv[8 * c + 5] * vf), pack_f16x2(pv[8 * c + 6] * vf, pv[8 * c + 7] * vf));
         };
-        load_scores(s_addr, pv);
+        if (!(UQ_ABL & 8) || cnt == c0) load_scores(s_addr, pv);
+        else {
+#pragma unroll
+          for (int i = 0; i < HW; i++) pv[i] = 0.5f;
+        }
         const int rbyte = (int)wr[4 + mcur];
         const float xm = probabilities(mref + mcur * NT);
-        write_p(rbyte);
+        if (!(UQ_ABL & 2) || cnt == c0) write_p(rbyte);
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
         const int vslot = nvote & 1;
         if (__any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte)) && lane == 0) atomicOr(&vote[vslot], 1);
-        ok = rendezvous(64, cnt);
+        if (!(UQ_ABL & 16) || cnt == c0) ok = rendezvous(64, cnt);
         if (!ok) break;
-        if (*reinterpret_cast<volatile int*>(&vote[vslot])) {
+        if ((!(UQ_ABL & 16) || cnt == c0) && *reinterpret_cast<volatile int*>(&vote[vslot])) {
           UQ_PROF_COUNT(6)
           // ---- move the references (the first tile of a segment, then only on growth), rescale what was accumulated,
           // and redo this tile against the new references

@@ -14,7 +14,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libuq_b200.so")
+_LIB_PATH = os.environ.get("UQ_B200_LIB") or os.path.join(_HERE, "libuq_b200.so")   # the override is for developers comparing builds
 _lib = None
 _ext = None
 
