@@ -41,6 +41,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_COUNT(n) pw[n]++;
 #define UQ_PROF_T0 const long long ps0 = clock64();
 #define UQ_PROF_T1(n) pw[n] += clock64() - ps0;
+#define UQ_PROF_TA long long psa = clock64();
+#define UQ_PROF_TA2 psa = clock64();
+#define UQ_PROF_TB(n) { const long long psb = clock64(); pw[n] += psb - psa; psa = psb; }
 #else
 #define UQ_PROF_DECL
 #define UQ_PROF_FLUSH(role, leader)
@@ -48,6 +51,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_COUNT(n)
 #define UQ_PROF_T0
 #define UQ_PROF_T1(n)
+#define UQ_PROF_TA
+#define UQ_PROF_TA2
+#define UQ_PROF_TB(n)
 #endif
 
 #ifndef UQ_ABL
@@ -229,6 +235,7 @@ struct Cfg {
   static constexpr int cK = 0;                 // 2 x 64: bf16 A operand of S^T
   static constexpr int cS = 128;               // 2 x NT: fp32 S^T
   static constexpr int cO = cS + 2 * NT;       // NT:     fp32 O^T
+  static constexpr int cL = cO + NT;           // NT:     fp32 per-key partial row sums (lane = key): the softmax threads' accumulators, kept out of their registers
 };
 
 // barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
@@ -591,6 +598,15 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       tc_wait_ld();
     };
+    auto store_cols = [&](uint32_t addr, const float* src) {
+      if constexpr (HW == 8) tmem_st8(addr, reinterpret_cast<const uint32_t*>(src));
+      else {
+#pragma unroll
+        for (int c = 0; c < HW / 16; c++) tmem_st16(addr + c * 16, reinterpret_cast<const uint32_t*>(src) + c * 16);
+      }
+      tc_wait_st();
+    };
+    const uint32_t l_addr = lane_addr + C::cL + r0;   // this thread's row sums over the keys it has seen (one TMEM lane per key slot)
     // items without a single key: nobody computes them, their slots must read as empty
     for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
@@ -646,17 +662,21 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 256)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
       ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
-      float l[HW];
+      {
+        float z[HW];
 #pragma unroll
-      for (int i = 0; i < HW; i++) l[i] = 0.f;
+        for (int i = 0; i < HW; i++) z[i] = 0.f;
+        store_cols(l_addr, z);
+      }
       const int c0 = cnt;
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
         const int buf = cnt & 1;
         ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(3));   // P buffer free
+        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(0));   // P buffer free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        UQ_PROF_TA
         const uint32_t s_addr = lane_addr + C::cS + buf * NT + r0;
         // this key: reference scale bytes, position, visibility
         const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk];
@@ -696,9 +716,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < HW; i++) pv[i] = 0.5f;
         }
+        UQ_PROF_TB(2)
         const int rbyte = (int)wr[4 + mcur];
         const float xm = probabilities(mref + mcur * NT);
+        UQ_PROF_TB(3)
         if (!(UQ_ABL & 2) || cnt == c0) write_p(rbyte);
+        UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
         const int vslot = nvote & 1;
         if (__any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte)) && lane == 0) atomicOr(&vote[vslot], 1);
@@ -737,11 +760,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           ok = rendezvous(67, cnt);
           if (!ok) break;
+          {
+            float lv[HW];
+            load_scores(l_addr, lv);
 #pragma unroll
-          for (int i = 0; i < HW; i++) l[i] *= fac_s[r0 + i];
+            for (int i = 0; i < HW; i++) lv[i] *= fac_s[r0 + i];
+            store_cols(l_addr, lv);
+          }
           if (cnt > c0) {
             // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's part
-            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt UQ_PROF_SITE(2));
+            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt UQ_PROF_SITE(0));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -749,36 +777,42 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             load_scores(lane_addr + C::cO + r0, ov);
 #pragma unroll
             for (int i = 0; i < HW; i++) ov[i] *= facO_s[r0 + i];
-            if constexpr (HW == 8) tmem_st8(lane_addr + C::cO + r0, reinterpret_cast<uint32_t*>(ov));
-            else {
-#pragma unroll
-              for (int c = 0; c < HW / 16; c++) tmem_st16(lane_addr + C::cO + r0 + c * 16, reinterpret_cast<uint32_t*>(ov) + c * 16);
-            }
-            tc_wait_st();
+            store_cols(lane_addr + C::cO + r0, ov);
           }
           mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
           load_scores(s_addr, pv);
           probabilities(mref + mcur * NT);
           write_p((int)wr[4 + mcur]);
         }
+        UQ_PROF_TA2
+        {
+          float lv[HW];
+          load_scores(l_addr, lv);
 #pragma unroll
-        for (int i = 0; i < HW; i++) l[i] += pv[i];
+          for (int i = 0; i < HW; i++) lv[i] += pv[i];
+          store_cols(l_addr, lv);
+        }
         tc_fence_before();
         warp_arrive(bar(bSfree + buf));   // the scores are consumed
         fence_async_smem();
         warp_arrive(bar(bPfull + buf));
+        UQ_PROF_TB(5)
       }
       if (!ok) break;
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
+      {
+        float lv[HW];
+        load_scores(l_addr, lv);
 #pragma unroll
-      for (int i = 0; i < HW; i++) {
-        float v = l[i];
+        for (int i = 0; i < HW; i++) {
+          float v = lv[i];
 #pragma unroll
-        for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-        if (lane == 0) atomicAdd(&lsum[r0 + i], v);
+          for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+          if (lane == 0) atomicAdd(&lsum[r0 + i], v);
+        }
       }
       ok = rendezvous(70, seg_i);
-      if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(4));
+      if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(0));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
