@@ -71,9 +71,13 @@ UQ_DEV uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_sha
 UQ_DEV void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
 UQ_DEV void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 UQ_DEV void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+// One blocking try: the thread is suspended by the hardware until the phase completes or the time hint (nanoseconds)
+// runs out.  Without the hint a failed try returns almost at once, and several waiting warps then spin through the
+// issue slots the working warps of their sub-partition need.
 UQ_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000000u) : "memory");
   return ok;
 }
 UQ_DEV unsigned long long now_ns() {
@@ -310,11 +314,17 @@ template <int D, int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc) {
   using C = Cfg<D, NT>;
-  extern __shared__ uint8_t smem_raw[];
+  // declared 1024-byte aligned (swizzled tiles need it) and used without any integer arithmetic on the pointer, so that the
+  // compiler keeps every access in the shared state space (ld.shared / st.shared instead of generic loads and stores)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const UQParams& p = prm.p;
   const UQLaunch& x = prm.x;
-  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sm = smem_raw;
   const uint32_t sm_a = smem_u32(sm);
+  if (sm_a & 1023u) {   // never expected; the swizzled layouts below would be wrong
+    if (threadIdx.x == 0) uq_report(prm.x.status, 2u, sm_a, 0u);
+    return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::oAbort);
   int* prefix = reinterpret_cast<int*>(sm + C::oPrefix);
