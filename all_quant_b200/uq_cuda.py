@@ -316,3 +316,50 @@ def last_path():
 
 def launch_count():
     return int(lib().uqb_launch_count())
+
+
+# ---------------------------------------------------------------------------------------------- multi-GPU host side
+# The reference has no multi-device code.  Two ways to spread the path over the GPUs of one box:
+#   (a) KV-head partition: every GPU owns Hkv / N heads of the cache and the matching query heads; no data-path collective.
+#   (b) context split: every GPU owns a contiguous range of each sequence's pages; partials are all-gathered and merged.
+
+def head_shard(q, kc, ks, vc, vs, rank, world):
+    """Mode (a): this rank's slice of the heads.  Returns contiguous (q [B,K,Hq/N,D], kc, ks, vc, vs [pages,Hkv/N,...]).
+    In a deployment each GPU only ever holds its own slice; the page table and seq_lens are the same on every rank."""
+    HKV, HQ = kc.shape[1], q.shape[2]
+    if HKV % world:
+        raise ValueError("the number of KV heads must be divisible by the number of ranks")
+    hk, G = HKV // world, HQ // HKV
+    sl = slice(rank * hk, (rank + 1) * hk)
+    return (q[:, :, rank * hk * G:(rank + 1) * hk * G].contiguous(),) + tuple(t[:, sl].contiguous() for t in (kc, ks, vc, vs))
+
+
+def context_shard(block_table, rank, world, page_size):
+    """Mode (b): this rank's slice of every sequence's page table and the global position of its first key.
+    Rank r owns logical pages [r * per, (r + 1) * per) with per = ceil(max_pages / world).  Returns
+    (local block_table [B, per], pos_offset int32 [B]); seq_lens stay global."""
+    B, max_pages = block_table.shape
+    per = max(1, -(-max_pages // world))
+    lo, hi = min(rank * per, max_pages), min((rank + 1) * per, max_pages)
+    bt = torch.zeros((B, per), dtype=block_table.dtype, device=block_table.device)
+    bt[:, : hi - lo] = block_table[:, lo:hi]
+    off = torch.full((B,), lo * page_size, dtype=torch.int32, device=block_table.device)
+    return bt.contiguous(), off
+
+
+def uq_decode_context_split(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, *, group=None, nsplit=None, sm_scale=None,
+                            partial_fn=None, merge_fn=None):
+    """Mode (b) on one rank: attention over this rank's context shard, an all-gather of the partials (o fp32 [B,K,Hq,D] and
+    lse2 fp32 [B,K,Hq] per rank: K*Hq*(D+1) floats per sequence) over `group`, then the log-sum-exp merge.  Every rank
+    returns the full bf16 output.  partial_fn / merge_fn default to the CUDA entry points; the CPU tests of the host logic
+    substitute the oracle for them."""
+    import torch.distributed as dist
+    partial_fn = partial_fn or uq_decode_partial
+    merge_fn = merge_fn or uq_merge
+    o, lse = partial_fn(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, nsplit=nsplit, sm_scale=sm_scale)
+    world = dist.get_world_size(group)
+    o_all = torch.empty((world * o.shape[0],) + tuple(o.shape[1:]), dtype=o.dtype, device=o.device)       # ranks concatenated along dim 0
+    l_all = torch.empty((world * lse.shape[0],) + tuple(lse.shape[1:]), dtype=lse.dtype, device=lse.device)
+    dist.all_gather_into_tensor(o_all, o.contiguous(), group=group)
+    dist.all_gather_into_tensor(l_all, lse.contiguous(), group=group)
+    return merge_fn(o_all.view((world,) + tuple(o.shape)), l_all.view((world,) + tuple(lse.shape)))

@@ -305,7 +305,7 @@ def run_ours(args, cfg):
     line = {"metric": "kv_read_throughput", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms_step, "us_per_layer_call": ms_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "l2": "two cache copies alternate; each 285 MB copy exceeds the 126 MB L2",
+            "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "l2": f"two cache copies alternate; each {by / 1e6:.0f} MB copy exceeds the 126 MB L2" if by > 126e6 else "two cache copies alternate (each smaller than L2: not a valid bench size)",
                        "sharding": "kv heads partitioned across ranks, no collective" if world > 1 else "single GPU",
                        "kernel_path": {1: "cuda-core", 2: "tcgen05"}.get(uq_cuda.last_path(), "?")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
@@ -337,9 +337,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kq", type=int, default=8, help="draft queries per sequence (K)")
     ap.add_argument("--config", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=0, help="override the context length (profiler captures use a shorter one; the JSON says so)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.ctx:
+        cfg["ctx"] = args.ctx
+        cfg["name"] = cfg["name"].replace("ctx32768", f"ctx{args.ctx}")
     if args.impl == "reference":
         run_reference_arm(args, cfg)
     else:
