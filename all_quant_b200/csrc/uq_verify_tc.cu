@@ -60,8 +60,11 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no per-tile rendezvous
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
-constexpr int kThreads = 640;      // 20 warps (5 per SM sub-partition): 96 registers per thread
-constexpr int kWarpSmB = 4, kWarpK = 8, kWarpV = 12, kWarpProd = 16, kWarpMma = 17;   // first warp of each role; softmax A = 0
+// Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
+// producer, Q.K issue, P.V issue, one idle warp.  The roles are latency bound (one warp of a role per SM sub-partition issues
+// about once per 10 cycles), so the softmax, the longest role at 64 rows, is spread over four warpgroups.
+__host__ __device__ constexpr int softmax_groups(int NT) { return NT >= 32 ? 4 : 2; }
+__host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
 constexpr int kRawStages = 4;
 constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
 constexpr float kNegBig = -1.0e30f;
@@ -311,7 +314,7 @@ struct Walker {
 
 // ---------------------------------------------------------------------------------------------- kernel
 template <int D, int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(cta_threads(NT), 1)
 uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc) {
   using C = Cfg<D, NT>;
   // declared 1024-byte aligned (swizzled tiles need it) and used without any integer arithmetic on the pointer, so that the
@@ -325,6 +328,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     if (threadIdx.x == 0) uq_report(prm.x.status, 2u, sm_a, 0u);
     return;
   }
+  constexpr int NSG = softmax_groups(NT), kThreads = cta_threads(NT);
+  constexpr int kWarpK = 4 * NSG, kWarpV = kWarpK + 4, kWarpProd = kWarpV + 4, kWarpMma = kWarpProd + 1;   // first warp of each role; softmax = 0
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::oAbort);
   int* prefix = reinterpret_cast<int*>(sm + C::oPrefix);
@@ -360,10 +365,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     for (int i = 0; i < 2; i++) {
       // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
       // barrier serialise in the shared-memory unit and cost more than the work they order
-      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 8);
-      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 8); mbar_init(bar(bPVdone + i), 1);
+      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 4 * NSG);
+      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPVdone + i), 1);
     }
-    mbar_init(bar(bQfull), 8); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 8); mbar_init(bar(bVote), 8);
+    mbar_init(bar(bQfull), 4 * NSG); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4 * NSG); mbar_init(bar(bVote), 4 * NSG);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
     reinterpret_cast<int*>(sm + C::oVote)[1] = 0;
@@ -576,10 +581,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
     }
     UQ_PROF_FLUSH(3, kk == 0)
-  } else if (warp < 8) {
-    // ================================================================= softmax + epilogue: two warpgroups, half the rows each
-    constexpr int HW = NT / 2;                          // rows (columns of S^T) per thread
-    const int grp = warp >> 2, quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = 0..255 within the role
+  } else if (warp < 4 * NSG) {
+    // ================================================================= softmax + epilogue: NSG warpgroups, NT / NSG rows each
+    constexpr int HW = NT / NSG;                        // rows (columns of S^T) per thread
+    constexpr int kSm = 128 * NSG;                      // threads of the role
+    const int grp = warp >> 2, quad = warp & 3, kk = quad * 32 + lane, st = tid;   // st = index within the role
     const int r0 = grp * HW;                            // first row of this thread
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     float* mref = reinterpret_cast<float*>(sm + C::oMref);     // [2][NT] per-row reference maxima, live copy = mref + mcur * NT
@@ -594,7 +600,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
     bool ok = true;
     UQ_PROF_DECL
-    auto rendezvous = [&](int id, int tile) -> bool {   // all 256 threads of the role; orders their shared-memory traffic
+    auto rendezvous = [&](int id, int tile) -> bool {   // every thread of the role; orders their shared-memory traffic
       warp_arrive(bar(bVote));
       const bool r = wait(bar(bVote), nvote & 1, id, tile UQ_PROF_SITE(1));
       nvote++;
@@ -620,7 +626,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // items without a single key: nobody computes them, their slots must read as empty
     for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
-      for (int i = st; i < x.ns_eff * rows; i += 256)
+      for (int i = st; i < x.ns_eff * rows; i += kSm)
         p.ml[uq_slot(p, it / p.HKV, it % p.HKV, i / rows) * x.BM + i % rows] = -INFINITY;
     }
     while (ok && wk.next(sg)) {
@@ -632,7 +638,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
       {
         uint32_t amax = 0;   // bf16 magnitudes compare as integers
-        for (int i = st; i < rows * (D / 8); i += 256) {
+        for (int i = st; i < rows * (D / 8); i += kSm) {
           const int n = i / (D / 8), a = i % (D / 8);
           const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
           const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
@@ -644,12 +650,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         ok = rendezvous(59, seg_i);
         if (!ok) break;
         const uint32_t* wq = reinterpret_cast<const uint32_t*>(wmax);
-        amax = max(max(max(wq[0], wq[1]), max(wq[2], wq[3])), max(max(wq[4], wq[5]), max(wq[6], wq[7])));
+        amax = 0;
+#pragma unroll
+        for (int w = 0; w < 4 * NSG; w++) amax = max(amax, wq[w]);
         int eq = amax ? (int)(amax >> 7) - 127 : 0;
         eq = min(max(eq, -126), 126);
         const float qf = __int_as_float((127 - eq) << 23);
         csc0 = x.sc2 * __int_as_float((127 + eq) << 23);
-        for (int i = st; i < NT * (D / 8); i += 256) {
+        for (int i = st; i < NT * (D / 8); i += kSm) {
           const int n = i / (D / 8), a = i % (D / 8);
           uint4 w = make_uint4(0, 0, 0, 0);
           if (n < rows) {
@@ -669,7 +677,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       warp_arrive(bar(bQfull));
       // the first segment of an item marks the slots the item does not use as empty
       if (sg.t0 == 0)
-        for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += 256)
+        for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += kSm)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
       ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
       {
@@ -917,7 +925,7 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   if (!make_code_map(&mk, p.kc, C::kCodeRow, p.PAGE) || !make_code_map(&mv, p.vc, C::kCodeRow, p.PAGE)) return cudaErrorInvalidValue;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  kern<<<sms, kThreads, C::kSmem, s>>>(prm, mk, mv);
+  kern<<<sms, cta_threads(NT), C::kSmem, s>>>(prm, mk, mv);
   return cudaGetLastError();
 }
 
