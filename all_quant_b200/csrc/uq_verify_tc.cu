@@ -66,6 +66,8 @@ constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 __host__ __device__ constexpr int softmax_groups(int NT) { return NT >= 32 ? 4 : 2; }
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
 constexpr int kRawStages = 4;
+constexpr int kSB = 3;   // ring depth of the K operand (TMEM), the S^T accumulators (TMEM) and the P^T tiles (shared memory)
+constexpr int kVB = 2;   // ring depth of the decoded V tiles (shared memory, 32 KB each)
 constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
 constexpr float kNegBig = -1.0e30f;
 
@@ -219,9 +221,9 @@ struct Cfg {
   static constexpr int oV = 0;
   static constexpr int oQ = oV + 2 * kVTile;
   static constexpr int oP = oQ + kQTile;
-  static constexpr int oRaw = oP + 2 * kPTile;
+  static constexpr int oRaw = oP + kSB * kPTile;
   static constexpr int oBar = oRaw + kRawStages * kRawStage;
-  static constexpr int kNumBars = 2 * kRawStages + 16;
+  static constexpr int kNumBars = 2 * kRawStages + 24;
   static constexpr int oMisc = oBar + kNumBars * 8;
   // misc: tmem slot, abort flag, vote flags, mref[2][NT], wmax[4][NT], lsum[NT], fac[NT], facO[NT], wr[8], ref side band, prefix[]
   static constexpr int oTmemSlot = oMisc;
@@ -235,18 +237,18 @@ struct Cfg {
   static constexpr int oWr = oFacO + NT * 4;          // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
   static constexpr int oRef = oWr + 32;          // [4][128] uint16: K reference byte | V reference byte << 8 of the last four tiles (a slot is rewritten only
                                                       // after the S^T buffer two tiles back was released, i.e. after its reader is done)
-  static constexpr int oPrefix = oRef + 4 * kKeys * 2;
+  static constexpr int oPrefix = oRef + 8 * kKeys * 2;
   static constexpr int kMaxB = 2048;
   static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4 + 1024;   // + slack for the 1024 alignment
   // TMEM columns
-  static constexpr int cK = 0;                 // 2 x 64: bf16 A operand of S^T
-  static constexpr int cS = 128;               // 2 x NT: fp32 S^T
-  static constexpr int cO = cS + 2 * NT;       // NT:     fp32 O^T
+  static constexpr int cK = 0;                 // kSB x 64: fp16 A operand of S^T
+  static constexpr int cS = kSB * 64;          // kSB x NT: fp32 S^T
+  static constexpr int cO = cS + kSB * NT;     // NT:       fp32 O^T
   static constexpr int cL = cO + NT;           // NT:     fp32 per-key partial row sums (lane = key): the softmax threads' accumulators, kept out of their registers
 };
 
 // barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
-enum { bKfull = 0, bSfull = 2, bSfree = 4, bVfull = 6, bPfull = 8, bPVdone = 10, bQfull = 12, bOdone = 13, bEpi = 14, bVote = 15 };
+enum { bKfull = 0, bSfull = 3, bSfree = 6, bPfull = 9, bPdone = 12, bVfull = 15, bVdone = 17, bQfull = 19, bOdone = 20, bEpi = 21, bVote = 22 };
 
 struct Params {
   UQParams p;
@@ -362,12 +364,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
     for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 8); }
-    for (int i = 0; i < 2; i++) {
-      // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
-      // barrier serialise in the shared-memory unit and cost more than the work they order
+    // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
+    // barrier serialise in the shared-memory unit and cost more than the work they order
+    for (int i = 0; i < kSB; i++) {
       mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 4 * NSG);
-      mbar_init(bar(bVfull + i), 4); mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPVdone + i), 1);
+      mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPdone + i), 1);
     }
+    for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), 4); mbar_init(bar(bVdone + i), 1); }
     mbar_init(bar(bQfull), 4 * NSG); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4 * NSG); mbar_init(bar(bVote), 4 * NSG);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
@@ -446,9 +449,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       if (lane == 0) {
         ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
-          const int buf = cnt & 1;
-          ok = wait(bar(bKfull + buf), (cnt >> 1) & 1, 24 + buf, cnt UQ_PROF_SITE(2));
-          if (ok && cnt >= 2) ok = wait(bar(bSfree + buf), ((cnt >> 1) - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
+          const int buf = cnt % kSB, ph = cnt / kSB;
+          ok = wait(bar(bKfull + buf), ph & 1, 24 + buf, cnt UQ_PROF_SITE(2));
+          if (ok && cnt >= kSB) ok = wait(bar(bSfree + buf), (ph - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
           if (!ok) break;
           tc_fence_after();
           UQ_PROF_T0
@@ -476,16 +479,17 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
         const int c0 = cnt;
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
-          const int buf = cnt & 1;
-          ok = wait(bar(bPfull + buf), (cnt >> 1) & 1, 20 + buf, cnt, nullptr);
-          if (ok) ok = wait(bar(bVfull + buf), (cnt >> 1) & 1, 22 + buf, cnt, nullptr);
+          const int buf = cnt % kSB, vb = cnt % kVB;
+          ok = wait(bar(bPfull + buf), (cnt / kSB) & 1, 20 + buf, cnt, nullptr);
+          if (ok) ok = wait(bar(bVfull + vb), (cnt / kVB) & 1, 22 + vb, cnt, nullptr);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t va = v_desc + (uint64_t)(buf * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
+          const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
           for (int kk = 0; kk < kKeys / 16; kk++)
             mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
-          tc_commit(bar(bPVdone + buf));
+          tc_commit(bar(bPdone + buf));
+          tc_commit(bar(bVdone + vb));
         }
         if (ok) tc_commit(bar(bOdone));
       } else {
@@ -503,9 +507,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     UQ_PROF_DECL
     while (ok && wk.next(sg)) {
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
-        const int stage = cnt % kRawStages, buf = cnt & 1;
+        const int stage = cnt % kRawStages, buf = cnt % kSB;
         ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= 2) ok = wait(bar(bSfull + buf), ((cnt >> 1) - 1) & 1, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T(cnt-2) done: its A operand is free
+        if (ok && cnt >= kSB) ok = wait(bar(bSfull + buf), (cnt / kSB - 1) & 1, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T of the tile that used this buffer is done: the A operand is free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -515,7 +519,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         {
           const uint32_t kref = max_byte(sc4);
           const uint32_t vref = max_byte(*reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + C::kRawScales + kk * 4));
-          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
+          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
           uint4 c4[C::kGroups];
 #pragma unroll
           for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));   // 64-byte swizzle
@@ -546,9 +550,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
-        const int stage = cnt % kRawStages, buf = cnt & 1;
+        const int stage = cnt % kRawStages, buf = cnt % kVB;
         ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 50 + stage, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of tile cnt-2 done: tile buffer free
+        if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), (cnt / kVB - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         UQ_PROF_T0
@@ -688,16 +692,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       const int c0 = cnt;
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
-        const int buf = cnt & 1;
-        ok = wait(bar(bSfull + buf), (cnt >> 1) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= 2) ok = wait(bar(bPVdone + buf), ((cnt >> 1) - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(0));   // P buffer free
+        const int buf = cnt % kSB;
+        ok = wait(bar(bSfull + buf), (cnt / kSB) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= kSB) ok = wait(bar(bPdone + buf), (cnt / kSB - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(0));   // P buffer free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         UQ_PROF_TA
         const uint32_t s_addr = lane_addr + C::cS + buf * NT + r0;
         // this key: reference scale bytes, position, visibility
-        const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 3) * kKeys + kk];
+        const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk];
         const int vref = (int)(rf >> 8);
         const float ck = csc0 * uq_scale_f32(rf & 0xFFu);
         const int key = t * kKeys + kk;
@@ -787,7 +791,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           if (cnt > c0) {
             // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's part
-            ok = wait(bar(bPVdone + ((cnt - 1) & 1)), ((cnt - 1) >> 1) & 1, 66, cnt UQ_PROF_SITE(0));
+            ok = wait(bar(bPdone + (cnt - 1) % kSB), ((cnt - 1) / kSB) & 1, 66, cnt UQ_PROF_SITE(0));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
