@@ -32,6 +32,13 @@
 
 namespace tc {
 
+#ifdef UQ_TC_TRACE
+// timeline of CTA 0 (developer build only): clock64 stamps of each role's events for its first 64 tiles
+__device__ long long g_tc_trace[64][16];
+#define UQ_TRACE(ev, c) if (blockIdx.x == 0 && (c) < 64) g_tc_trace[c][ev] = clock64();
+#else
+#define UQ_TRACE(ev, c)
+#endif
 #ifdef UQ_TC_PROF
 // per-role cycle counters (profiling build only): [role][0..5] cycles spent in the role's wait sites, [6] event count, [7] total cycles
 __device__ unsigned long long g_tc_prof[5][8];
@@ -244,11 +251,10 @@ struct Cfg {
   static constexpr int cK = 0;                 // kSB x 64: fp16 A operand of S^T
   static constexpr int cS = kSB * 64;          // kSB x NT: fp32 S^T
   static constexpr int cO = cS + kSB * NT;     // NT:       fp32 O^T
-  static constexpr int cL = cO + NT;           // NT:     fp32 per-key partial row sums (lane = key): the softmax threads' accumulators, kept out of their registers
 };
 
 // barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
-enum { bKfull = 0, bSfull = 3, bSfree = 6, bPfull = 9, bPdone = 12, bVfull = 15, bVdone = 17, bQfull = 19, bOdone = 20, bEpi = 21, bVote = 22 };
+enum { bKfull = 0, bSfull = 3, bPfull = 9, bPdone = 12, bVfull = 15, bVdone = 17, bQfull = 19, bOdone = 20, bEpi = 21, bVote = 22 };
 
 struct Params {
   UQParams p;
@@ -367,7 +373,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
-      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1); mbar_init(bar(bSfree + i), 4 * NSG);
+      mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1);
       mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPdone + i), 1);
     }
     for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), 4); mbar_init(bar(bVdone + i), 1); }
@@ -422,6 +428,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t dst = sm_a + C::oRaw + stage * C::kRawStage;
+        if (lane == 0) { UQ_TRACE(0, cnt) }
         if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * 2u * (page_bytes_codes + page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
@@ -451,14 +458,19 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
           const int buf = cnt % kSB, ph = cnt / kSB;
           ok = wait(bar(bKfull + buf), ph & 1, 24 + buf, cnt UQ_PROF_SITE(2));
-          if (ok && cnt >= kSB) ok = wait(bar(bSfree + buf), (ph - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
+          // ring slot free: the softmax wrote the slot's previous P^T (so it has consumed the slot's S^T) and the P.V that read
+          // that P^T is done (so the softmax may overwrite it without a wait of its own)
+          if (ok && cnt >= kSB) ok = wait(bar(bPfull + buf), (ph - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
+          if (ok && cnt >= kSB) ok = wait(bar(bPdone + buf), (ph - 1) & 1, 28 + buf, cnt UQ_PROF_SITE(3));
           if (!ok) break;
           tc_fence_after();
+          UQ_TRACE(5, cnt)
           UQ_PROF_T0
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++)
             mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
           tc_commit(bar(bSfull + buf));
+          UQ_TRACE(6, cnt)
           UQ_PROF_T1(6)
         }
       } else {
@@ -484,12 +496,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (ok) ok = wait(bar(bVfull + vb), (cnt / kVB) & 1, 22 + vb, cnt, nullptr);
           if (!ok) break;
           tc_fence_after();
+          UQ_TRACE(7, cnt)
           const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
           for (int kk = 0; kk < kKeys / 16; kk++)
             mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
           tc_commit(bar(bPdone + buf));
           tc_commit(bar(bVdone + vb));
+          UQ_TRACE(8, cnt)
         }
         if (ok) tc_commit(bar(bOdone));
       } else {
@@ -513,6 +527,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        if (kk == 0) { UQ_TRACE(1, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
         const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
@@ -536,6 +551,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         tc_fence_before();
         warp_arrive(bar(bKfull + buf));
         warp_arrive(bar_raw_empty(stage));
+        if (kk == 0) { UQ_TRACE(2, cnt) }
         UQ_PROF_T1(3)
       }
     }
@@ -555,6 +571,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), (cnt / kVB - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (kk == 0) { UQ_TRACE(3, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kRawCodes;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
@@ -581,6 +598,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         fence_async_smem();
         warp_arrive(bar(bVfull + buf));
         warp_arrive(bar_raw_empty(stage));
+        if (kk == 0) { UQ_TRACE(4, cnt) }
         UQ_PROF_T1(3)
       }
     }
@@ -626,7 +644,6 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       tc_wait_st();
     };
-    const uint32_t l_addr = lane_addr + C::cL + r0;   // this thread's row sums over the keys it has seen (one TMEM lane per key slot)
     // items without a single key: nobody computes them, their slots must read as empty
     for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
@@ -684,20 +701,17 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += kSm)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
       ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
-      {
-        float z[HW];
+      float l[HW];
 #pragma unroll
-        for (int i = 0; i < HW; i++) z[i] = 0.f;
-        store_cols(l_addr, z);
-      }
+      for (int i = 0; i < HW; i++) l[i] = 0.f;
       const int c0 = cnt;
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
         const int buf = cnt % kSB;
         ok = wait(bar(bSfull + buf), (cnt / kSB) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= kSB) ok = wait(bar(bPdone + buf), (cnt / kSB - 1) & 1, 68 + buf, cnt UQ_PROF_SITE(0));   // P buffer free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        if (st == 0) { UQ_TRACE(9, cnt) }
         UQ_PROF_TA
         const uint32_t s_addr = lane_addr + C::cS + buf * NT + r0;
         // this key: reference scale bytes, position, visibility
@@ -738,11 +752,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < HW; i++) pv[i] = 0.5f;
         }
+        if (st == 0) { UQ_TRACE(10, cnt) }
         UQ_PROF_TB(2)
         const int rbyte = (int)wr[4 + mcur];
         const float xm = probabilities(mref + mcur * NT);
         UQ_PROF_TB(3)
         if (!(UQ_ABL & 2) || cnt == c0) write_p(rbyte);
+        if (st == 0) { UQ_TRACE(11, cnt) }
         UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
         const int vslot = nvote & 1;
@@ -782,13 +798,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           ok = rendezvous(67, cnt);
           if (!ok) break;
-          {
-            float lv[HW];
-            load_scores(l_addr, lv);
 #pragma unroll
-            for (int i = 0; i < HW; i++) lv[i] *= fac_s[r0 + i];
-            store_cols(l_addr, lv);
-          }
+          for (int i = 0; i < HW; i++) l[i] *= fac_s[r0 + i];
           if (cnt > c0) {
             // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's part
             ok = wait(bar(bPdone + (cnt - 1) % kSB), ((cnt - 1) / kSB) & 1, 66, cnt UQ_PROF_SITE(0));
@@ -807,31 +818,22 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           write_p((int)wr[4 + mcur]);
         }
         UQ_PROF_TA2
-        {
-          float lv[HW];
-          load_scores(l_addr, lv);
 #pragma unroll
-          for (int i = 0; i < HW; i++) lv[i] += pv[i];
-          store_cols(l_addr, lv);
-        }
+        for (int i = 0; i < HW; i++) l[i] += pv[i];
         tc_fence_before();
-        warp_arrive(bar(bSfree + buf));   // the scores are consumed
         fence_async_smem();
-        warp_arrive(bar(bPfull + buf));
+        warp_arrive(bar(bPfull + buf));   // P^T is written; it also tells the Q.K issuer that this slot's S^T is consumed
+        if (st == 0) { UQ_TRACE(13, cnt) }
         UQ_PROF_TB(5)
       }
       if (!ok) break;
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
-      {
-        float lv[HW];
-        load_scores(l_addr, lv);
 #pragma unroll
-        for (int i = 0; i < HW; i++) {
-          float v = lv[i];
+      for (int i = 0; i < HW; i++) {
+        float v = l[i];
 #pragma unroll
-          for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-          if (lane == 0) atomicAdd(&lsum[r0 + i], v);
-        }
+        for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+        if (lane == 0) atomicAdd(&lsum[r0 + i], v);
       }
       ok = rendezvous(70, seg_i);
       if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(0));
@@ -935,6 +937,13 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
 
 }  // namespace tc
 
+#ifdef UQ_TC_TRACE
+extern "C" int uqb_debug_tc_trace(long long* out1024) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out1024, tc::g_tc_trace, sizeof(long long) * 1024);
+  return (int)e;
+}
+#endif
 #ifdef UQ_TC_PROF
 // profiling build only: read and clear the per-role cycle counters (5 roles x 8 counters)
 extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
