@@ -8,24 +8,31 @@
 //     S^T[key, row] = Kdeq[key, :] . Q[row, :]        M = 128 keys, N = NT rows, K = D      (A from TMEM)
 //     O^T[d,   row] += Vdeq[key, d] * P[key, row]     M = 128 channels, N = NT rows, K = 128 keys
 //
-// One CTA per SM, 512 threads = four warpgroups:
-//   warps 0-3   softmax   thread = key: reads its lane of S^T, exp2 with a lazily updated per-row reference
-//                         maximum, writes P^T to shared memory (MN-major B operand), keeps per-thread row sums;
-//                         at the end of a segment reduces the sums, reads O^T and writes the partial.
-//   warps 4-7   K decode  thread = key: nibbles + UE8M0 -> bf16 in registers -> tcgen05.st into the A operand
-//   warps 8-11  V decode  thread = key: -> 128-byte-swizzled bf16 tile in shared memory (MN-major A operand)
-//   warp 12     producer  TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code
-//                         row without bank conflicts) of the K/V code pages + bulk copies of the scale pages
-//   warp 13     MMA       issues tcgen05.mma, owns the TMEM allocation        (warps 14-15 idle)
+// One CTA per SM.  Warp roles (NSG = 4 softmax warpgroups when there are 32+ rows, else 2):
+//   softmax   4*NSG warps  thread = (key, NT/NSG rows): reads its lane of S^T from TMEM, exp2 against a per-row REFERENCE
+//                          maximum that moves only when a score exceeds it by 2^8 (the threads agree through one
+//                          rendezvous per tile), writes P^T fp16 to shared memory (MN-major B operand), keeps row sums in
+//                          registers; at the end of a segment reduces the sums, reads O^T and writes the partial.
+//   K decode  4 warps      thread = key: e2m1 -> fp16 by the hardware conversion, one fp16 multiply by the group scale
+//                          relative to the key's largest, tcgen05.st into the TMEM A operand (ring of 3)
+//   V decode  4 warps      thread = key: the same decode -> 128-byte-swizzled fp16 tile in shared memory (ring of 2)
+//   producer  1 warp       TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code row without
+//                          bank conflicts) of the K/V code pages + bulk copies of the scale pages, ring of 4 tiles
+//   Q.K issue 1 warp       8 tcgen05.mma per tile (one thread), owns the TMEM allocation
+//   P.V issue 1 warp       8 tcgen05.mma per tile (one thread)
+// The key's reference scales 2^(ref-127) are applied in fp32 by the softmax threads that own the key (K's to the score,
+// V's to the probability, relative to a running reference of the segment so that P fits fp16).
 // Work is a flat list of 128-key tiles over all (sequence, kv head) items, cut into equal chunks, one per CTA;
 // a chunk that crosses items yields several segments, each written to its own partial slot.
 //
-// Decoded operands carry a fixed bias of 2^-64 (K and V alike: value * 2^(s-127-64)) so that one bf16
-// multiply covers scale bytes 59..192 exactly; the bias is undone in fp32 (scores: folded into the softmax
-// scale; outputs: one multiply in the epilogue).  Scale bytes above 192 take a two-multiply path.
-//
 // Every wait is bounded (about one second): on expiry the thread records the barrier in the status record,
 // raises the CTA's abort flag and every role drains to the common exit, which frees TMEM.
+//
+// Where the time goes (clock64 timeline of one CTA, headline shape, K=8): the roles are latency bound, not throughput
+// bound.  A tile takes the softmax role about 3 200 cycles (score load 220, exp2 burst of all softmax warps at once and
+// the P^T write 1 500, rendezvous and hand-over 1 000, gap 500) against about 1 120 for the tensor pipe (a tcgen05.mma with
+// M = 128 costs 65-76 cycles for any N <= 128) and 600-1 000 for each decode role; every change of segment drains and
+// refills the pipeline (about 30 000 cycles: epilogue, query tile conversion, first-tile reference move).
 #include <cuda.h>
 
 #include "uq_common.cuh"
