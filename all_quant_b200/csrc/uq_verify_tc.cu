@@ -79,9 +79,10 @@ constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // about once per 10 cycles), so the softmax, the longest role at 64 rows, is spread over four warpgroups.
 __host__ __device__ constexpr int softmax_groups(int NT) { return NT >= 32 ? 4 : 2; }
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
-constexpr int kRawStages = 4;
-constexpr int kSB = 3;   // ring depth of the K operand (TMEM), the S^T accumulators (TMEM) and the P^T tiles (shared memory)
-constexpr int kVB = 2;   // ring depth of the decoded V tiles (shared memory, 32 KB each)
+// ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
+__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : 4; }   // raw code/scale tiles in flight (TMA)
+__host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : 3; }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
+__host__ __device__ constexpr int ring_vb(int D) { return D == 256 ? 1 : 2; }      // decoded V tiles (shared memory)
 constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
 constexpr float kNegBig = -1.0e30f;
 
@@ -209,7 +210,20 @@ UQ_DEV uint32_t pow2_f16x2(int e) {
   const uint32_t b = e >= -14 ? (uint32_t)(e + 15) << 10 : (e >= -24 ? 1u << (e + 24) : 0u);
   return b | (b << 16);
 }
-UQ_DEV uint32_t max_byte(uint32_t v) { return max(max(v & 0xFFu, (v >> 8) & 0xFFu), max((v >> 16) & 0xFFu, v >> 24)); }
+// the D/32 scale bytes of one key (2, 4 or 8 bytes, contiguous) as one 64-bit value, byte g = group g
+template <int G>
+UQ_DEV unsigned long long load_scales(const uint8_t* p) {
+  if constexpr (G == 2) return *reinterpret_cast<const uint16_t*>(p);
+  else if constexpr (G == 4) return *reinterpret_cast<const uint32_t*>(p);
+  else return *reinterpret_cast<const unsigned long long*>(p);
+}
+template <int G>
+UQ_DEV uint32_t max_byte(unsigned long long v) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int g = 0; g < G; g++) m = max(m, (uint32_t)(v >> (8 * g)) & 0xFFu);
+  return m;
+}
 // 2^e as fp32 for any integer e (clamped to the finite range; e <= -127 uses the denormal / zero)
 UQ_DEV float pow2_f32(int e) {
   e = min(e, 127);
@@ -219,21 +233,26 @@ UQ_DEV float pow2_f32(int e) {
 // ---------------------------------------------------------------------------------------------- layout
 template <int D, int NT>
 struct Cfg {
-  static_assert(D == 128, "head_dim 128 only");
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim 64 / 128 / 256");
   static_assert(NT == 16 || NT == 32 || NT == 64, "rows padded to 16 / 32 / 64");
+  static constexpr int kRawStages = raw_stages(D), kSB = ring_sb(D), kVB = ring_vb(D);
   static constexpr int kCodeRow = D / 2;                 // bytes of codes per key
   static constexpr int kGroups = D / 32;                 // scale bytes per key
-  static constexpr int kRawCodes = kKeys * kCodeRow;     // 8192
-  static constexpr int kRawScales = kKeys * kGroups;     // 512
+  static constexpr int kChunks = kCodeRow / 16;          // 16-byte chunks per code row = scale groups
+  static constexpr int kRowsPer128 = 128 / kCodeRow;     // code rows per 128 bytes: the TMA swizzle (32 / 64 / 128 B) XORs the chunk index with (row / this)
+  static constexpr int kRawCodes = kKeys * kCodeRow;
+  static constexpr int kRawScales = kKeys * kGroups;
   static constexpr int kRawStage = 2 * (kRawCodes + kRawScales);
-  static constexpr int kVTile = kKeys * D * 2;           // bf16 [key][d], two 64-channel halves of [128][128 B]
-  static constexpr int kVHalf = kKeys * 128;
-  static constexpr int kQTile = NT * D * 2;              // bf16 [row][position], two halves of [NT][128 B]
-  static constexpr int kQHalf = NT * 128;
-  static constexpr int kPTile = kKeys * 128;             // bf16 [key][row], rows padded to 64
-  // shared memory map (offsets from a 1024-aligned base)
+  static constexpr int kHalves = D / 64;                 // 64-channel (128-byte) column blocks of the fp16 tiles
+  static constexpr int kVHalf = kKeys * 128;             // fp16 [key][64 channels]
+  static constexpr int kVTile = kHalves * kVHalf;
+  static constexpr int kQHalf = NT * 128;                // fp16 [row][64 channels]
+  static constexpr int kQTile = kHalves * kQHalf;
+  static constexpr int kPTile = kKeys * 128;             // fp16 [key][row], rows padded to 64
+  static constexpr int kDB = D > 128 ? D / 128 : 1;      // 128-channel blocks of O^T (one accumulator each); head_dim 64 uses the lower half of one
+  // shared memory map (offsets from the 1024-aligned base)
   static constexpr int oV = 0;
-  static constexpr int oQ = oV + 2 * kVTile;
+  static constexpr int oQ = oV + kVB * kVTile;
   static constexpr int oP = oQ + kQTile;
   static constexpr int oRaw = oP + kSB * kPTile;
   static constexpr int oBar = oRaw + kRawStages * kRawStage;
@@ -247,17 +266,20 @@ struct Cfg {
   static constexpr int oWmax = oMref + 2 * NT * 4;
   static constexpr int oLsum = oWmax + 4 * NT * 4;
   static constexpr int oFac = oLsum + NT * 4;
-  static constexpr int oFacO = oFac + NT * 4;         // per-row factor for O^T (row factor x V-reference factor)
-  static constexpr int oWr = oFacO + NT * 4;          // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
-  static constexpr int oRef = oWr + 32;          // [4][128] uint16: K reference byte | V reference byte << 8 of the last four tiles (a slot is rewritten only
-                                                      // after the S^T buffer two tiles back was released, i.e. after its reader is done)
+  static constexpr int oFacO = oFac + NT * 4;            // per-row factor for O^T (row factor x V-reference factor)
+  static constexpr int oWr = oFacO + NT * 4;             // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
+  static constexpr int oRef = oWr + 32;                  // [8][128] uint16: K reference byte | V reference byte << 8 of the last eight tiles (a slot is rewritten
+                                                         // only after its readers, the softmax threads of a tile several ring turns back, are done)
   static constexpr int oPrefix = oRef + 8 * kKeys * 2;
-  static constexpr int kMaxB = 2048;
-  static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4 + 1024;   // + slack for the 1024 alignment
+  static constexpr int kMaxB = 1024;
+  static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4;
+  static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // TMEM columns
-  static constexpr int cK = 0;                 // kSB x 64: fp16 A operand of S^T
-  static constexpr int cS = kSB * 64;          // kSB x NT: fp32 S^T
-  static constexpr int cO = cS + kSB * NT;     // NT:       fp32 O^T
+  static constexpr int kKCols = D / 2;                   // fp16 A operand of S^T: two channels per 32-bit column
+  static constexpr int cK = 0;                           // kSB x kKCols
+  static constexpr int cS = kSB * kKCols;                // kSB x NT: fp32 S^T
+  static constexpr int cO = cS + kSB * NT;               // kDB x NT: fp32 O^T
+  static_assert(cO + kDB * NT <= 512, "TMEM budget");
 };
 
 // barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
@@ -344,6 +366,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     return;
   }
   constexpr int NSG = softmax_groups(NT), kThreads = cta_threads(NT);
+  constexpr int kRawStages = C::kRawStages, kSB = C::kSB, kVB = C::kVB;
   constexpr int kWarpK = 4 * NSG, kWarpV = kWarpK + 4, kWarpProd = kWarpV + 4, kWarpMma = kWarpProd + 1;   // first warp of each role; softmax = 0
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::oAbort);
@@ -475,7 +498,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           UQ_PROF_T0
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++)
-            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * 64 + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * C::kKCols + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
           tc_commit(bar(bSfull + buf));
           UQ_TRACE(6, cnt)
           UQ_PROF_T1(6)
@@ -492,7 +515,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
     int cnt = 0, seg_i = 0;
     bool ok = true;
-    const uint64_t v_desc = smem_desc(sm_a + C::oV, C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
+    // A = V^T: M = 128 channels = two 64-channel halves (leading-dimension offset = one half).  head_dim 64 has one half only:
+    // offset 0 makes the upper 64 accumulator lanes a copy of the lower ones, which the epilogue ignores.
+    const uint64_t v_desc = smem_desc(sm_a + C::oV, D == 64 ? 0 : C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
     while (ok && wk.next(sg)) {
       if (lane == 0) {
         if (seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
@@ -506,8 +531,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           UQ_TRACE(7, cnt)
           const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
-          for (int kk = 0; kk < kKeys / 16; kk++)
-            mma_ss(tmem + C::cO, va + (uint64_t)(kk * (2048 >> 4)), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
+          for (int db = 0; db < C::kDB; db++) {
+#pragma unroll
+            for (int kk = 0; kk < kKeys / 16; kk++)
+              mma_ss(tmem + C::cO + db * NT, va + (uint64_t)((db * 2 * C::kVHalf + kk * 2048) >> 4), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
+          }
           tc_commit(bar(bPdone + buf));
           tc_commit(bar(bVdone + vb));
           UQ_TRACE(8, cnt)
@@ -537,20 +565,25 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (kk == 0) { UQ_TRACE(1, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
-        const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + kk * 4);
-        {
-          const uint32_t kref = max_byte(sc4);
-          const uint32_t vref = max_byte(*reinterpret_cast<const uint32_t*>(raw + 2 * C::kRawCodes + C::kRawScales + kk * 4));
-          reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
-          uint4 c4[C::kGroups];
+        const unsigned long long sc = load_scales<C::kGroups>(raw + 2 * C::kRawCodes + kk * C::kGroups);
+        const uint32_t kref = max_byte<C::kGroups>(sc);
+        const uint32_t vref = max_byte<C::kGroups>(load_scales<C::kGroups>(raw + 2 * C::kRawCodes + C::kRawScales + kk * C::kGroups));
+        reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
+        // the code row of this key: chunk g (16 bytes = group g) sits at chunk g ^ ((key / rows per 128 B) mod chunks) (TMA swizzle)
+        const uint8_t* krow = raw + kk * C::kCodeRow;
+        const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
 #pragma unroll
-          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));   // 64-byte swizzle
+        for (int g0 = 0; g0 < C::kGroups; g0 += 4) {   // four groups at a time: loads first, then conversion
+          constexpr int GN = C::kGroups < 4 ? C::kGroups : 4;
+          uint4 c4[GN];
 #pragma unroll
-          for (int g = 0; g < C::kGroups; g++) {
-            const uint32_t m = pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - (int)kref);
+          for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(krow + (((g0 + g) ^ swz) << 4));
+#pragma unroll
+          for (int g = 0; g < GN; g++) {
+            const uint32_t m = pow2_f16x2((int)((uint32_t)(sc >> (8 * (g0 + g))) & 0xFFu) - (int)kref);
             uint32_t o[16];
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
-            tmem_st16(lane_addr + C::cK + buf * 64 + g * 16, o);
+            tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
           }
         }
         UQ_PROF_T1(2)
@@ -583,22 +616,27 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kRawCodes;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
-        const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * 4);
-        {
-          const int vref = (int)max_byte(sc4);
-          uint4 c4[C::kGroups];
+        const unsigned long long sc = load_scales<C::kGroups>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * C::kGroups);
+        const int vref = (int)max_byte<C::kGroups>(sc);
+        const uint8_t* vcode = raw + kk * C::kCodeRow;
+        const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
 #pragma unroll
-          for (int g = 0; g < C::kGroups; g++) c4[g] = *reinterpret_cast<const uint4*>(raw + kk * 64 + ((g ^ ((kk >> 1) & 3)) << 4));
+        for (int g0 = 0; g0 < C::kGroups; g0 += 4) {
+          constexpr int GN = C::kGroups < 4 ? C::kGroups : 4;
+          uint4 c4[GN];
 #pragma unroll
-          for (int g = 0; g < C::kGroups; g++) {
-            const uint32_t m = live ? pow2_f16x2((int)((sc4 >> (8 * g)) & 0xFFu) - vref) : 0u;   // multiplier 0: keys past the end decode to zeros
+          for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(vcode + (((g0 + g) ^ swz) << 4));
+#pragma unroll
+          for (int g = 0; g < GN; g++) {
+            const int gg = g0 + g;
+            const uint32_t m = live ? pow2_f16x2((int)((uint32_t)(sc >> (8 * gg)) & 0xFFu) - vref) : 0u;   // multiplier 0: keys past the end decode to zeros
             uint32_t o[16];
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
-            // output chunk 4g + w (8 channels) of the key's 256-byte row: half (4g + w) >> 3, slot ((4g + w) & 7) ^ (key & 7)
-            uint8_t* vrow = vt + (g >> 1) * C::kVHalf + kk * 128;
+            // output chunk 4gg + w (8 channels) of the key's row: 64-channel half (4gg + w) >> 3, slot ((4gg + w) & 7) ^ (key & 7)
+            uint8_t* vrow = vt + (gg >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
             for (int w = 0; w < 4; w++)
-              *reinterpret_cast<uint4*>(vrow + ((((4 * g + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
+              *reinterpret_cast<uint4*>(vrow + ((((4 * gg + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
           }
         }
         UQ_PROF_T1(2)
@@ -813,11 +851,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            float ov[HW];
-            load_scores(lane_addr + C::cO + r0, ov);
 #pragma unroll
-            for (int i = 0; i < HW; i++) ov[i] *= facO_s[r0 + i];
-            store_cols(lane_addr + C::cO + r0, ov);
+            for (int db = 0; db < C::kDB; db++) {
+              float ov[HW];
+              load_scores(lane_addr + C::cO + db * NT + r0, ov);
+#pragma unroll
+              for (int i = 0; i < HW; i++) ov[i] *= facO_s[r0 + i];
+              store_cols(lane_addr + C::cO + db * NT + r0, ov);
+            }
           }
           mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
           load_scores(s_addr, pv);
@@ -853,14 +894,19 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         float* ml = p.ml + slot * x.BM;
         const float* mr = mref + mcur * NT;
         const float osc = pow2_f32((int)wr[4 + mcur] - 127);   // O^T was accumulated relative to the segment's V reference
-        float ov[HW];
-        load_scores(lane_addr + C::cO + r0, ov);   // accumulator lane kk = channel kk
 #pragma unroll
-        for (int i = 0; i < HW; i++) {
-          const int r = r0 + i;
-          if (r < rows) {
-            const float lr = lsum[r];
-            mo[(size_t)r * D + kk] = lr > 0.f ? ov[i] * (osc / lr) : 0.f;
+        for (int db = 0; db < C::kDB; db++) {
+          float ov[HW];
+          load_scores(lane_addr + C::cO + db * NT + r0, ov);   // accumulator lane kk of block db = channel 128 db + kk
+          if (db * 128 + kk < D) {                              // head_dim 64: the upper 64 lanes are a copy
+#pragma unroll
+            for (int i = 0; i < HW; i++) {
+              const int r = r0 + i;
+              if (r < rows) {
+                const float lr = lsum[r];
+                mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * (osc / lr) : 0.f;
+              }
+            }
           }
         }
         if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
@@ -905,6 +951,8 @@ EncodeTiledFn encode_fn() {
 // of physical pages is not part of the launch arguments, so the row extent is the largest the map can hold:
 // only rows named by the page table are ever touched.
 bool make_code_map(CUtensorMap* map, const uint8_t* base, int code_row_bytes, int page) {
+  // the swizzle span equals the code row (32 / 64 / 128 bytes): a thread reading its key's row then hits every bank once
+  const CUtensorMapSwizzle swz = code_row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (code_row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)code_row_bytes, (cuuint64_t)1 << 31};
@@ -912,7 +960,7 @@ bool make_code_map(CUtensorMap* map, const uint8_t* base, int code_row_bytes, in
   const cuuint32_t box[2] = {(cuuint32_t)code_row_bytes, (cuuint32_t)page};
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int D, int NT>
@@ -963,7 +1011,7 @@ extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
 #endif
 
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
-  if (p.D != 128) return false;
+  if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
   if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
   if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
@@ -973,8 +1021,18 @@ bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
 
 int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) { return p.nsplit; }
 
+template <int D>
+static cudaError_t dispatch_rows(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
+  if (x.rows <= 16) return tc::launch<D, 16>(p, x, s);
+  if (x.rows <= 32) return tc::launch<D, 32>(p, x, s);
+  return tc::launch<D, 64>(p, x, s);
+}
+
 cudaError_t uq_verify_tc_dispatch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
-  if (x.rows <= 16) return tc::launch<128, 16>(p, x, s);
-  if (x.rows <= 32) return tc::launch<128, 32>(p, x, s);
-  return tc::launch<128, 64>(p, x, s);
+  switch (p.D) {
+    case 64: return dispatch_rows<64>(p, x, s);
+    case 128: return dispatch_rows<128>(p, x, s);
+    case 256: return dispatch_rows<256>(p, x, s);
+  }
+  return cudaErrorInvalidValue;
 }
