@@ -83,7 +83,8 @@ __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_grou
 __host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : 4; }   // raw code/scale tiles in flight (TMA)
 __host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : 3; }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
 __host__ __device__ constexpr int ring_vb(int D) { return D == 256 ? 1 : 2; }      // decoded V tiles (shared memory)
-constexpr float kRescaleAt = 8.0f;   // a score this far (log2) above the row's reference maximum moves the reference
+constexpr float kRescaleAt = 12.0f;  // a score this far (log2) above the row's reference maximum does not fit the fp16 probability tile
+constexpr int kRedoWords = 32;       // a CTA's first 32 * kRedoWords segments can be marked for the second pass; later ones take the careful path at once
 constexpr float kNegBig = -1.0e30f;
 
 // ---------------------------------------------------------------------------------------------- PTX
@@ -272,7 +273,8 @@ struct Cfg {
                                                          // only after its readers, the softmax threads of a tile several ring turns back, are done)
   static constexpr int oPrefix = oRef + 8 * kKeys * 2;
   static constexpr int kMaxB = 1024;
-  static constexpr int kSmem = oPrefix + (kMaxB + 1) * 4;
+  static constexpr int oRedo = oPrefix + (kMaxB + 1) * 4;   // kRedoWords words of per-segment "run again" bits, then one word "any bit set"
+  static constexpr int kSmem = oRedo + (kRedoWords + 1) * 4;
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // TMEM columns
   static constexpr int kKCols = D / 2;                   // fp16 A operand of S^T: two channels per 32-bit column
@@ -413,6 +415,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     reinterpret_cast<int*>(sm + C::oVote)[1] = 0;
     fence_barrier_init();
   }
+  uint32_t* redo = reinterpret_cast<uint32_t*>(sm + C::oRedo);
+  for (int i = tid; i <= kRedoWords; i += kThreads) redo[i] = 0u;
   for (int b = tid; b < p.B; b += kThreads) {   // tiles per sequence, then an in-place scan by one thread
     int off;
     const int n = uq_n_local(p, x, b, &off);
@@ -433,18 +437,30 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sm + C::oTmemSlot);
 
   Walker wk;
-  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min);
   const int G = x.G, rows = x.rows;
   Seg sg;
+  // Two passes over the CTA's segments.  The first takes every segment on the quick path: the softmax threads fix each
+  // row's reference at the segment's first tile and afterwards only watch for a score or a V scale that no longer fits the
+  // fp16 probability tile; a segment where that happens is marked (its result is garbage) and the second pass runs the
+  // marked segments again on the careful path, where the threads agree tile by tile on moving the references.  Every role
+  // walks the same list and reads the same marks, so ring slots and barrier phases simply keep counting across the passes.
+  int cnt = 0, seg_i = 0;          // tiles and segments this role has processed: ring slots and barrier phases derive from them
+  bool ok = true;
+  int mcur = 0, nvote = 0;         // softmax role: live copy of the double-buffered references, rendezvous count
+  float csc0 = x.sc2;
+  for (int pass = 0; pass < 2; pass++) {
+  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min);
+  int ord = -1;                    // ordinal of the segment in the CTA's list
+  // does this pass run segment `ord`?  (pass 1: the marked ones)
+  auto take = [&]() -> bool { ord++; return pass == 0 || (ord < 32 * kRedoWords && ((redo[ord >> 5] >> (ord & 31)) & 1u)); };
 
   if (warp == kWarpProd) {
     // ================================================================= producer
     const int ppt = kKeys / p.PAGE;   // pages per tile
     UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kGroups;
-    int cnt = 0;
-    bool ok = true;
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int pages_valid = (n_loc + p.PAGE - 1) / p.PAGE;
@@ -477,12 +493,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // issued by two warps: an instruction occupies its issuing thread for as long as the tensor pipe takes to accept it
     // (about 70 cycles), so one thread doing both spends its waits and commits on the pipe's critical path.
     constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, 0, 0);   // A = K, B = Q, both fp16 (mixed 16-bit formats are not legal)
-    int cnt = 0, seg_i = 0;
-    bool ok = true;
     UQ_PROF_DECL
     // descriptors differ between instructions only in the start-address field (bits 0-13, units of 16 bytes)
     const uint64_t q_desc = smem_desc(sm_a + C::oQ, 16, 1024);
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
       if (lane == 0) {
         ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
         for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
@@ -513,12 +528,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   } else if (warp == kWarpMma + 1) {
     // ================================================================= MMA issue, O^T += V^T.P^T (one thread)
     constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
-    int cnt = 0, seg_i = 0;
-    bool ok = true;
     // A = V^T: M = 128 channels = two 64-channel halves (leading-dimension offset = one half).  head_dim 64 has one half only:
     // offset 0 makes the upper 64 accumulator lanes a copy of the lower ones, which the epilogue ignores.
     const uint64_t v_desc = smem_desc(sm_a + C::oV, D == 64 ? 0 : C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
       if (lane == 0) {
         if (seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
         const int c0 = cnt;
@@ -551,10 +565,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // ================================================================= K decode -> TMEM
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    int cnt = 0;
-    bool ok = true;
     UQ_PROF_DECL
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
         const int stage = cnt % kRawStages, buf = cnt % kSB;
         ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt UQ_PROF_SITE(0));
@@ -599,10 +612,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   } else if (warp >= kWarpV && warp < kWarpV + 4) {
     // ================================================================= V decode -> shared memory
     const int kk = (warp - kWarpV) * 32 + lane;
-    int cnt = 0;
-    bool ok = true;
     UQ_PROF_DECL
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
@@ -663,9 +675,6 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     uint32_t* wr = reinterpret_cast<uint32_t*>(sm + C::oWr);   // [0..3] per-warp maxima of V reference bytes, [4 + mcur] the segment's V reference byte
     int* vote = reinterpret_cast<int*>(sm + C::oVote);
     const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
-    float csc0 = x.sc2;
-    int cnt = 0, seg_i = 0, mcur = 0, nvote = 0;
-    bool ok = true;
     UQ_PROF_DECL
     auto rendezvous = [&](int id, int tile) -> bool {   // every thread of the role; orders their shared-memory traffic
       warp_arrive(bar(bVote));
@@ -690,12 +699,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       tc_wait_st();
     };
     // items without a single key: nobody computes them, their slots must read as empty
-    for (int it = blockIdx.x; it < wk.nitems; it += gridDim.x) {
+    for (int it = blockIdx.x; pass == 0 && it < wk.nitems; it += gridDim.x) {
       if (wk.item_tiles(it) != 0) continue;
       for (int i = st; i < x.ns_eff * rows; i += kSm)
         p.ml[uq_slot(p, it / p.HKV, it % p.HKV, i / rows) * x.BM + i % rows] = -INFINITY;
     }
     while (ok && wk.next(sg)) {
+      if (!take()) continue;
+      const bool careful = pass == 1 || ord >= 32 * kRedoWords;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int n_glob = p.seq_lens[sg.b];
@@ -806,11 +817,18 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (st == 0) { UQ_TRACE(11, cnt) }
         UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
+        const bool grew = __any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte));
+        const bool agree = careful || cnt == c0;   // the first tile of a segment sets the references; later tiles only on the careful path
         const int vslot = nvote & 1;
-        if (__any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte)) && lane == 0) atomicOr(&vote[vslot], 1);
-        if (!(UQ_ABL & 16) || cnt == c0) ok = rendezvous(64, cnt);
-        if (!ok) break;
-        if ((!(UQ_ABL & 16) || cnt == c0) && *reinterpret_cast<volatile int*>(&vote[vslot])) {
+        if (!agree) {
+          // quick path: what this tile wrote may have overflowed; mark the segment for the second pass and carry on
+          if (grew && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
+        } else {
+          if (grew && lane == 0) atomicOr(&vote[vslot], 1);
+          ok = rendezvous(64, cnt);
+          if (!ok) break;
+        }
+        if (agree && *reinterpret_cast<volatile int*>(&vote[vslot])) {
           UQ_PROF_COUNT(6)
           // ---- move the references (the first tile of a segment, then only on growth), rescale what was accumulated,
           // and redo this tile against the new references
@@ -919,9 +937,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     UQ_PROF_FLUSH(4, st == 0)
   }
 
-  // ---- common exit: every role gets here (all waits are bounded); TMEM goes back before the CTA ends
+  // ---- end of a pass: every role gets here (all waits are bounded)
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag || !*reinterpret_cast<volatile uint32_t*>(&redo[kRedoWords])) break;
+  }
+  // ---- common exit: TMEM goes back before the CTA ends
   if (warp == kWarpMma) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");

@@ -2,15 +2,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--kq 8] [--config 1]
 
-A step is one attention layer call on the headline configuration: B=8 sequences at context 32768,
+Default (--config 1, the headline): a step is one attention layer call with B=8 sequences at context 32768,
 Hq=64 / Hkv=8 / D=128, page 64, K draft queries (default 8), seeded synthetic data (bf16 N(0,1) queries,
 fp32 N(0,1) K/V with a lognormal(0,0.5) multiplier per K channel, encoded to UltraQuant FP4 by this
 library's append kernel, physical pages randomly permuted).  The metric is the KV-read throughput
-(algorithmic KV bytes of the call / time) and, in ms_per_step, the time per layer call.
+(algorithmic KV bytes of the step / time) and, in ms_per_step, the time per step.
 
-N > 1 (launched with torch.distributed.run, one rank per GPU): KV heads are partitioned across ranks with no
-collective; every rank owns Hkv=8 heads of its own (per-GPU work fixed: weak scaling) and the value is the
-bytes all ranks read over the slowest rank's time.
+N > 1 (launched with torch.distributed.run, one rank per GPU), by configuration:
+  1  every rank owns Hkv=8 heads of its own and runs the whole call (per-GPU work fixed: weak scaling, no collective);
+  2  Mistral-7B-shaped step: 32 layers, each the append-quantize of the K new tokens per sequence and the verify
+     call, B=8, context uniform in [8192, 16384], Hq=32 / Hkv=8; KV heads are divided across ranks (strong, no collective);
+  3  ragged serving batch: B=32, context uniform in [4096, 65536], Hq=64 / Hkv=8; KV heads divided across ranks (strong);
+  4  one long sequence: B=1, context 131072, Hq=32 / Hkv=4 / D=256; context pages divided across ranks, every rank
+     emits partials, an NCCL all-gather and the log-sum-exp merge kernel follow inside the timed step (strong).
+The value is the KV bytes all ranks read over the slowest rank's time.
 
 --impl reference times the CPU implementation of the same path (the C restatement of the reference's
 uqmt.attn.reference, all host threads) on a bounded sample of the same workload.
@@ -28,8 +33,43 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    1: dict(name="cfg1: B8 ctx32768 Hq64 Hkv8 D128 page64", B=8, ctx=32768, HQ=64, HKV=8, D=128, PAGE=64),
+    1: dict(name="cfg1: B8 ctx32768 Hq64 Hkv8 D128 page64", B=8, ctx=32768, HQ=64, HKV=8, D=128, PAGE=64, shard="replicas", layers=1, append=False),
+    2: dict(name="cfg2: 32 layers x (append + verify) B8 ctx U[8192,16384] Hq32 Hkv8 D128 page64", B=8, ctx=(8192, 16384), HQ=32, HKV=8, D=128,
+            PAGE=64, shard="heads", layers=32, append=True),
+    3: dict(name="cfg3: B32 ctx U[4096,65536] Hq64 Hkv8 D128 page64", B=32, ctx=(4096, 65536), HQ=64, HKV=8, D=128, PAGE=64, shard="heads",
+            layers=1, append=False),
+    4: dict(name="cfg4: B1 ctx131072 Hq32 Hkv4 D256 page64", B=1, ctx=131072, HQ=32, HKV=4, D=256, PAGE=64, shard="context", layers=1, append=False),
 }
+
+
+def seq_lengths(cfg):
+    """Per-sequence context lengths (drafts included): fixed, or seeded uniform in the configured range; the same on every rank."""
+    if isinstance(cfg["ctx"], tuple):
+        lo, hi = cfg["ctx"]
+        return np.random.default_rng(7).integers(lo, hi + 1, cfg["B"]).astype(np.int64)
+    return np.full(cfg["B"], cfg["ctx"], np.int64)
+
+
+def shard_plan(cfg, rank, world):
+    """What this rank holds: its head counts, per-sequence local token counts and the global position of its first key."""
+    lens = seq_lengths(cfg)
+    mode = cfg["shard"] if world > 1 else "single"
+    plan = dict(mode=mode, lens=lens, local=lens.copy(), off=0, hkv=cfg["HKV"], hq=cfg["HQ"])
+    if mode == "heads":
+        if cfg["HKV"] % world:
+            raise SystemExit(f"config needs Hkv={cfg['HKV']} divisible by the number of ranks")
+        plan["hkv"], plan["hq"] = cfg["HKV"] // world, cfg["HQ"] // world
+    elif mode == "context":
+        page = cfg["PAGE"]
+        max_pages = int(-(-lens.max() // page))
+        per = -(-max_pages // world)
+        plan["off"] = rank * per * page
+        plan["local"] = np.clip(lens - plan["off"], 0, per * page)
+    return plan
+
+
+def local_kv_bytes(cfg, plan):
+    return int(plan["local"].sum() * plan["hkv"] * 2 * (cfg["D"] // 2 + cfg["D"] // 32))
 
 
 def peaks():
@@ -99,37 +139,55 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ data
-def build_case(cfg, K, seed, device, copies=2):
-    """Seeded synthetic cache(s) and queries on `device`; the cache is encoded by the library's append kernel."""
+def build_case(cfg, plan, K, seed, device, copies=2):
+    """Seeded synthetic cache(s) and queries on `device` for this rank's shard; the cache is encoded by the
+    library's append kernel.  Returns q, the page table, global seq_lens, pos_offset, `copies` caches with the
+    same bytes at different addresses, and (for the append leg) the K newest tokens of every sequence with their slots."""
     import torch
     from all_quant_b200 import uq_cuda
-    B, ctx, HQ, HKV, D, PAGE = (cfg[k] for k in ("B", "ctx", "HQ", "HKV", "D", "PAGE"))
+    B, D, PAGE = cfg["B"], cfg["D"], cfg["PAGE"]
+    hkv, hq, local, off = plan["hkv"], plan["hq"], plan["local"], plan["off"]
     g = torch.Generator(device=device).manual_seed(seed)
-    npg = (ctx + PAGE - 1) // PAGE
-    pages = B * npg
-    chan = torch.exp(0.5 * torch.randn(1, HKV, D, generator=g, device=device))
-    perm = torch.randperm(pages, generator=g, device=device)
-    bt = perm.reshape(B, npg).to(torch.int32).contiguous()
-    kc = torch.empty(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device=device)
-    ks = torch.empty(pages, HKV, PAGE, D // 32, dtype=torch.uint8, device=device)
+    npgs = [int(-(-n // PAGE)) for n in local]
+    pages, width = max(1, sum(npgs)), max(1, max(npgs))
+    chan = torch.exp(0.5 * torch.randn(1, hkv, D, generator=g, device=device))
+    perm = torch.randperm(pages, generator=g, device=device).to(torch.int32)
+    bt = torch.zeros(B, width, dtype=torch.int32, device=device)
+    kc = torch.empty(pages, hkv, PAGE, D // 2, dtype=torch.uint8, device=device)
+    ks = torch.empty(pages, hkv, PAGE, D // 32, dtype=torch.uint8, device=device)
     vc, vs = torch.empty_like(kc), torch.empty_like(ks)
-    pos = torch.arange(ctx, device=device)
+    new_k, new_v, new_slots = [], [], []
+    first = 0
     for b in range(B):
-        k = torch.randn(ctx, HKV, D, generator=g, device=device) * chan
-        v = torch.randn(ctx, HKV, D, generator=g, device=device)
+        n, npg = int(local[b]), npgs[b]
+        bt[b, :npg] = perm[first:first + npg]
+        first += npg
+        if n == 0:
+            continue
+        pos = torch.arange(n, device=device)
+        k = torch.randn(n, hkv, D, generator=g, device=device) * chan
+        v = torch.randn(n, hkv, D, generator=g, device=device)
         slots = bt[b].long()[pos // PAGE] * PAGE + pos % PAGE
         uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots)
-    q = torch.randn(B, K, HQ, D, generator=g, device=device).bfloat16()
-    sl = torch.full((B,), ctx, dtype=torch.int32, device=device)
+        # the K newest tokens of the sequence (global positions len-K .. len-1) that fall into this shard
+        lo = max(0, int(plan["lens"][b]) - K - off)
+        if lo < n:
+            new_k.append(k[lo:].bfloat16())
+            new_v.append(v[lo:].bfloat16())
+            new_slots.append(slots[lo:])
+    q = torch.randn(B, K, hq, D, generator=g, device=device).bfloat16()
+    sl = torch.tensor(plan["lens"], dtype=torch.int32, device=device)
+    po = torch.full((B,), off, dtype=torch.int32, device=device)
     caches = [(kc, ks, vc, vs)]
-    for _ in range(copies - 1):   # identical bytes at other addresses, so consecutive steps never hit L2
+    for _ in range(copies - 1):   # identical bytes at other addresses, so consecutive calls never hit L2
         caches.append(tuple(t.clone() for t in (kc, ks, vc, vs)))
-    return dict(q=q, bt=bt, sl=sl, caches=caches)
+    cat = lambda xs: torch.cat(xs).contiguous() if xs else None
+    return dict(q=q, bt=bt.contiguous(), sl=sl, po=po, caches=caches, new_k=cat(new_k), new_v=cat(new_v), new_slots=cat(new_slots))
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
-def cpu_sample(cfg, K, case_np, steps, warmup):
-    """Times the CPU oracle on sequence 0 (all KV heads, full context): 1/B of a layer call per step."""
+def cpu_sample(case_np, steps, warmup):
+    """Times the CPU oracle on sequence 0 (all KV heads, full context) of one layer."""
     from oracle import uq_oracle as O
     q, kc, ks, vc, vs, bt, sl = case_np
     ts = []
@@ -143,8 +201,8 @@ def cpu_sample(cfg, K, case_np, steps, warmup):
 
 
 def case_to_numpy(case, cache=0):
-    kc, ks, vc, vs = (t.cpu().numpy() for t in case["caches"][cache])
     import torch
+    kc, ks, vc, vs = (t.cpu().numpy() for t in case["caches"][cache])
     q = case["q"].view(torch.int16).cpu().numpy().view(np.uint16)
     return q, kc, ks, vc, vs, case["bt"].cpu().numpy(), case["sl"].cpu().numpy()
 
@@ -155,9 +213,11 @@ def run_reference_arm(args, cfg):
         return
     from oracle import uq_oracle as O
     rng = np.random.default_rng(1001)
-    B, ctx, HQ, HKV, D, PAGE = (cfg[k] for k in ("B", "ctx", "HQ", "HKV", "D", "PAGE"))
+    B, HQ, HKV, D, PAGE = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE"))
+    lens = seq_lengths(cfg)
+    ctx = int(lens[0])
     K = args.kq
-    npg = ctx // PAGE
+    npg = -(-ctx // PAGE)
     chan = np.exp(0.5 * rng.standard_normal((1, HKV, 1, D))).astype(np.float32)
     k = rng.standard_normal((npg, HKV, PAGE, D)).astype(np.float32) * chan
     v = rng.standard_normal((npg, HKV, PAGE, D)).astype(np.float32)
@@ -186,18 +246,20 @@ def run_reference_arm(args, cfg):
         O.reference(q2, kc2, ks2, vc2, vs2, bt, sl)
         if i >= args.warmup:
             ts.append(time.perf_counter() - t0)
-    sample_frac = frac_heads / (HKV * B)                 # of one layer call
-    t_call = float(np.mean(ts)) / sample_frac            # seconds per full layer call, scaled linearly
-    by = kv_bytes(cfg, [ctx] * B)
-    val = by / t_call / 1e12
-    sample = f"1 of {B} sequences x {frac_heads} of {HKV} kv heads, full context, K={K}; scaled linearly to a layer call"
+    # fraction of one step the sample covers: its tokens x heads over all sequences, heads and layers
+    sample_frac = ctx * frac_heads / (float(lens.sum()) * HKV * cfg["layers"])
+    t_step = float(np.mean(ts)) / sample_frac            # seconds per full step, scaled linearly
+    by = kv_bytes(cfg, lens) * cfg["layers"]
+    val = by / t_step / 1e12
+    sample = (f"sequence 0 ({ctx} tokens) of {B} x {frac_heads} of {HKV} kv heads, one layer of {cfg['layers']}, K={K}; "
+              "scaled linearly by tokens x heads x layers to a step" + ("; the append leg is not in the sample" if cfg["append"] else ""))
     line = {"impl": "reference", "metric": "kv_read_throughput", "value": val, "unit": "TB/s", "n_gpus": args.gpus, "steps": steps,
-            "warmup": args.warmup, "ms_per_step": t_call * 1e3, "us_per_layer_call": t_call * 1e6, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "warmup": args.warmup, "ms_per_step": t_step * 1e3, "us_per_layer_call": t_step * 1e6 / cfg["layers"], "higher_is_better": True,
+            "scaling": "weak" if cfg["shard"] == "replicas" else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": cfg["name"] + f" K={K}", "kq": K},
             "cpu_baseline": {"value": val, "unit": "TB/s", "cores": O.max_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "tokens_verified_per_s": B * K / t_call}
+            "tokens_verified_per_s": B * K / t_step}
     print(json.dumps(line))
 
 
@@ -217,19 +279,32 @@ def run_ours(args, cfg):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     K = args.kq
-    B, ctx, HQ, HKV, D, PAGE = (cfg[k] for k in ("B", "ctx", "HQ", "HKV", "D", "PAGE"))
-    case = build_case(cfg, K, 1001 + rank, dev, copies=2)
-    q, bt, sl, caches = case["q"], case["bt"], case["sl"], case["caches"]
+    B, HQ, HKV, D, PAGE, layers = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE", "layers"))
+    plan = shard_plan(cfg, rank, world)
+    mode, hkv, hq = plan["mode"], plan["hkv"], plan["hq"]
+    # one cache per layer; a single-layer configuration alternates two copies so that no call finds its cache in L2
+    case = build_case(cfg, plan, K, 1001 + rank, dev, copies=layers if layers > 1 else 2)
+    q, bt, sl, po, caches = case["q"], case["bt"], case["sl"], case["po"], case["caches"]
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    nsplit = uq_cuda.auto_nsplit(B, HKV, bt.shape[1], sms, K, HQ // HKV)
-    ws = torch.empty(uq_cuda.workspace_floats(B, K, HQ, HKV, D, nsplit), dtype=torch.float32, device=dev)
+    nsplit = uq_cuda.auto_nsplit(B, hkv, bt.shape[1], sms, K, hq // hkv)
+    ws = torch.empty(uq_cuda.workspace_floats(B, K, hq, hkv, D, nsplit), dtype=torch.float32, device=dev)
     out = torch.empty_like(q)
-    by = kv_bytes(cfg, [ctx] * B)
+    by_local = local_kv_bytes(cfg, plan)                       # one layer, this rank
+    by_step = kv_bytes(cfg, plan["lens"]) * layers * (world if mode == "replicas" else 1)   # one step, all ranks
+    cache_bytes = sum(t.numel() for t in caches[0])
     lib = uq_cuda.lib()
 
-    def step(i, qq=q, oo=out):
-        kc, ks, vc, vs = caches[i % len(caches)]
-        return uq_cuda.uq_decode_cuda(qq, kc, ks, vc, vs, bt, sl, nsplit=nsplit, workspace=ws, out=oo)
+    def step(i, qq=q, btt=bt, sll=sl, oo=out):
+        o = None
+        for layer in range(layers):
+            kc, ks, vc, vs = caches[(i * layers + layer) % len(caches)]
+            if cfg["append"] and case["new_k"] is not None:
+                uq_cuda.append_kv(kc, ks, vc, vs, case["new_k"], case["new_v"], case["new_slots"])
+            if mode == "context":
+                o = uq_cuda.uq_decode_context_split(qq, kc, ks, vc, vs, btt, sll, po, nsplit=nsplit)
+            else:
+                o = uq_cuda.uq_decode_cuda(qq, kc, ks, vc, vs, btt, sll, nsplit=nsplit, workspace=ws, out=oo)
+        return o
 
     def barrier():
         if world > 1:
@@ -246,7 +321,7 @@ def run_ours(args, cfg):
     for i in range(max(3, args.warmup)):
         step(i)
     barrier()
-    # ---- device-resident timing: exactly `steps` layer calls
+    # ---- device-resident timing: exactly `steps` steps
     n0 = uq_cuda.launch_count()
     with ClockSampler(local) as clk:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -258,29 +333,36 @@ def run_ours(args, cfg):
         barrier()
         ms_total = e0.elapsed_time(e1)
         launches = uq_cuda.launch_count() - n0
-        # ---- dominant kernel alone: events recorded by the library around the verify kernel of each call
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        # ---- dominant kernel alone: events recorded by the library around the verify kernel (of the step's last layer)
+        nk = min(args.steps, 50)
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
         for i, (a, b) in enumerate(pairs):
             a.record()
             b.record()      # a torch event gets its handle at its first record
             lib.uqb_debug_events(a.cuda_event, b.cuda_event)
             step(i)
         lib.uqb_debug_events(None, None)
-        torch.cuda.synchronize()
+        barrier()
         kern_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
-        # ---- end to end through the public API with host buffers
-        hq = q.cpu().pin_memory()
-        hbt, hsl = bt.cpu().pin_memory(), sl.cpu().pin_memory()
-        hout = torch.empty_like(hq).pin_memory()
+        # ---- end to end through the public API with host buffers: per step the queries, page table and lengths
+        # (and the new tokens of the append leg) come from pinned host memory and the step's output goes back
+        hq_, hbt, hsl = q.cpu().pin_memory(), bt.cpu().pin_memory(), sl.cpu().pin_memory()
+        hout = torch.empty_like(hq_).pin_memory()
         dq, dbt, dsl = torch.empty_like(q), torch.empty_like(bt), torch.empty_like(sl)
+        h2d = int(hq_.numel() * 2 + hbt.numel() * 4 + hsl.numel() * 4)
+        hnew = None
+        if cfg["append"] and case["new_k"] is not None:
+            hnew = (case["new_k"].cpu().pin_memory(), case["new_v"].cpu().pin_memory())
+            h2d += int(2 * hnew[0].numel() * 2)
 
         def e2e_step(i):
-            dq.copy_(hq, non_blocking=True)
+            dq.copy_(hq_, non_blocking=True)
             dbt.copy_(hbt, non_blocking=True)
             dsl.copy_(hsl, non_blocking=True)
-            kc, ks, vc, vs = caches[i % len(caches)]
-            o = uq_cuda.uq_decode_cuda(dq, kc, ks, vc, vs, dbt, dsl, nsplit=nsplit, workspace=ws, out=out)
-            hout.copy_(o, non_blocking=True)
+            if hnew is not None:
+                case["new_k"].copy_(hnew[0], non_blocking=True)
+                case["new_v"].copy_(hnew[1], non_blocking=True)
+            hout.copy_(step(i, dq, dbt, dsl, out), non_blocking=True)
 
         for i in range(3):
             e2e_step(i)
@@ -294,32 +376,39 @@ def run_ours(args, cfg):
         e2e_ms = f0.elapsed_time(f1)
     ms_step = max_over_ranks(ms_total / args.steps)
     e2e_step_ms = max_over_ranks(e2e_ms / args.steps)
+    kern_ms = max_over_ranks(kern_ms)
     status = uq_cuda.last_status()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     peak, peak_kind = peaks()
-    value = world * by / (ms_step * 1e-3) / 1e12
-    achieved = by / (kern_ms * 1e-3) / 1e9
+    value = by_step / (ms_step * 1e-3) / 1e12
+    achieved = by_local / (kern_ms * 1e-3) / 1e9
+    sharding = {"single": "single GPU", "replicas": "every rank runs the whole call on kv heads of its own, no collective",
+                "heads": f"kv heads divided across ranks ({hkv} per rank), no collective",
+                "context": "context pages divided across ranks; partials all-gathered over NCCL and merged by the log-sum-exp kernel inside the step"}[mode]
+    l2 = (f"{len(caches)} cache copies alternate; each {cache_bytes / 1e6:.0f} MB copy exceeds the 126 MB L2" if cache_bytes > 126e6 else
+          f"{len(caches)} caches of {cache_bytes / 1e6:.0f} MB are read in turn ({len(caches) * cache_bytes / 1e6:.0f} MB between two reads of the same bytes; L2 is 126 MB)")
     line = {"metric": "kv_read_throughput", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_step, "us_per_layer_call": ms_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "l2": f"two cache copies alternate; each {by / 1e6:.0f} MB copy exceeds the 126 MB L2" if by > 126e6 else "two cache copies alternate (each smaller than L2: not a valid bench size)",
-                       "sharding": "kv heads partitioned across ranks, no collective" if world > 1 else "single GPU",
+            "ms_per_step": ms_step, "us_per_layer_call": ms_step * 1e3 / layers, "higher_is_better": True,
+            "scaling": "weak" if cfg["shard"] == "replicas" else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "layers": layers, "l2": l2, "sharding": sharding,
                        "kernel_path": {1: "cuda-core", 2: "tcgen05"}.get(uq_cuda.last_path(), "?")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "peak_kind": peak_kind, "kernel_us": kern_ms * 1e3, "algorithmic_bytes": by},
-            "e2e": {"value": world * by / (e2e_step_ms * 1e-3) / 1e12, "unit": "TB/s", "us_per_layer_call": e2e_step_ms * 1e3,
-                    "h2d_bytes_per_step": int(hq.numel() * 2 + hbt.numel() * 4 + hsl.numel() * 4), "d2h_bytes_per_step": int(hout.numel() * 2)},
-            "gpu_launches": int(launches), "tokens_verified_per_s": world * B * K / (ms_step * 1e-3),
+                         "peak_kind": peak_kind, "kernel_us": kern_ms * 1e3, "algorithmic_bytes": by_local},
+            "e2e": {"value": by_step / (e2e_step_ms * 1e-3) / 1e12, "unit": "TB/s", "us_per_layer_call": e2e_step_ms * 1e3 / layers,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(hout.numel() * 2)},
+            "gpu_launches": int(launches), "tokens_verified_per_s": B * K * (world if mode == "replicas" else 1) / (ms_step * 1e-3),
             "clocks": clk.summary(), "device_status": list(status)}
     # ---- CPU baseline beside it (N = 1 only), and a parity check of sequence 0 for free
     if world == 1 and not args.no_cpu:
-        t_seq, ref0, cores = cpu_sample(cfg, K, case_to_numpy(case), steps=2, warmup=1)
-        t_call = t_seq * B
-        line["cpu_baseline"] = {"value": by / t_call / 1e12, "unit": "TB/s", "cores": cores, "kind": "port", "us_per_layer_call": t_call * 1e6,
-                                "sample": f"sequence 0 of {B} (all kv heads, full context, K={K}), 2 timed runs; scaled x{B} to a layer call"}
+        t_seq, ref0, cores = cpu_sample(case_to_numpy(case), steps=2, warmup=1)
+        scale = float(plan["lens"].sum()) / float(plan["lens"][0]) * layers
+        t_step = t_seq * scale
+        line["cpu_baseline"] = {"value": by_step / t_step / 1e12, "unit": "TB/s", "cores": cores, "kind": "port", "us_per_layer_call": t_step * 1e6 / layers,
+                                "sample": f"sequence 0 ({int(plan['lens'][0])} tokens) of {B}, all kv heads, one layer of {layers}, K={K}, 2 timed runs; "
+                                          f"scaled x{scale:.2f} (tokens x layers) to a step"}
         got = step(0).float().cpu().numpy()[:1]
         d = np.abs(got - ref0)
         line["parity"] = {"max_abs_err": float(d.max()), "mean_abs_err": float(d.mean()), "max_abs_ref": float(np.abs(ref0).max()),
@@ -332,18 +421,20 @@ def run_ours(args, cfg):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=0, help="timed steps (default 200; 10 for the 32-layer configuration)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kq", type=int, default=8, help="draft queries per sequence (K)")
-    ap.add_argument("--config", type=int, default=1)
+    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS))
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (profiler captures use a shorter one; the JSON says so)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
+    if args.steps <= 0:
+        args.steps = 200 if cfg["layers"] == 1 else 10
     if args.ctx:
         cfg["ctx"] = args.ctx
-        cfg["name"] = cfg["name"].replace("ctx32768", f"ctx{args.ctx}")
+        cfg["name"] += f" (context overridden to {args.ctx})"
     if args.impl == "reference":
         run_reference_arm(args, cfg)
     else:

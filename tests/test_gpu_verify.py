@@ -104,6 +104,26 @@ def test_scale_extremes():
     check_close(out.float().cpu().numpy() / mx, ref / mx, "scale extremes")
 
 
+def test_late_outliers_take_the_second_pass():
+    """Keys whose scores (and V scales) dwarf those of a segment's first tile arrive late in every sequence: the quick path
+    marks the segment and the careful pass redoes it; outputs follow the oracle on the same bytes."""
+    c = [x for x in CASES if x.name == "ref_cuda_main_K8"][0]
+    ks, vs = c.ks.copy(), c.vs.copy()
+    for b in range(c.B):
+        npg = -(-int(c.sl[b]) // c.PAGE)
+        first, late = c.bt[b, : max(1, 128 // c.PAGE)], c.bt[b, npg // 2]
+        ks[first] = (ks[first].astype(np.int32) - 10).clip(0, 255).astype(np.uint8)
+        ks[late] = (ks[late].astype(np.int32) + 3).clip(0, 255).astype(np.uint8)
+        vs[late] = (vs[late].astype(np.int32) + 5).clip(0, 255).astype(np.uint8)
+    ref = O.reference(c.q, c.kc, ks, c.vc, vs, c.bt, c.sl, c.sm_scale)
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    for nsplit in (1, 4):
+        out = uq_cuda.uq_decode_cuda(q, dev(c.kc), dev(ks), dev(c.vc), dev(vs), dev(c.bt), dev(c.sl), nsplit=nsplit)
+        assert uq_cuda.last_status() == (0, 0, 0, 0)
+        mx = np.abs(ref).max()
+        check_close(out.float().cpu().numpy() / mx, ref / mx, f"late outliers nsplit={nsplit}")
+
+
 def test_unserved_shapes_answer_invalid_value_before_any_work():
     c = [x for x in CASES if x.name == "ref_cuda_main_K1"][0]
     q = dev(c.q.view(np.int16), torch.bfloat16)
