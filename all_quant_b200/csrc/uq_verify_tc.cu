@@ -71,7 +71,7 @@ __device__ unsigned long long g_tc_prof[5][8];
 #endif
 
 #ifndef UQ_ABL
-#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no per-tile rendezvous
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 32 no V tile stores, 64 no K operand stores
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
@@ -105,6 +105,13 @@ UQ_DEV unsigned long long now_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+// One lane of the (converged) warp: the compiler knows the guarded region runs in a single thread and can keep its
+// addresses and descriptors on the uniform datapath.
+UQ_DEV bool elect_one() {
+  uint32_t r;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(r));
+  return r != 0;
 }
 UQ_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 UQ_DEV void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -489,78 +496,68 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     }
     UQ_PROF_FLUSH(0, lane == 0)
   } else if (warp == kWarpMma) {
-    // ================================================================= MMA issue, S^T = K.Q^T (one thread).  The two contractions are
-    // issued by two warps: an instruction occupies its issuing thread for as long as the tensor pipe takes to accept it
-    // (about 70 cycles), so one thread doing both spends its waits and commits on the pipe's critical path.
+    // ================================================================= MMA issue: one thread issues both contractions.
+    // A tcgen05.mma with N <= 64 takes the tensor pipe about 48 cycles (its operands come from shared memory at 128 bytes a
+    // cycle) when one thread issues a straight run of them; two threads issuing at once got 63 cycles per instruction between
+    // them in a probe and 100-170 in this kernel.  The order is P.V of tile i, then Q.K of tile i + LA (LA = ring depth - 1):
+    // S^T of the next tiles is complete before the softmax asks for it.  Everything is issued in program order and a commit
+    // covers all earlier instructions of the thread, so S^T(c) complete implies P.V(c - ring depth) complete: the softmax may
+    // overwrite that P^T slot without a wait of its own.
     constexpr uint32_t idesc_qk = instr_desc(128, NT, 0, 0, 0, 0);   // A = K, B = Q, both fp16 (mixed 16-bit formats are not legal)
+    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
+    constexpr int LA = kSB - 1;
     UQ_PROF_DECL
     // descriptors differ between instructions only in the start-address field (bits 0-13, units of 16 bytes)
     const uint64_t q_desc = smem_desc(sm_a + C::oQ, 16, 1024);
-    while (ok && wk.next(sg)) {
-      if (!take()) continue;
-      if (lane == 0) {
-        ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
-        for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
-          const int buf = cnt % kSB, ph = cnt / kSB;
-          ok = wait(bar(bKfull + buf), ph & 1, 24 + buf, cnt UQ_PROF_SITE(2));
-          // ring slot free: the softmax wrote the slot's previous P^T (so it has consumed the slot's S^T) and the P.V that read
-          // that P^T is done (so the softmax may overwrite it without a wait of its own)
-          if (ok && cnt >= kSB) ok = wait(bar(bPfull + buf), (ph - 1) & 1, 26 + buf, cnt UQ_PROF_SITE(3));
-          if (ok && cnt >= kSB) ok = wait(bar(bPdone + buf), (ph - 1) & 1, 28 + buf, cnt UQ_PROF_SITE(3));
-          if (!ok) break;
-          tc_fence_after();
-          UQ_TRACE(5, cnt)
-          UQ_PROF_T0
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ks++)
-            mma_ts(tmem + C::cS + buf * NT, tmem + C::cK + buf * C::kKCols + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
-          tc_commit(bar(bSfull + buf));
-          UQ_TRACE(6, cnt)
-          UQ_PROF_T1(6)
-        }
-      } else {
-        cnt += sg.t1 - sg.t0;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      seg_i++;
-    }
-    UQ_PROF_FLUSH(1, lane == 0)
-  } else if (warp == kWarpMma + 1) {
-    // ================================================================= MMA issue, O^T += V^T.P^T (one thread)
-    constexpr uint32_t idesc_pv = instr_desc(128, NT, 1, 1, 0, 0);   // A = V, B = P, both fp16
     // A = V^T: M = 128 channels = two 64-channel halves (leading-dimension offset = one half).  head_dim 64 has one half only:
     // offset 0 makes the upper 64 accumulator lanes a copy of the lower ones, which the epilogue ignores.
     const uint64_t v_desc = smem_desc(sm_a + C::oV, D == 64 ? 0 : C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
     while (ok && wk.next(sg)) {
       if (!take()) continue;
-      if (lane == 0) {
-        if (seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
-        const int c0 = cnt;
-        for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
-          const int buf = cnt % kSB, vb = cnt % kVB;
-          ok = wait(bar(bPfull + buf), (cnt / kSB) & 1, 20 + buf, cnt, nullptr);
-          if (ok) ok = wait(bar(bVfull + vb), (cnt / kVB) & 1, 22 + vb, cnt, nullptr);
+      const int n = sg.t1 - sg.t0, c0 = cnt;
+      if (elect_one()) {
+        auto issue_qk = [&](int c) -> bool {
+          const int buf = c % kSB;
+          if (!wait(bar(bKfull + buf), (c / kSB) & 1, 24 + buf, c UQ_PROF_SITE(2))) return false;
+          tc_fence_after();
+          UQ_TRACE(5, c)
+          const uint32_t d = tmem + C::cS + buf * NT, a = tmem + C::cK + buf * C::kKCols;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ks++)
+            mma_ts(d, a + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
+          tc_commit(bar(bSfull + buf));
+          UQ_TRACE(6, c)
+          return true;
+        };
+        ok = wait(bar(bQfull), seg_i & 1, 30, seg_i UQ_PROF_SITE(0));
+        if (ok && seg_i > 0) ok = wait(bar(bEpi), (seg_i - 1) & 1, 31, seg_i, nullptr);   // the previous segment's O^T has been read
+        for (int i = 0; ok && i < LA && i < n; i++) ok = issue_qk(c0 + i);
+        for (int i = 0; ok && i < n; i++) {
+          const int c = c0 + i, buf = c % kSB, vb = c % kVB;
+          ok = wait(bar(bPfull + buf), (c / kSB) & 1, 20 + buf, c UQ_PROF_SITE(3));
+          if (ok) ok = wait(bar(bVfull + vb), (c / kVB) & 1, 22 + vb, c UQ_PROF_SITE(4));
           if (!ok) break;
           tc_fence_after();
-          UQ_TRACE(7, cnt)
+          UQ_TRACE(7, c)
           const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
           for (int db = 0; db < C::kDB; db++) {
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; kk++)
-              mma_ss(tmem + C::cO + db * NT, va + (uint64_t)((db * 2 * C::kVHalf + kk * 2048) >> 4), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (cnt == c0 && kk == 0) ? 0u : 1u);
+              mma_ss(tmem + C::cO + db * NT, va + (uint64_t)((db * 2 * C::kVHalf + kk * 2048) >> 4), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i == 0 && kk == 0) ? 0u : 1u);
           }
-          tc_commit(bar(bPdone + buf));
+          tc_commit(bar(bPdone + buf));   // the careful path waits for it before it rescales O^T
           tc_commit(bar(bVdone + vb));
-          UQ_TRACE(8, cnt)
+          UQ_TRACE(8, c)
+          if (i + LA < n) ok = issue_qk(c + LA);
         }
         if (ok) tc_commit(bar(bOdone));
-      } else {
-        cnt += sg.t1 - sg.t0;
       }
+      cnt = c0 + n;
       ok = __all_sync(0xffffffffu, ok);
       seg_i++;
     }
+    UQ_PROF_FLUSH(1, lane == 0)
   } else if (warp >= kWarpK && warp < kWarpK + 4) {
     // ================================================================= K decode -> TMEM
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
@@ -596,7 +593,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             const uint32_t m = pow2_f16x2((int)((uint32_t)(sc >> (8 * (g0 + g))) & 0xFFu) - (int)kref);
             uint32_t o[16];
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
-            tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
+            if (!(UQ_ABL & 64) || cnt == 0) tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
           }
         }
         UQ_PROF_T1(2)
@@ -648,7 +645,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             uint8_t* vrow = vt + (gg >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
             for (int w = 0; w < 4; w++)
-              *reinterpret_cast<uint4*>(vrow + ((((4 * gg + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
+              if (!(UQ_ABL & 32) || cnt == 0 || o[4 * w] == 0x12345678u)
+                *reinterpret_cast<uint4*>(vrow + ((((4 * gg + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
           }
         }
         UQ_PROF_T1(2)
