@@ -35,6 +35,8 @@
 // refills the pipeline (about 30 000 cycles: epilogue, query tile conversion, first-tile reference move).
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "uq_common.cuh"
 
 namespace tc {
@@ -70,6 +72,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_TB(n)
 #endif
 
+#ifndef UQ_NSG4_AT
+#define UQ_NSG4_AT 32
+#endif
 #ifndef UQ_ABL
 #define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 32 no V tile stores, 64 no K operand stores
 #endif
@@ -77,7 +82,7 @@ constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
 // producer, Q.K issue, P.V issue, one idle warp.  The roles are latency bound (one warp of a role per SM sub-partition issues
 // about once per 10 cycles), so the softmax, the longest role at 64 rows, is spread over four warpgroups.
-__host__ __device__ constexpr int softmax_groups(int NT) { return NT >= 32 ? 4 : 2; }
+__host__ __device__ constexpr int softmax_groups(int NT) { return NT >= UQ_NSG4_AT ? 4 : 2; }
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
 __host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : 4; }   // raw code/scale tiles in flight (TMA)
@@ -772,26 +777,36 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk];
         const int vref = (int)(rf >> 8);
         const float ck = csc0 * uq_scale_f32(rf & 0xFFu);
-        const int key = t * kKeys + kk;
-        const bool live = key < n_loc;
-        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 > n_glob - p.K;   // same for every thread
+        // only a tile that reaches the end of the sequence or the draft positions needs masks (same answer in every thread)
+        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 > n_glob - p.K;
+        bool live = true;
         int rmin = 0;   // rows r >= rmin see this key (causal limit among the drafts); none if past the end
-        if (!live) rmin = NT;
-        else { const int jmin = off + key - (n_glob - p.K); if (jmin > 0) rmin = jmin * G; }
+        if (need_mask) {
+          const int key = t * kKeys + kk;
+          live = key < n_loc;
+          if (!live) rmin = NT;
+          else { const int jmin = off + key - (n_glob - p.K); if (jmin > 0) rmin = jmin * G; }
+        }
         uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
         float pv[HW];
-        // scores -> probabilities against the references `mrow`, in place; returns the largest exponent seen
-        auto probabilities = [&](const float* mrow) -> float {
+        // scores -> probabilities against the references `mrow`, in place.  The full form applies the masks and returns the
+        // largest exponent seen; the lean form (no masks needed, nobody asks for the maximum) is the common tile's.
+        auto probabilities = [&](const float* mrow, auto full_c) -> float {
+          constexpr bool kFull = decltype(full_c)::value;
           float xm = kNegBig;
 #pragma unroll
           for (int i = 0; i < HW; i++) {
             float xv = fmaf(pv[i], ck, (UQ_ABL & 4) ? -1.0f : -mrow[r0 + i]);
-            if (need_mask) xv = (r0 + i >= rmin) ? xv : -INFINITY;
-            xm = fmaxf(xm, xv);
+            if (kFull) {
+              xv = (r0 + i >= rmin) ? xv : -INFINITY;
+              xm = fmaxf(xm, xv);
+            }
             pv[i] = (UQ_ABL & 1) ? xv * 0.001f : fast_exp2(xv);
           }
           return xm;
         };
+        constexpr std::true_type full_c{};
+        constexpr std::false_type lean_c{};
         // P^T row of this key: probabilities times the key's V reference relative to the segment's, fp16
         auto write_p = [&](int rbyte) {
           const float vf = live ? pow2_f32(vref - rbyte) : 0.f;   // past the end the bytes are arbitrary: keep 0 * vf finite
@@ -809,14 +824,19 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (st == 0) { UQ_TRACE(10, cnt) }
         UQ_PROF_TB(2)
         const int rbyte = (int)wr[4 + mcur];
-        const float xm = probabilities(mref + mcur * NT);
+        const bool agree = careful || cnt == c0;   // the first tile of a segment sets the references; later tiles only on the careful path
+        const bool lean = !agree && !need_mask;
+        float xm = kNegBig;
+        if (lean) probabilities(mref + mcur * NT, lean_c);
+        else xm = probabilities(mref + mcur * NT, full_c);
         UQ_PROF_TB(3)
         if (!(UQ_ABL & 2) || cnt == c0) write_p(rbyte);
         if (st == 0) { UQ_TRACE(11, cnt) }
         UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
-        const bool grew = __any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte));
-        const bool agree = careful || cnt == c0;   // the first tile of a segment sets the references; later tiles only on the careful path
+        // (the lean tiles of the quick path do not look: an overflow there leaves infinities or NaNs in O^T, which the
+        // segment's epilogue finds)
+        const bool grew = !lean && __any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte));
         const int vslot = nvote & 1;
         if (!agree) {
           // quick path: what this tile wrote may have overflowed; mark the segment for the second pass and carry on
@@ -878,7 +898,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
           load_scores(s_addr, pv);
-          probabilities(mref + mcur * NT);
+          probabilities(mref + mcur * NT, full_c);
           write_p((int)wr[4 + mcur]);
         }
         UQ_PROF_TA2
@@ -910,6 +930,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         float* ml = p.ml + slot * x.BM;
         const float* mr = mref + mcur * NT;
         const float osc = pow2_f32((int)wr[4 + mcur] - 127);   // O^T was accumulated relative to the segment's V reference
+        bool bad = false;   // an infinity or a NaN in the sums: a probability or a V value overflowed fp16 somewhere in the segment
 #pragma unroll
         for (int db = 0; db < C::kDB; db++) {
           float ov[HW];
@@ -920,11 +941,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
               const int r = r0 + i;
               if (r < rows) {
                 const float lr = lsum[r];
+                bad |= !(fabsf(ov[i]) <= 3.0e38f) || !(lr <= 3.0e38f);
                 mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * (osc / lr) : 0.f;
               }
             }
           }
         }
+        // quick path: the segment's result is garbage then; the second pass computes it again on the careful path
+        if (!careful && __any_sync(0xffffffffu, bad) && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
         if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       }
       tc_fence_before();
