@@ -76,7 +76,7 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_NSG4_AT 32
 #endif
 #ifndef UQ_ABL
-#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 32 no V tile stores, 64 no K operand stores
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
@@ -85,7 +85,8 @@ constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 __host__ __device__ constexpr int softmax_groups(int NT) { return NT >= UQ_NSG4_AT ? 4 : 2; }
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
-__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : 4; }   // raw code/scale tiles in flight (TMA)
+__host__ __device__ constexpr bool block_scaled(int D) { return D == 128; }          // Q.K straight from the e2m1 codes and scale bytes (see Cfg::kBS)
+__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : (D == 128 ? 3 : 4); }   // raw code/scale tiles in flight (TMA)
 __host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : 3; }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
 __host__ __device__ constexpr int ring_vb(int D) { return D == 256 ? 1 : 2; }      // decoded V tiles (shared memory)
 constexpr float kRescaleAt = 12.0f;  // a score this far (log2) above the row's reference maximum does not fit the fp16 probability tile
@@ -147,6 +148,17 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, 
 UQ_DEV void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// block-scaled form (kind::mxf8f6f4, UE8M0 scales, one per 32 elements of K): the scale bytes sit in TMEM, lane l of every
+// 32-lane quarter, column j, byte id = row 32 j + l's scale for the instruction whose descriptor names byte `id`
+UQ_DEV void mma_bs(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %6, 0;\n tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate) : "memory");
+}
+// its instruction descriptor: B scale byte id [4,6), A format [7,10) and B format [10,13) (0 = e4m3, 5 = e2m1), both K-major,
+// N >> 3 at [17,23), UE8M0 scales (bit 23), M >> 4 at [24,29), A scale byte id [29,31)
+__host__ __device__ constexpr uint32_t instr_desc_bs(int M, int N, int a_fmt, int b_fmt, int a_sf, int b_sf) {
+  return ((uint32_t)b_sf << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) | ((uint32_t)(M >> 4) << 24) | ((uint32_t)a_sf << 29);
+}
 UQ_DEV void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
@@ -164,6 +176,9 @@ UQ_DEV void tmem_st8(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
+UQ_DEV void tmem_st4(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
 UQ_DEV void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
@@ -178,6 +193,18 @@ UQ_DEV uint32_t pack_f16x2(float lo, float hi) {
   uint32_t d;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
   return d;
+}
+// two floats -> e4m3 pair (low byte = lo), saturating; and back
+UQ_DEV uint32_t pack_e4m3x2(float lo, float hi) {
+  unsigned short d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+UQ_DEV void unpack_e4m3x2(uint32_t v, float& lo, float& hi) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((unsigned short)v));
+  lo = __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
+  hi = __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
 }
 UQ_DEV uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t d;
@@ -253,9 +280,19 @@ struct Cfg {
   static constexpr int kGroups = D / 32;                 // scale bytes per key
   static constexpr int kChunks = kCodeRow / 16;          // 16-byte chunks per code row = scale groups
   static constexpr int kRowsPer128 = 128 / kCodeRow;     // code rows per 128 bytes: the TMA swizzle (32 / 64 / 128 B) XORs the chunk index with (row / this)
+  // head_dim 128: S^T comes from a block-scaled contraction (kind::mxf8f6f4, one UE8M0 scale per 32 channels: the cache's own
+  // format), so the K codes are never decoded.  The TMA unpacks them into the layout that instruction reads (16 codes = 8
+  // bytes, then 8 bytes of padding: 128 bytes per key), the scale bytes go to TMEM as they are, and Q is two e4m3 tiles
+  // (leading bits + remainder, each with a scale per row and 32 channels).
+  static constexpr bool kBS = block_scaled(D);
   static constexpr int kRawCodes = kKeys * kCodeRow;
   static constexpr int kRawScales = kKeys * kGroups;
-  static constexpr int kRawStage = 2 * (kRawCodes + kRawScales);
+  static constexpr int kRawK = kBS ? kKeys * D : kRawCodes;   // K codes of a tile as they sit in shared memory
+  static constexpr int kOffVC = kRawK;                        // offsets within a raw stage: V codes, K scales, V scales
+  static constexpr int kOffKS = kOffVC + kRawCodes;
+  static constexpr int kOffVS = kOffKS + kRawScales;
+  static constexpr int kRawStage = kOffVS + kRawScales;
+  static_assert(!kBS || kRawStage % 1024 == 0, "the unpacked K tile is a swizzled MMA operand");
   static constexpr int kHalves = D / 64;                 // 64-channel (128-byte) column blocks of the fp16 tiles
   static constexpr int kVHalf = kKeys * 128;             // fp16 [key][64 channels]
   static constexpr int kVTile = kHalves * kVHalf;
@@ -281,7 +318,8 @@ struct Cfg {
   static constexpr int oFac = oLsum + NT * 4;
   static constexpr int oFacO = oFac + NT * 4;            // per-row factor for O^T (row factor x V-reference factor)
   static constexpr int oWr = oFacO + NT * 4;             // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
-  static constexpr int oRef = oWr + 32;                  // [8][128] uint16: K reference byte | V reference byte << 8 of the last eight tiles (a slot is rewritten
+  static constexpr int oSfb = oWr + 32;                  // [2][NT][4] scale bytes of the two Q tiles (block-scaled path)
+  static constexpr int oRef = oSfb + 2 * NT * 4;                  // [8][128] uint16: K reference byte | V reference byte << 8 of the last eight tiles (a slot is rewritten
                                                          // only after its readers, the softmax threads of a tile several ring turns back, are done)
   static constexpr int oPrefix = oRef + 8 * kKeys * 2;
   static constexpr int kMaxB = 1024;
@@ -289,9 +327,10 @@ struct Cfg {
   static constexpr int kSmem = oRedo + (kRedoWords + 1) * 4;
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // TMEM columns
-  static constexpr int kKCols = D / 2;                   // fp16 A operand of S^T: two channels per 32-bit column
+  static constexpr int kKCols = kBS ? 4 : D / 2;         // fp16 A operand of S^T: two channels per 32-bit column; block-scaled: the keys' scale bytes
   static constexpr int cK = 0;                           // kSB x kKCols
-  static constexpr int cS = kSB * kKCols;                // kSB x NT: fp32 S^T
+  static constexpr int cSFB = kSB * kKCols;              // block-scaled: scale bytes of the two Q tiles, 4 columns each
+  static constexpr int cS = kBS ? 32 : kSB * kKCols;     // kSB x NT: fp32 S^T
   static constexpr int cO = cS + kSB * NT;               // kDB x NT: fp32 O^T
   static_assert(cO + kDB * NT <= 512, "TMEM budget");
 };
@@ -413,7 +452,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 8); }
+    // a raw stage is free again after the four K and four V warps have read it (block-scaled: and after the Q.K instructions have)
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), C::kBS ? 9 : 8); }
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
@@ -492,10 +532,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (lane < vp) {
           const int row0 = (pid * p.HKV + sg.hk) * p.PAGE;   // first cache row of this (page, head)
           const uint32_t fb = bar_raw_full(stage);
-          tma_load_2d(dst + lane * page_bytes_codes, &map_kc, 0, row0, fb);
-          tma_load_2d(dst + C::kRawCodes + lane * page_bytes_codes, &map_vc, 0, row0, fb);
-          bulk_load(dst + 2 * C::kRawCodes + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
-          bulk_load(dst + 2 * C::kRawCodes + C::kRawScales + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
+          // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
+          tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
+          tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
+          bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
+          bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
         }
       }
     }
@@ -527,10 +568,23 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           tc_fence_after();
           UQ_TRACE(5, c)
           const uint32_t d = tmem + C::cS + buf * NT, a = tmem + C::cK + buf * C::kKCols;
+          if constexpr (C::kBS) {
+            // A = the unpacked K codes of the tile's raw stage (K-major, 128-byte rows), B = the leading and the remainder tile of Q
+            const int stage = c % kRawStages;
+            const uint64_t a_desc = smem_desc(sm_a + C::oRaw + stage * C::kRawStage, 16, 1024);
+#pragma unroll
+            for (int kb = 0; kb < D / 32; kb++) {
+              mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)(kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB, kb ? 1u : 0u);
+              mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)((C::kQHalf >> 4) + kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB + 4, 1u);
+            }
+            tc_commit(bar(bSfull + buf));
+            tc_commit(bar_raw_empty(stage));   // the K codes of the stage have been read
+          } else {
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++)
             mma_ts(d, a + ks * 8, q_desc + (uint64_t)(((ks >> 2) * C::kQHalf + (ks & 3) * 32) >> 4), idesc_qk, ks ? 1u : 0u);
           tc_commit(bar(bSfull + buf));
+          }
           UQ_TRACE(6, c)
           return true;
         };
@@ -580,10 +634,17 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (kk == 0) { UQ_TRACE(1, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
-        const unsigned long long sc = load_scales<C::kGroups>(raw + 2 * C::kRawCodes + kk * C::kGroups);
-        const uint32_t kref = max_byte<C::kGroups>(sc);
-        const uint32_t vref = max_byte<C::kGroups>(load_scales<C::kGroups>(raw + 2 * C::kRawCodes + C::kRawScales + kk * C::kGroups));
+        const unsigned long long sc = load_scales<C::kGroups>(raw + C::kOffKS + kk * C::kGroups);
+        const uint32_t kref = C::kBS ? 127u : max_byte<C::kGroups>(sc);
+        const uint32_t vref = max_byte<C::kGroups>(load_scales<C::kGroups>(raw + C::kOffVS + kk * C::kGroups));
         reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
+        if constexpr (C::kBS) {
+          // block-scaled: nothing to decode.  The contraction wants the scale bytes of key 32 j + l (one 32-bit word: byte b =
+          // channels 32 b ..) in column j of lane l of every 32-lane quarter: each warp writes its quarter.
+          const uint32_t* ksw = reinterpret_cast<const uint32_t*>(raw + C::kOffKS);
+          const uint32_t w4[4] = {ksw[lane], ksw[32 + lane], ksw[64 + lane], ksw[96 + lane]};
+          tmem_st4(lane_addr + C::cK + buf * C::kKCols, w4);
+        } else {
         // the code row of this key: chunk g (16 bytes = group g) sits at chunk g ^ ((key / rows per 128 B) mod chunks) (TMA swizzle)
         const uint8_t* krow = raw + kk * C::kCodeRow;
         const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
@@ -598,8 +659,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             const uint32_t m = pow2_f16x2((int)((uint32_t)(sc >> (8 * (g0 + g))) & 0xFFu) - (int)kref);
             uint32_t o[16];
             decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
-            if (!(UQ_ABL & 64) || cnt == 0) tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
+            tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
           }
+        }
         }
         UQ_PROF_T1(2)
         tc_wait_st();
@@ -627,10 +689,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (!ok) break;
         if (kk == 0) { UQ_TRACE(3, cnt) }
         UQ_PROF_T0
-        const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kRawCodes;
+        const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kOffVC;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
-        const unsigned long long sc = load_scales<C::kGroups>(sm + C::oRaw + stage * C::kRawStage + 2 * C::kRawCodes + C::kRawScales + kk * C::kGroups);
+        const unsigned long long sc = load_scales<C::kGroups>(sm + C::oRaw + stage * C::kRawStage + C::kOffVS + kk * C::kGroups);
         const int vref = (int)max_byte<C::kGroups>(sc);
         const uint8_t* vcode = raw + kk * C::kCodeRow;
         const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
@@ -650,8 +712,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             uint8_t* vrow = vt + (gg >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
             for (int w = 0; w < 4; w++)
-              if (!(UQ_ABL & 32) || cnt == 0 || o[4 * w] == 0x12345678u)
-                *reinterpret_cast<uint4*>(vrow + ((((4 * gg + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
+              *reinterpret_cast<uint4*>(vrow + ((((4 * gg + w) & 7) ^ (kk & 7)) << 4)) = make_uint4(o[4 * w], o[4 * w + 1], o[4 * w + 2], o[4 * w + 3]);
           }
         }
         UQ_PROF_T1(2)
@@ -716,7 +777,67 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
       // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
       // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
-      {
+      if constexpr (C::kBS) {
+        // ---- block-scaled: Q as two e4m3 tiles, Q = hi * 2^eh + lo * 2^el with one exponent pair per row and 32 channels
+        // (eh puts the block's largest magnitude in [128, 256), el = eh - 5 the remainder below 256: about nine significant bits
+        // relative to the block's largest entry).  A thread converts 16 channels; the two threads of a block are neighbours.
+        uint8_t* sfb = sm + C::oSfb;   // [2][NT][4] scale bytes, then relayed to TMEM
+        constexpr int kItems = NT * (D / 16);
+        for (int i0 = 0; i0 < kItems; i0 += kSm) {
+          const int i = i0 + st, n = i / (D / 16), a = i % (D / 16);
+          float qv[16];
+          uint32_t amax = 0;   // bf16 magnitudes compare as integers
+#pragma unroll
+          for (int j = 0; j < 16; j++) qv[j] = 0.f;
+          if (i < kItems && n < rows) {
+            const uint4* src = reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + 2 * a;
+            const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+            const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              qv[2 * j] = __uint_as_float(w8[j] << 16);
+              qv[2 * j + 1] = __uint_as_float(w8[j] & 0xFFFF0000u);
+              amax = max(amax, max(w8[j] & 0x7FFFu, (w8[j] >> 16) & 0x7FFFu));
+            }
+          }
+          amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          const int eh = max((int)(amax >> 7) - 127 - 7, -127), el = max(eh - 5, -127);
+          const float sh = pow2_f32(-eh), sl = pow2_f32(-el), dh = pow2_f32(eh);
+          uint32_t hw[4] = {0, 0, 0, 0}, lw[4] = {0, 0, 0, 0};
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint32_t h = pack_e4m3x2(qv[2 * j] * sh, qv[2 * j + 1] * sh);
+            float f0, f1;
+            unpack_e4m3x2(h, f0, f1);
+            const uint32_t l = pack_e4m3x2((qv[2 * j] - f0 * dh) * sl, (qv[2 * j + 1] - f1 * dh) * sl);
+            hw[j >> 1] |= h << (16 * (j & 1));
+            lw[j >> 1] |= l << (16 * (j & 1));
+          }
+          if (i < kItems) {
+            const int o = n * 128 + ((a ^ (n & 7)) << 4);
+            *reinterpret_cast<uint4*>(sm + C::oQ + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4*>(sm + C::oQ + C::kQHalf + o) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            if (!(a & 1)) { sfb[n * 4 + (a >> 1)] = (uint8_t)(eh + 127); sfb[(NT + n) * 4 + (a >> 1)] = (uint8_t)(el + 127); }
+          }
+        }
+        ok = rendezvous(59, seg_i);
+        if (!ok) break;
+        if (grp == 0) {   // one warp per 32-lane quarter: the scale bytes of row 32 j + l go to column j of lane l
+          const uint32_t* sw = reinterpret_cast<const uint32_t*>(sfb);
+          uint32_t h4[4], l4[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int row = 32 * j + lane;
+            h4[j] = row < NT ? sw[row] : 0x7F7F7F7Fu;
+            l4[j] = row < NT ? sw[NT + row] : 0x7F7F7F7Fu;
+          }
+          tmem_st4(lane_addr + C::cSFB, h4);
+          tmem_st4(lane_addr + C::cSFB + 4, l4);
+          tc_wait_st();
+        }
+        tc_fence_before();
+        csc0 = x.sc2;
+      } else {
         uint32_t amax = 0;   // bf16 magnitudes compare as integers
         for (int i = st; i < rows * (D / 8); i += kSm) {
           const int n = i / (D / 8), a = i % (D / 8);
@@ -776,7 +897,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         // this key: reference scale bytes, position, visibility
         const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk];
         const int vref = (int)(rf >> 8);
-        const float ck = csc0 * uq_scale_f32(rf & 0xFFu);
+        const float ck = C::kBS ? csc0 : csc0 * uq_scale_f32(rf & 0xFFu);   // block-scaled scores carry the keys' scales already
         // only a tile that reaches the end of the sequence or the draft positions needs masks (same answer in every thread)
         const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 > n_glob - p.K;
         bool live = true;
@@ -1006,6 +1127,19 @@ bool make_code_map(CUtensorMap* map, const uint8_t* base, int code_row_bytes, in
             swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The K codes for the block-scaled contraction: the same rows as packed 4-bit elements, which the copy engine unpacks on the
+// way in (16 elements = 8 bytes, then 8 bytes of padding), so a key's 128 channels land as one 128-byte row, 128-byte swizzle.
+bool make_unpack_map(CUtensorMap* map, const uint8_t* base, int channels, int page) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)channels, (cuuint64_t)1 << 31};
+  const cuuint64_t strides[1] = {(cuuint64_t)channels / 2};
+  const cuuint32_t box[2] = {(cuuint32_t)channels, (cuuint32_t)page};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<uint8_t*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int D, int NT>
 cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   using C = Cfg<D, NT>;
@@ -1026,7 +1160,8 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   const long long max_tiles = ((long long)p.max_pages * p.PAGE + kKeys - 1) / kKeys;
   prm.chunk_min = x.ns_eff >= 2 ? (int)((max_tiles + x.ns_eff - 2) / (x.ns_eff - 1)) : 1;
   CUtensorMap mk, mv;
-  if (!make_code_map(&mk, p.kc, C::kCodeRow, p.PAGE) || !make_code_map(&mv, p.vc, C::kCodeRow, p.PAGE)) return cudaErrorInvalidValue;
+  if (!(C::kBS ? make_unpack_map(&mk, p.kc, D, p.PAGE) : make_code_map(&mk, p.kc, C::kCodeRow, p.PAGE)) || !make_code_map(&mv, p.vc, C::kCodeRow, p.PAGE))
+    return cudaErrorInvalidValue;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   kern<<<sms, cta_threads(NT), C::kSmem, s>>>(prm, mk, mv);
@@ -1058,6 +1193,7 @@ bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
   if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
   if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
+  if (tc::block_scaled(p.D) && (reinterpret_cast<uintptr_t>(p.kc) & 31)) return false;   // the unpacking tensor map wants 32-byte alignment
   if ((long long)p.max_pages * p.PAGE >= (1ll << 30)) return false;
   return tc::encode_fn() != nullptr;
 }
