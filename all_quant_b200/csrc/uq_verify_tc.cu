@@ -35,8 +35,6 @@
 // refills the pipeline (about 30 000 cycles: epilogue, query tile conversion, first-tile reference move).
 #include <cuda.h>
 
-#include <type_traits>
-
 #include "uq_common.cuh"
 
 namespace tc {
@@ -44,9 +42,18 @@ namespace tc {
 #ifdef UQ_TC_TRACE
 // timeline of CTA 0 (developer build only): clock64 stamps of each role's events for its first 64 tiles
 __device__ long long g_tc_trace[64][16];
-#define UQ_TRACE(ev, c) if (blockIdx.x == 0 && (c) < 64) g_tc_trace[c][ev] = clock64();
+#ifndef UQ_TRACE_CTA
+#define UQ_TRACE_CTA 0
+#endif
+#ifndef UQ_TRACE_FROM
+#define UQ_TRACE_FROM 0
+#endif
+#define UQ_TRACE(ev, c) if (blockIdx.x == UQ_TRACE_CTA && (c) >= UQ_TRACE_FROM && (c) < UQ_TRACE_FROM + 64) g_tc_trace[(c) - UQ_TRACE_FROM][ev] = clock64();
+// stamps of the softmax role's steps around a change of segment (rows 60-63 of the same table, one row per segment)
+#define UQ_TRACE_SEG(ev) if (blockIdx.x == UQ_TRACE_CTA && st == 0 && seg_i < 4) g_tc_trace[60 + seg_i][ev] = clock64();
 #else
 #define UQ_TRACE(ev, c)
+#define UQ_TRACE_SEG(ev)
 #endif
 #ifdef UQ_TC_PROF
 // per-role cycle counters (profiling build only): [role][0..5] cycles spent in the role's wait sites, [6] event count, [7] total cycles
@@ -76,14 +83,17 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_NSG4_AT 32
 #endif
 #ifndef UQ_ABL
-#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no work in the softmax's common tile, 32 no V decode, 64 no scale relay
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
 // producer, Q.K issue, P.V issue, one idle warp.  The roles are latency bound (one warp of a role per SM sub-partition issues
 // about once per 10 cycles), so the softmax, the longest role at 64 rows, is spread over four warpgroups.
 __host__ __device__ constexpr int softmax_groups(int NT) { return NT >= UQ_NSG4_AT ? 4 : 2; }
-__host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 12) * 32; }
+// With fewer than 64 rows the V decode is the longest role and the CTA has warps to spare: eight V warps, each thread
+// half of its key's scale groups; with 64 rows the softmax is, and issue slots are what it lacks: four V warps.
+__host__ __device__ constexpr int v_warps(int NT) { return NT < 64 ? 8 : 4; }
+__host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 8 + v_warps(NT)) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
 __host__ __device__ constexpr bool block_scaled(int D) { return D == 128; }          // Q.K straight from the e2m1 codes and scale bytes (see Cfg::kBS)
 __host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : (D == 128 ? 3 : 4); }   // raw code/scale tiles in flight (TMA)
@@ -189,6 +199,20 @@ UQ_DEV float fast_exp2(float v) {   // 2^v, -inf -> 0
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(v));
   return d;
 }
+// packed fp32 pairs: one issue slot for two operations (the kernel is short of issue slots, not of FMA-pipe cycles)
+UQ_DEV void fma_f32x2(float& d0, float& d1, float a0, float a1, float b, float c0, float c1) {   // d = a * b + c
+  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %4};\n mov.b64 rc, {%5, %6};\n fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c0), "f"(c1));
+}
+UQ_DEV void add_f32x2(float& d0, float& d1, float a0, float a1) {   // d += a
+  asm("{\n .reg .b64 ra, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rd, {%0, %1};\n add.rn.f32x2 rd, rd, ra;\n mov.b64 {%0, %1}, rd;\n}"
+      : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
+UQ_DEV uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 UQ_DEV uint32_t pack_f16x2(float lo, float hi) {
   uint32_t d;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
@@ -268,6 +292,40 @@ UQ_DEV uint32_t max_byte(unsigned long long v) {
 UQ_DEV float pow2_f32(int e) {
   e = min(e, 127);
   return e >= -126 ? __int_as_float((e + 127) << 23) : (e >= -149 ? __int_as_float(1 << (e + 149)) : 0.f);
+}
+
+// Reduction of N values per lane across the warp (N = 8 or 16), sum or maximum.  Instead of one butterfly per value
+// (5 N shuffles), every step halves the values a lane still holds: lanes with the step's bit clear keep the lower half and
+// take the partner's lower half, the others the upper halves: N - 1 + log2(32 / N) shuffles.  Returns the reduction of value
+// warp_fold_row<N>(lane); the 32 / N lanes that differ only in their low bits hold the same value.
+template <int N>
+UQ_DEV int warp_fold_row(int lane) {
+  int row = 0, bit = 16;
+#pragma unroll
+  for (int h = N / 2; h >= 1; h >>= 1, bit >>= 1) row += (lane & bit) ? h : 0;
+  return row;
+}
+template <int N, bool kMax>
+UQ_DEV float warp_fold(float* v, int lane) {
+  int bit = 16;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1, bit >>= 1) {
+    const bool hi = (lane & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; i++) {
+      const float give = hi ? v[i] : v[i + n / 2];
+      const float keep = hi ? v[i + n / 2] : v[i];
+      const float got = __shfl_xor_sync(0xffffffffu, give, bit);
+      v[i] = kMax ? fmaxf(keep, got) : keep + got;
+    }
+  }
+  float r = v[0];
+#pragma unroll
+  for (; bit; bit >>= 1) {
+    const float got = __shfl_xor_sync(0xffffffffu, r, bit);
+    r = kMax ? fmaxf(r, got) : r + got;
+  }
+  return r;
 }
 
 // ---------------------------------------------------------------------------------------------- layout
@@ -420,7 +478,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   }
   constexpr int NSG = softmax_groups(NT), kThreads = cta_threads(NT);
   constexpr int kRawStages = C::kRawStages, kSB = C::kSB, kVB = C::kVB;
-  constexpr int kWarpK = 4 * NSG, kWarpV = kWarpK + 4, kWarpProd = kWarpV + 4, kWarpMma = kWarpProd + 1;   // first warp of each role; softmax = 0
+  constexpr int kNV = v_warps(NT);
+  constexpr int kWarpK = 4 * NSG, kWarpV = kWarpK + 4, kWarpProd = kWarpV + kNV, kWarpMma = kWarpProd + 1;   // first warp of each role; softmax = 0
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::oAbort);
   int* prefix = reinterpret_cast<int*>(sm + C::oPrefix);
@@ -452,15 +511,15 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
-    // a raw stage is free again after the four K and four V warps have read it (block-scaled: and after the Q.K instructions have)
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), C::kBS ? 9 : 8); }
+    // a raw stage is free again after the four K (or relay) warps and the V warps have read it (block-scaled: and after the Q.K instructions have)
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 4 + kNV + (C::kBS ? 1 : 0)); }
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
       mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1);
       mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPdone + i), 1);
     }
-    for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), 4); mbar_init(bar(bVdone + i), 1); }
+    for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), kNV); mbar_init(bar(bVdone + i), 1); }
     mbar_init(bar(bQfull), 4 * NSG); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4 * NSG); mbar_init(bar(bVote), 4 * NSG);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
@@ -641,9 +700,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if constexpr (C::kBS) {
           // block-scaled: nothing to decode.  The contraction wants the scale bytes of key 32 j + l (one 32-bit word: byte b =
           // channels 32 b ..) in column j of lane l of every 32-lane quarter: each warp writes its quarter.
-          const uint32_t* ksw = reinterpret_cast<const uint32_t*>(raw + C::kOffKS);
-          const uint32_t w4[4] = {ksw[lane], ksw[32 + lane], ksw[64 + lane], ksw[96 + lane]};
-          tmem_st4(lane_addr + C::cK + buf * C::kKCols, w4);
+          if (!(UQ_ABL & 64) || cnt == 0) {
+            const uint32_t* ksw = reinterpret_cast<const uint32_t*>(raw + C::kOffKS);
+            const uint32_t w4[4] = {ksw[lane], ksw[32 + lane], ksw[64 + lane], ksw[96 + lane]};
+            tmem_st4(lane_addr + C::cK + buf * C::kKCols, w4);
+          }
         } else {
         // the code row of this key: chunk g (16 bytes = group g) sits at chunk g ^ ((key / rows per 128 B) mod chunks) (TMA swizzle)
         const uint8_t* krow = raw + kk * C::kCodeRow;
@@ -673,9 +734,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
     }
     UQ_PROF_FLUSH(2, kk == 0)
-  } else if (warp >= kWarpV && warp < kWarpV + 4) {
-    // ================================================================= V decode -> shared memory
-    const int kk = (warp - kWarpV) * 32 + lane;
+  } else if (warp >= kWarpV && warp < kWarpV + kNV) {
+    // ================================================================= V decode -> shared memory (thread = key, or half a key with eight warps)
+    constexpr int kGPT = C::kGroups / (kNV / 4);        // scale groups per thread
+    const int vw = warp - kWarpV, kk = (vw & 3) * 32 + lane, gfirst = (vw >> 2) * kGPT;
     UQ_PROF_DECL
     while (ok && wk.next(sg)) {
       if (!take()) continue;
@@ -687,7 +749,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), (cnt / kVB - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (kk == 0) { UQ_TRACE(3, cnt) }
+        if (vw == 0 && lane == 0) { UQ_TRACE(3, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kOffVC;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
@@ -697,8 +759,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const uint8_t* vcode = raw + kk * C::kCodeRow;
         const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
 #pragma unroll
-        for (int g0 = 0; g0 < C::kGroups; g0 += 4) {
-          constexpr int GN = C::kGroups < 4 ? C::kGroups : 4;
+        for (int gb = 0; gb < ((UQ_ABL & 32) && cnt ? 0 : kGPT); gb += 4) {
+          constexpr int GN = kGPT < 4 ? kGPT : 4;
+          const int g0 = gfirst + gb;
           uint4 c4[GN];
 #pragma unroll
           for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(vcode + (((g0 + g) ^ swz) << 4));
@@ -719,11 +782,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         fence_async_smem();
         warp_arrive(bar(bVfull + buf));
         warp_arrive(bar_raw_empty(stage));
-        if (kk == 0) { UQ_TRACE(4, cnt) }
+        if (vw == 0 && lane == 0) { UQ_TRACE(4, cnt) }
         UQ_PROF_T1(3)
       }
     }
-    UQ_PROF_FLUSH(3, kk == 0)
+    UQ_PROF_FLUSH(3, vw == 0 && lane == 0)
   } else if (warp < 4 * NSG) {
     // ================================================================= softmax + epilogue: NSG warpgroups, NT / NSG rows each
     constexpr int HW = NT / NSG;                        // rows (columns of S^T) per thread
@@ -770,6 +833,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     }
     while (ok && wk.next(sg)) {
       if (!take()) continue;
+      UQ_TRACE_SEG(0)
       const bool careful = pass == 1 || ord >= 32 * kRedoWords;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
@@ -820,7 +884,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             if (!(a & 1)) { sfb[n * 4 + (a >> 1)] = (uint8_t)(eh + 127); sfb[(NT + n) * 4 + (a >> 1)] = (uint8_t)(el + 127); }
           }
         }
+        UQ_TRACE_SEG(1)
         ok = rendezvous(59, seg_i);
+        UQ_TRACE_SEG(2)
         if (!ok) break;
         if (grp == 0) {   // one warp per 32-lane quarter: the scale bytes of row 32 j + l go to column j of lane l
           const uint32_t* sw = reinterpret_cast<const uint32_t*>(sfb);
@@ -876,11 +942,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       if (st == 0) wr[4 + mcur] = 0u;
       fence_async_smem();
       warp_arrive(bar(bQfull));
+      UQ_TRACE_SEG(3)
       // the first segment of an item marks the slots the item does not use as empty
       if (sg.t0 == 0)
         for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += kSm)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
       ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
+      UQ_TRACE_SEG(4)
       float l[HW];
 #pragma unroll
       for (int i = 0; i < HW; i++) l[i] = 0.f;
@@ -910,34 +978,31 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         }
         uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
         float pv[HW];
-        // scores -> probabilities against the references `mrow`, in place.  The full form applies the masks and returns the
-        // largest exponent seen; the lean form (no masks needed, nobody asks for the maximum) is the common tile's.
-        auto probabilities = [&](const float* mrow, auto full_c) -> float {
-          constexpr bool kFull = decltype(full_c)::value;
+        // scores -> probabilities against the references `mrow`, in place, with the masks; returns the largest exponent seen
+        // (the form for masked tiles, first tiles and the careful path; the common tile has a leaner one below)
+        auto probabilities = [&](const float* mrow) -> float {
           float xm = kNegBig;
 #pragma unroll
           for (int i = 0; i < HW; i++) {
             float xv = fmaf(pv[i], ck, (UQ_ABL & 4) ? -1.0f : -mrow[r0 + i]);
-            if (kFull) {
-              xv = (r0 + i >= rmin) ? xv : -INFINITY;
-              xm = fmaxf(xm, xv);
-            }
+            xv = (r0 + i >= rmin) ? xv : -INFINITY;
+            xm = fmaxf(xm, xv);
             pv[i] = (UQ_ABL & 1) ? xv * 0.001f : fast_exp2(xv);
           }
           return xm;
         };
-        constexpr std::true_type full_c{};
-        constexpr std::false_type lean_c{};
         // P^T row of this key: probabilities times the key's V reference relative to the segment's, fp16
         auto write_p = [&](int rbyte) {
-          const float vf = live ? pow2_f32(vref - rbyte) : 0.f;   // past the end the bytes are arbitrary: keep 0 * vf finite
+          // the power of two is applied to the packed pairs (exact; a pair that no longer fits becomes an infinity, which the
+          // votes or the epilogue see); past the end of the sequence the bytes are arbitrary: factor 0
+          const uint32_t vf = live ? pow2_f16x2(min(vref - rbyte, 16)) : 0u;
 #pragma unroll
           for (int c = 0; c < HW / 8; c++)
             *reinterpret_cast<uint4*>(pt + (((r0 / 8 + c) ^ (kk & 7)) << 4)) =
-                make_uint4(pack_f16x2(pv[8 * c] * vf, pv[8 * c + 1] * vf), pack_f16x2(pv[8 * c + 2] * vf, pv[8 * c + 3] * vf),
-                           pack_f16x2(pv[8 * c + 4] * vf, pv[8 * c + 5] * vf), pack_f16x2(pv[8 * c + 6] * vf, pv[8 * c + 7] * vf));
+                make_uint4(mul_f16x2(pack_f16x2(pv[8 * c], pv[8 * c + 1]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 2], pv[8 * c + 3]), vf),
+                           mul_f16x2(pack_f16x2(pv[8 * c + 4], pv[8 * c + 5]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 6], pv[8 * c + 7]), vf));
         };
-        if (!(UQ_ABL & 8) || cnt == c0) load_scores(s_addr, pv);
+        if (!(UQ_ABL & (8 | 16)) || cnt == c0) load_scores(s_addr, pv);
         else {
 #pragma unroll
           for (int i = 0; i < HW; i++) pv[i] = 0.5f;
@@ -948,10 +1013,22 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const bool agree = careful || cnt == c0;   // the first tile of a segment sets the references; later tiles only on the careful path
         const bool lean = !agree && !need_mask;
         float xm = kNegBig;
-        if (lean) probabilities(mref + mcur * NT, lean_c);
-        else xm = probabilities(mref + mcur * NT, full_c);
+        if (lean && (UQ_ABL & 16)) {
+        } else if (lean) {
+          // the common tile: 2^(s * ck - m) as 2^-(s * (-ck) + m), two rows per fused multiply-add
+          const float4* m4 = reinterpret_cast<const float4*>(mref + mcur * NT + r0);
+          const float nck = -ck;
+#pragma unroll
+          for (int j = 0; j < HW / 4; j++) {
+            const float4 m = m4[j];
+            float y0, y1, y2, y3;
+            fma_f32x2(y0, y1, pv[4 * j], pv[4 * j + 1], nck, m.x, m.y);
+            fma_f32x2(y2, y3, pv[4 * j + 2], pv[4 * j + 3], nck, m.z, m.w);
+            pv[4 * j] = fast_exp2(-y0); pv[4 * j + 1] = fast_exp2(-y1); pv[4 * j + 2] = fast_exp2(-y2); pv[4 * j + 3] = fast_exp2(-y3);
+          }
+        } else xm = probabilities(mref + mcur * NT);
         UQ_PROF_TB(3)
-        if (!(UQ_ABL & 2) || cnt == c0) write_p(rbyte);
+        if (!(UQ_ABL & 2) && !((UQ_ABL & 16) && lean) || cnt == c0) write_p(rbyte);
         if (st == 0) { UQ_TRACE(11, cnt) }
         UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
@@ -973,12 +1050,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           // and redo this tile against the new references
           const float* mr = mref + mcur * NT;
           load_scores(s_addr, pv);
+          {
+            float vv[HW];
 #pragma unroll
-          for (int i = 0; i < HW; i++) {
-            float v = (!need_mask || r0 + i >= rmin) ? pv[i] * ck : -INFINITY;
-#pragma unroll
-            for (int m = 16; m; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
-            if (lane == 0) wmax[quad * NT + r0 + i] = v;
+            for (int i = 0; i < HW; i++) vv[i] = (!need_mask || r0 + i >= rmin) ? pv[i] * ck : -INFINITY;
+            const float vmax = warp_fold<HW, true>(vv, lane);
+            if ((lane & (32 / HW - 1)) == 0) wmax[quad * NT + r0 + warp_fold_row<HW>(lane)] = vmax;
           }
           if (grp == 0) {
             const uint32_t vr = __reduce_max_sync(0xffffffffu, live ? (uint32_t)vref : 0u);
@@ -1019,12 +1096,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
           load_scores(s_addr, pv);
-          probabilities(mref + mcur * NT, full_c);
+          probabilities(mref + mcur * NT);
           write_p((int)wr[4 + mcur]);
         }
         UQ_PROF_TA2
+        if (!((UQ_ABL & 16) && lean)) {
 #pragma unroll
-        for (int i = 0; i < HW; i++) l[i] += pv[i];
+          for (int i = 0; i < HW; i += 2) add_f32x2(l[i], l[i + 1], pv[i], pv[i + 1]);
+        }
         tc_fence_before();
         fence_async_smem();
         warp_arrive(bar(bPfull + buf));   // P^T is written; it also tells the Q.K issuer that this slot's S^T is consumed
@@ -1032,19 +1111,20 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         UQ_PROF_TB(5)
       }
       if (!ok) break;
+      UQ_TRACE_SEG(5)
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
-#pragma unroll
-      for (int i = 0; i < HW; i++) {
-        float v = l[i];
-#pragma unroll
-        for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-        if (lane == 0) atomicAdd(&lsum[r0 + i], v);
+      {
+        const float lw = warp_fold<HW, false>(l, lane);
+        if ((lane & (32 / HW - 1)) == 0) atomicAdd(&lsum[r0 + warp_fold_row<HW>(lane)], lw);
       }
+      UQ_TRACE_SEG(6)
       ok = rendezvous(70, seg_i);
+      UQ_TRACE_SEG(7)
       if (ok) ok = wait(bar(bOdone), seg_i & 1, 71, seg_i UQ_PROF_SITE(0));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      UQ_TRACE_SEG(8)
       {
         const size_t slot = uq_slot(p, sg.b, sg.hk, sg.slot);
         float* mo = p.mo + slot * x.BM * D;
@@ -1063,7 +1143,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
               if (r < rows) {
                 const float lr = lsum[r];
                 bad |= !(fabsf(ov[i]) <= 3.0e38f) || !(lr <= 3.0e38f);
-                mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * (osc / lr) : 0.f;
+                mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * __fdividef(osc, lr) : 0.f;
               }
             }
           }
@@ -1074,7 +1154,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       tc_fence_before();
       warp_arrive(bar(bEpi));
+      UQ_TRACE_SEG(9)
       ok = rendezvous(72, seg_i);   // everyone has read the sums and references before the next segment overwrites them
+      UQ_TRACE_SEG(10)
       seg_i++;
     }
     UQ_PROF_FLUSH(4, st == 0)
