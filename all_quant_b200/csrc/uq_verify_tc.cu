@@ -953,7 +953,62 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
       for (int i = 0; i < HW; i++) l[i] = 0.f;
       const int c0 = cnt;
+      // tiles from this index on need masks (they reach the end of the sequence or the draft positions); the others are
+      // the common tiles
+      int tmask;
+      {
+        const int xq = n_glob - p.K - off - (kKeys - 1);
+        tmask = min(n_loc / kKeys, xq < 0 ? 0 : xq / kKeys + 1);
+      }
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
+        if (!careful && cnt > c0 && t < tmask) {
+          // ---- a run of common tiles of the quick path: references fixed, no masks, nothing to agree on.  The loop keeps
+          // only what such a tile needs (the kernel is bound by the number of instructions per tile): ring slot
+          // and phase are counted up instead of divided out, per-segment values are read once.
+          const int t_end = min(sg.t1, tmask);
+          int buf = cnt % kSB;
+          uint32_t sph = (uint32_t)(cnt / kSB) & 1u;
+          const float4* m4 = reinterpret_cast<const float4*>(mref + mcur * NT + r0);   // fixed for the run
+          const int rbyte = (int)wr[4 + mcur];
+          const uint16_t* oref = reinterpret_cast<const uint16_t*>(sm + C::oRef) + kk;
+          uint8_t* pk = sm + C::oP + kk * 128;
+          for (; t < t_end; t++, cnt++) {
+            bool r = wait(bar(bSfull + buf), sph, 62 + buf, cnt UQ_PROF_SITE(0));
+            r = __all_sync(0xffffffffu, r);
+            if (!r) { ok = false; break; }
+            tc_fence_after();
+            if (st == 0) { UQ_TRACE(9, cnt) }
+            float pv[HW];
+            load_scores(lane_addr + C::cS + buf * NT + r0, pv);
+            const uint32_t rf = oref[(cnt & 7) * kKeys];
+            const float nck = C::kBS ? -csc0 : -(csc0 * uq_scale_f32(rf & 0xFFu));
+            const uint32_t vf = pow2_f16x2(min((int)(rf >> 8) - rbyte, 16));
+            if (st == 0) { UQ_TRACE(10, cnt) }
+#pragma unroll
+            for (int j = 0; j < HW / 4; j++) {   // 2^(s * ck - m) as 2^-(s * (-ck) + m), two rows per fused multiply-add
+              const float4 m = m4[j];
+              float y0, y1, y2, y3;
+              fma_f32x2(y0, y1, pv[4 * j], pv[4 * j + 1], nck, m.x, m.y);
+              fma_f32x2(y2, y3, pv[4 * j + 2], pv[4 * j + 3], nck, m.z, m.w);
+              pv[4 * j] = fast_exp2(-y0); pv[4 * j + 1] = fast_exp2(-y1); pv[4 * j + 2] = fast_exp2(-y2); pv[4 * j + 3] = fast_exp2(-y3);
+            }
+            uint8_t* pt = pk + buf * C::kPTile;
+#pragma unroll
+            for (int c = 0; c < HW / 8; c++)
+              *reinterpret_cast<uint4*>(pt + (((r0 / 8 + c) ^ (kk & 7)) << 4)) =
+                  make_uint4(mul_f16x2(pack_f16x2(pv[8 * c], pv[8 * c + 1]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 2], pv[8 * c + 3]), vf),
+                             mul_f16x2(pack_f16x2(pv[8 * c + 4], pv[8 * c + 5]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 6], pv[8 * c + 7]), vf));
+            if (st == 0) { UQ_TRACE(11, cnt) }
+#pragma unroll
+            for (int i = 0; i < HW; i += 2) add_f32x2(l[i], l[i + 1], pv[i], pv[i + 1]);
+            tc_fence_before();
+            fence_async_smem();
+            warp_arrive(bar(bPfull + buf));
+            if (st == 0) { UQ_TRACE(13, cnt) }
+            if (++buf == kSB) { buf = 0; sph ^= 1u; }
+          }
+          if (!ok || t >= sg.t1) break;
+        }
         const int buf = cnt % kSB;
         ok = wait(bar(bSfull + buf), (cnt / kSB) & 1, 62 + buf, cnt UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
@@ -1010,10 +1065,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (st == 0) { UQ_TRACE(10, cnt) }
         UQ_PROF_TB(2)
         const int rbyte = (int)wr[4 + mcur];
-        const bool agree = careful || cnt == c0;   // the first tile of a segment sets the references; later tiles only on the careful path
-        const bool lean = !agree && !need_mask;
+        const bool first = cnt == c0;              // the first tile of a segment sets the references: straight to the move below
+        const bool agree = careful && !first;      // later tiles agree on a move only on the careful path
+        const bool lean = !careful && !first && !need_mask;
         float xm = kNegBig;
-        if (lean && (UQ_ABL & 16)) {
+        if (first || (lean && (UQ_ABL & 16))) {
         } else if (lean) {
           // the common tile: 2^(s * ck - m) as 2^-(s * (-ck) + m), two rows per fused multiply-add
           const float4* m4 = reinterpret_cast<const float4*>(mref + mcur * NT + r0);
@@ -1028,28 +1084,28 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
         } else xm = probabilities(mref + mcur * NT);
         UQ_PROF_TB(3)
-        if (!(UQ_ABL & 2) && !((UQ_ABL & 16) && lean) || cnt == c0) write_p(rbyte);
+        if (!first && !(UQ_ABL & 2) && !((UQ_ABL & 16) && lean)) write_p(rbyte);
         if (st == 0) { UQ_TRACE(11, cnt) }
         UQ_PROF_TB(4)
         // ---- did any score leave the window of its row's reference, or any key's V scale exceed the segment's reference?
         // (the lean tiles of the quick path do not look: an overflow there leaves infinities or NaNs in O^T, which the
         // segment's epilogue finds)
-        const bool grew = !lean && __any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte));
+        const bool grew = !lean && !first && __any_sync(0xffffffffu, xm > kRescaleAt || (live && vref > rbyte));
         const int vslot = nvote & 1;
-        if (!agree) {
-          // quick path: what this tile wrote may have overflowed; mark the segment for the second pass and carry on
-          if (grew && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
-        } else {
+        if (agree) {
           if (grew && lane == 0) atomicOr(&vote[vslot], 1);
           ok = rendezvous(64, cnt);
           if (!ok) break;
+        } else if (!first) {
+          // quick path: what this tile wrote may have overflowed; mark the segment for the second pass and carry on
+          if (grew && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
         }
-        if (agree && *reinterpret_cast<volatile int*>(&vote[vslot])) {
+        if (first || (agree && *reinterpret_cast<volatile int*>(&vote[vslot]))) {
           UQ_PROF_COUNT(6)
           // ---- move the references (the first tile of a segment, then only on growth), rescale what was accumulated,
           // and redo this tile against the new references
           const float* mr = mref + mcur * NT;
-          load_scores(s_addr, pv);
+          if (!first) load_scores(s_addr, pv);   // (a first tile still holds the scores it loaded)
           {
             float vv[HW];
 #pragma unroll
@@ -1155,8 +1211,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       tc_fence_before();
       warp_arrive(bar(bEpi));
       UQ_TRACE_SEG(9)
-      ok = rendezvous(72, seg_i);   // everyone has read the sums and references before the next segment overwrites them
-      UQ_TRACE_SEG(10)
+      // (no rendezvous here: the next segment initialises the sums and references only after the rendezvous in the middle of
+      // its prologue, which every thread reaches after it has read them above)
       seg_i++;
     }
     UQ_PROF_FLUSH(4, st == 0)
