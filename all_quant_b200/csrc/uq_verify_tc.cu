@@ -35,6 +35,8 @@
 // refills the pipeline (about 30 000 cycles: epilogue, query tile conversion, first-tile reference move).
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "uq_common.cuh"
 
 namespace tc {
@@ -402,6 +404,16 @@ struct Params {
   int chunk_min;      // lower bound on the chunk (tiles per CTA) that keeps segments per item within ns_eff
 };
 
+// Position in a ring of N slots: the slot and the phase bit of the current lap, counted up tile by tile (a division and
+// a remainder per tile, role and ring add up in a kernel that is bound by its instruction count).
+template <int N>
+struct RingPos {
+  int slot;
+  uint32_t phase;
+  UQ_DEV void set(int cnt) { slot = cnt % N; phase = (uint32_t)(cnt / N) & 1u; }
+  UQ_DEV void next() { if (++slot == N) { slot = 0; phase ^= 1u; } }
+};
+
 // ---------------------------------------------------------------------------------------------- work list
 struct Seg {
   int b, hk, t0, t1;   // tiles [t0, t1) of item (b, hk)
@@ -681,12 +693,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     const int quad = warp & 3, kk = quad * 32 + lane;   // key of this thread = accumulator lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     UQ_PROF_DECL
+    RingPos<kRawStages> rp;
+    RingPos<kSB> sp;
+    rp.set(cnt);
+    sp.set(cnt);
     while (ok && wk.next(sg)) {
       if (!take()) continue;
-      for (int t = sg.t0; t < sg.t1; t++, cnt++) {
-        const int stage = cnt % kRawStages, buf = cnt % kSB;
-        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 40 + stage, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= kSB) ok = wait(bar(bSfull + buf), (cnt / kSB - 1) & 1, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T of the tile that used this buffer is done: the A operand is free
+      for (int t = sg.t0; t < sg.t1; t++, cnt++, rp.next(), sp.next()) {
+        const int stage = rp.slot, buf = sp.slot;
+        ok = wait(bar_raw_full(stage), rp.phase, 40 + stage, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= kSB) ok = wait(bar(bSfull + buf), sp.phase ^ 1u, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T of the tile that used this buffer is done: the A operand is free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -739,14 +755,18 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     constexpr int kGPT = C::kGroups / (kNV / 4);        // scale groups per thread
     const int vw = warp - kWarpV, kk = (vw & 3) * 32 + lane, gfirst = (vw >> 2) * kGPT;
     UQ_PROF_DECL
+    RingPos<kRawStages> rp;
+    RingPos<kVB> vp;
+    rp.set(cnt);
+    vp.set(cnt);
     while (ok && wk.next(sg)) {
       if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
-      for (int t = sg.t0; t < sg.t1; t++, cnt++) {
-        const int stage = cnt % kRawStages, buf = cnt % kVB;
-        ok = wait(bar_raw_full(stage), (cnt / kRawStages) & 1, 50 + stage, cnt UQ_PROF_SITE(0));
-        if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), (cnt / kVB - 1) & 1, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
+      for (int t = sg.t0; t < sg.t1; t++, cnt++, rp.next(), vp.next()) {
+        const int stage = rp.slot, buf = vp.slot;
+        ok = wait(bar_raw_full(stage), rp.phase, 50 + stage, cnt UQ_PROF_SITE(0));
+        if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), vp.phase ^ 1u, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (vw == 0 && lane == 0) { UQ_TRACE(3, cnt) }
@@ -1336,7 +1356,16 @@ bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
   return tc::encode_fn() != nullptr;
 }
 
-int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) { return p.nsplit; }
+// Partial slots the kernel uses per (sequence, kv head): at most the caller's nsplit, and no more than an item can span.
+// The flat list gives a CTA ceil(total / SMs) tiles and total >= Hkv x (tiles of the longest item), so an item spans at
+// most ceil(SMs / Hkv) + 1 CTAs; slots beyond that would only be marked empty by the kernel and skipped by the combine.
+int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); return p.nsplit; }
+  const int span = (sms + p.HKV - 1) / p.HKV + 1;
+  return std::max(1, std::min(p.nsplit, span));
+}
 
 template <int D>
 static cudaError_t dispatch_rows(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
