@@ -119,6 +119,14 @@ UQ_DEV uint32_t mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000000u) : "memory");
   return ok;
 }
+// Non-blocking test of a phase: about a third of the cost of a blocking try when the phase is already complete, which is
+// the common case for most waits of this kernel.
+UQ_DEV uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
 UQ_DEV unsigned long long now_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -422,8 +430,13 @@ struct Seg {
   int ntiles;          // tiles of the whole item
 };
 
+// The list is cut in WEIGHTED units: an item of n tiles counts n + kSegW, the extra units standing for what the start of
+// a segment costs (query conversion, first-tile reference, epilogue: about eight tiles' time), so that a CTA whose chunk
+// crosses into a second item gets correspondingly fewer tiles and all CTAs finish together.
+constexpr int kSegW = 8;
+
 struct Walker {
-  const int* prefix;   // prefix[b] = tiles of sequences < b (one kv head)
+  const int* prefix;   // prefix[b] = weighted units of sequences < b (one kv head): tiles + kSegW per non-empty sequence
   int B, HKV, nitems, total, chunk, per_item;
   int pos, end, it, cta;
 
@@ -439,8 +452,7 @@ struct Walker {
     end = min(pos + chunk, total);
     it = 0;
   }
-  UQ_DEV int item_tiles(int item) const { const int b = item / HKV; return prefix[b + 1] - prefix[b]; }
-  UQ_DEV int item_start(int item) const { const int b = item / HKV, hk = item % HKV; return HKV * prefix[b] + hk * (prefix[b + 1] - prefix[b]); }
+  UQ_DEV int item_tiles(int item) const { const int b = item / HKV; return max(prefix[b + 1] - prefix[b] - kSegW, 0); }
   __device__ __noinline__ bool next(Seg& s) {
     if (per_item) {
       for (it += (int)gridDim.x; it < nitems; it += (int)gridDim.x) {
@@ -451,24 +463,29 @@ struct Walker {
       }
       return false;
     }
-    if (pos >= end) return false;
-    // sequence containing flat tile `pos`: largest b with HKV * prefix[b] <= pos
-    int lo = 0, hi = B;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (HKV * prefix[mid] <= pos) lo = mid; else hi = mid;
+    while (pos < end) {
+      // sequence containing unit `pos`: largest b with HKV * prefix[b] <= pos
+      int lo = 0, hi = B;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (HKV * prefix[mid] <= pos) lo = mid; else hi = mid;
+      }
+      const int nv = prefix[lo + 1] - prefix[lo];   // > 0 because pos < HKV * prefix[lo + 1]
+      const int n = nv - kSegW;
+      const int hk = (pos - HKV * prefix[lo]) / nv;
+      const int first = HKV * prefix[lo] + hk * nv + kSegW;   // unit of the item's tile 0 (the kSegW units before it are the start-up weight)
+      const int t0 = max(pos, first) - first, t1 = min(first + n, end) - first;
+      if (t1 > t0) {
+        s.b = lo; s.hk = hk; s.ntiles = n; s.t0 = t0; s.t1 = t1;
+        const int c0 = first / chunk;   // the CTA of the item's tile 0 writes slot 0
+        s.slot = cta - c0;
+        s.nseg = (first + n - 1) / chunk - c0 + 1;
+        pos = first + t1;
+        return true;
+      }
+      pos = min(first + n, end);   // only start-up units of this item fall into the chunk
     }
-    const int n = prefix[lo + 1] - prefix[lo];   // > 0 because pos < HKV * prefix[lo + 1]
-    const int hk = (pos - HKV * prefix[lo]) / n;
-    const int start = HKV * prefix[lo] + hk * n;
-    s.b = lo; s.hk = hk; s.ntiles = n;
-    s.t0 = pos - start;
-    s.t1 = min(start + n, end) - start;
-    const int c0 = start / chunk;
-    s.slot = cta - c0;
-    s.nseg = (start + n - 1) / chunk - c0 + 1;
-    pos = start + s.t1;
-    return true;
+    return false;
   }
 };
 
@@ -500,14 +517,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   auto bar_raw_empty = [&](int s) { return sm_a + C::oBar + 8 * (kRawStages + s); };
   auto bar = [&](int i) { return sm_a + C::oBar + 8 * (2 * kRawStages + i); };
 
-  // Wait on an mbarrier: two blocking tries inline (try_wait itself suspends the thread for a while, so these almost always
-  // suffice), then the out-of-line bounded wait.  The call sits on the rare path so that the registers live across it
+  // Wait on an mbarrier: a test and one blocking try inline (try_wait itself suspends the thread for a while, so these
+  // almost always suffice), then the out-of-line bounded wait.  The call sits on the rare path so that the registers live across it
   // are not saved and restored on every tile.
   auto wait = [&](uint32_t b, uint32_t parity, int id, int tile, unsigned long long* site) -> bool {
 #ifdef UQ_TC_PROF
     const long long c_start = clock64();
 #endif
-    bool r = mbar_try(b, parity) || mbar_try(b, parity);
+    bool r = mbar_test(b, parity) || mbar_try(b, parity);
     if (!r) r = bounded_wait(b, parity, abort_flag, x.status, id, tile);
 #ifdef UQ_TC_PROF
     if (site) *site += clock64() - c_start;
@@ -543,7 +560,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   for (int b = tid; b < p.B; b += kThreads) {   // tiles per sequence, then an in-place scan by one thread
     int off;
     const int n = uq_n_local(p, x, b, &off);
-    prefix[b + 1] = (n + kKeys - 1) / kKeys;
+    const int tiles = (n + kKeys - 1) / kKeys;
+    prefix[b + 1] = tiles ? tiles + kSegW : 0;
   }
   __syncthreads();
   if (tid == 0) {
