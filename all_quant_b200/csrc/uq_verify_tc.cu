@@ -541,14 +541,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
     // a raw stage is free again after the four K (or relay) warps and the V warps have read it (block-scaled: and after the Q.K instructions have)
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 4 + kNV + (C::kBS ? 1 : 0)); }
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 4 + (kNV == 8 && kVB == 2 ? 4 : kNV) + (C::kBS ? 1 : 0)); }
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
       mbar_init(bar(bKfull + i), 4); mbar_init(bar(bSfull + i), 1);
       mbar_init(bar(bPfull + i), 4 * NSG); mbar_init(bar(bPdone + i), 1);
     }
-    for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), kNV); mbar_init(bar(bVdone + i), 1); }
+    for (int i = 0; i < kVB; i++) { mbar_init(bar(bVfull + i), kNV == 8 && kVB == 2 ? 4 : kNV); mbar_init(bar(bVdone + i), 1); }
     mbar_init(bar(bQfull), 4 * NSG); mbar_init(bar(bOdone), 1); mbar_init(bar(bEpi), 4 * NSG); mbar_init(bar(bVote), 4 * NSG);
     *abort_flag = 0;
     reinterpret_cast<int*>(sm + C::oVote)[0] = 0;
@@ -770,8 +770,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     UQ_PROF_FLUSH(2, kk == 0)
   } else if (warp >= kWarpV && warp < kWarpV + kNV) {
     // ================================================================= V decode -> shared memory (thread = key, or half a key with eight warps)
-    constexpr int kGPT = C::kGroups / (kNV / 4);        // scale groups per thread
-    const int vw = warp - kWarpV, kk = (vw & 3) * 32 + lane, gfirst = (vw >> 2) * kGPT;
+    // Eight warps with two V buffers: two groups of four take turns at the tiles (even tiles / buffer 0, odd tiles / buffer 1),
+    // a thread decoding its whole key.  A role's time per tile is mostly latency (waits, fences, dependent loads), which
+    // splitting a key between two threads does not shorten; two tiles in flight hide it.
+    constexpr bool kAlt = kNV == 8 && kVB == 2;
+    constexpr int kGPT = kAlt ? C::kGroups : C::kGroups / (kNV / 4);   // scale groups per thread
+    const int vw = warp - kWarpV, kk = (vw & 3) * 32 + lane, gfirst = kAlt ? 0 : (vw >> 2) * kGPT;
     UQ_PROF_DECL
     RingPos<kRawStages> rp;
     RingPos<kVB> vp;
@@ -782,6 +786,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       for (int t = sg.t0; t < sg.t1; t++, cnt++, rp.next(), vp.next()) {
+        if (kAlt && (cnt & 1) != (vw >> 2)) continue;   // the other group's tile
         const int stage = rp.slot, buf = vp.slot;
         ok = wait(bar_raw_full(stage), rp.phase, 50 + stage, cnt UQ_PROF_SITE(0));
         if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), vp.phase ^ 1u, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
