@@ -20,23 +20,59 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
   const int hk = h / x.G, r = j * x.G + (h % x.G);
   const int D = p.D;
   const size_t slot0 = uq_slot(p, b, hk, 0);
+  // The slots' log-sum-exps are read lane-parallel (slot s by lane s mod 32: up to four per lane for nsplit <= 128), so the
+  // row's maximum, weights and denominator cost a few loads instead of a serial chain of nsplit of them.
+  const int ns = x.ns_eff;
+  float lse[4], w[4];
   float mx = -INFINITY;
-  for (int s = 0; s < x.ns_eff; s++) mx = fmaxf(mx, p.ml[(slot0 + s) * x.BM + r]);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int s = lane + 32 * j;
+    lse[j] = s < ns ? p.ml[(slot0 + s) * x.BM + r] : -INFINITY;
+    mx = fmaxf(mx, lse[j]);
+  }
+#pragma unroll
+  for (int m = 16; m; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
   float acc[8];   // D <= 256: 8 channels per lane
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
   float den = 0.f;
   if (mx != -INFINITY) {
-    for (int s = 0; s < x.ns_eff; s++) {
-      const float lse = p.ml[(slot0 + s) * x.BM + r];
-      if (lse == -INFINITY) continue;   // an empty split never wrote its o
-      const float w = exp2f(lse - mx);
-      den += w;
-      const float* o = p.mo + ((slot0 + s) * x.BM + r) * (size_t)D;
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int d = lane + 32 * i;
-        if (d < D) acc[i] = fmaf(w, o[d], acc[i]);
+    for (int j = 0; j < 4; j++) {
+      w[j] = lse[j] == -INFINITY ? 0.f : exp2f(lse[j] - mx);   // an empty split never wrote its o
+      den += w[j];
+    }
+#pragma unroll
+    for (int m = 16; m; m >>= 1) den += __shfl_xor_sync(0xffffffffu, den, m);
+    for (int j = 0; j < 4 && 32 * j < ns; j++) {
+      const unsigned live = __ballot_sync(0xffffffffu, w[j] != 0.f);
+      for (unsigned rest = live; rest;) {
+        // up to four non-empty slots at a time: their loads are in flight together
+        int sl[4];
+        float ws[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          sl[u] = rest ? __ffs(rest) - 1 : -1;
+          if (rest) rest &= rest - 1;
+          ws[u] = __shfl_sync(0xffffffffu, w[j], sl[u] < 0 ? 0 : sl[u]);
+        }
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const float* o = p.mo + ((slot0 + 32 * j + (sl[u] < 0 ? 0 : sl[u])) * x.BM + r) * (size_t)D;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            v[u][i] = (sl[u] >= 0 && d < D) ? o[d] : 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          if (sl[u] < 0) continue;
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[i] = fmaf(ws[u], v[u][i], acc[i]);
+        }
       }
     }
   }

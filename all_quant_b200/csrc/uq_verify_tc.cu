@@ -41,6 +41,12 @@
 
 namespace tc {
 
+__device__ __forceinline__ unsigned long long now_ns_early() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 #ifdef UQ_TC_TRACE
 // timeline of CTA 0 (developer build only): clock64 stamps of each role's events for its first 64 tiles
 __device__ long long g_tc_trace[64][16];
@@ -51,11 +57,17 @@ __device__ long long g_tc_trace[64][16];
 #define UQ_TRACE_FROM 0
 #endif
 #define UQ_TRACE(ev, c) if (blockIdx.x == UQ_TRACE_CTA && (c) >= UQ_TRACE_FROM && (c) < UQ_TRACE_FROM + 64) g_tc_trace[(c) - UQ_TRACE_FROM][ev] = clock64();
+// per-CTA milestones (global timer, ns): 0 entry, 1 set-up done, 2 first tile's softmax done, 3 last tile's softmax done, 4 exit, 5 tiles, 6 segments
+__device__ unsigned long long g_tc_cta[160][8];
+#define UQ_TRACE_CTA_T(i) if (threadIdx.x == 0 && blockIdx.x < 160) g_tc_cta[blockIdx.x][i] = now_ns_early();
+#define UQ_TRACE_CTA_V(i, v) if (threadIdx.x == 0 && blockIdx.x < 160) g_tc_cta[blockIdx.x][i] = (unsigned long long)(v);
 // stamps of the softmax role's steps around a change of segment (rows 60-63 of the same table, one row per segment)
 #define UQ_TRACE_SEG(ev) if (blockIdx.x == UQ_TRACE_CTA && st == 0 && seg_i < 4) g_tc_trace[60 + seg_i][ev] = clock64();
 #else
 #define UQ_TRACE(ev, c)
 #define UQ_TRACE_SEG(ev)
+#define UQ_TRACE_CTA_T(i)
+#define UQ_TRACE_CTA_V(i, v)
 #endif
 #ifdef UQ_TC_PROF
 // per-role cycle counters (profiling build only): [role][0..5] cycles spent in the role's wait sites, [6] event count, [7] total cycles
@@ -431,17 +443,18 @@ struct Seg {
 };
 
 // The list is cut in WEIGHTED units: an item of n tiles counts n + kSegW, the extra units standing for what the start of
-// a segment costs (query conversion, first-tile reference, epilogue: about eight tiles' time), so that a CTA whose chunk
-// crosses into a second item gets correspondingly fewer tiles and all CTAs finish together.
-constexpr int kSegW = 8;
+// a segment costs (query conversion, first-tile reference, epilogue), so that a CTA whose chunk crosses into a second item
+// gets correspondingly fewer tiles and all CTAs finish together.  Measured from per-CTA exit times: about twelve tiles'
+// time at 64 rows, eight below.
+__host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? 12 : 8; }
 
 struct Walker {
   const int* prefix;   // prefix[b] = weighted units of sequences < b (one kv head): tiles + kSegW per non-empty sequence
-  int B, HKV, nitems, total, chunk, per_item;
+  int B, HKV, nitems, total, chunk, per_item, kSegW;
   int pos, end, it, cta;
 
-  UQ_DEV void init(const int* pre, int B_, int HKV_, int ns_eff, int chunk_min) {
-    prefix = pre; B = B_; HKV = HKV_; nitems = B * HKV; total = HKV * pre[B];
+  UQ_DEV void init(const int* pre, int B_, int HKV_, int ns_eff, int chunk_min, int seg_w) {
+    prefix = pre; B = B_; HKV = HKV_; nitems = B * HKV; total = HKV * pre[B]; kSegW = seg_w;
     cta = blockIdx.x;
     per_item = ns_eff < 2;
     if (per_item) { it = cta - (int)gridDim.x; pos = end = 0; chunk = 1; return; }
@@ -497,6 +510,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // declared 1024-byte aligned (swizzled tiles need it) and used without any integer arithmetic on the pointer, so that the
   // compiler keeps every access in the shared state space (ld.shared / st.shared instead of generic loads and stores)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  UQ_TRACE_CTA_T(0)
   const UQParams& p = prm.p;
   const UQLaunch& x = prm.x;
   uint8_t* sm = smem_raw;
@@ -561,7 +575,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     int off;
     const int n = uq_n_local(p, x, b, &off);
     const int tiles = (n + kKeys - 1) / kKeys;
-    prefix[b + 1] = tiles ? tiles + kSegW : 0;
+    prefix[b + 1] = tiles ? tiles + seg_weight(NT) : 0;
   }
   __syncthreads();
   if (tid == 0) {
@@ -576,6 +590,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sm + C::oTmemSlot);
+  UQ_TRACE_CTA_T(1)
 
   Walker wk;
   const int G = x.G, rows = x.rows;
@@ -590,7 +605,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   int mcur = 0, nvote = 0;         // softmax role: live copy of the double-buffered references, rendezvous count
   float csc0 = x.sc2;
   for (int pass = 0; pass < 2; pass++) {
-  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min);
+  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min, seg_weight(NT));
   int ord = -1;                    // ordinal of the segment in the CTA's list
   // does this pass run segment `ord`?  (pass 1: the marked ones)
   auto take = [&]() -> bool { ord++; return pass == 0 || (ord < 32 * kRedoWords && ((redo[ord >> 5] >> (ord & 31)) & 1u)); };
@@ -990,7 +1005,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       if (sg.t0 == 0)
         for (int i = st; i < (x.ns_eff - sg.nseg) * rows; i += kSm)
           p.ml[uq_slot(p, sg.b, sg.hk, sg.nseg + i / rows) * x.BM + i % rows] = -INFINITY;
-      ok = rendezvous(60, seg_i);   // references and sums initialised before anyone's first tile
+      // (no rendezvous here: the first tile reads none of these before the rendezvous of its reference move)
       UQ_TRACE_SEG(4)
       float l[HW];
 #pragma unroll
@@ -1048,6 +1063,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             fence_async_smem();
             warp_arrive(bar(bPfull + buf));
             if (st == 0) { UQ_TRACE(13, cnt) }
+            UQ_TRACE_CTA_T(3)
             if (++buf == kSB) { buf = 0; sph ^= 1u; }
           }
           if (!ok || t >= sg.t1) break;
@@ -1176,8 +1192,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
           ok = rendezvous(67, cnt);
           if (!ok) break;
+          if (!first) {
 #pragma unroll
-          for (int i = 0; i < HW; i++) l[i] *= fac_s[r0 + i];
+            for (int i = 0; i < HW; i++) l[i] *= fac_s[r0 + i];
+          }
           if (cnt > c0) {
             // O^T holds sums relative to the old references: wait for the tile before this one, then rescale this thread's part
             ok = wait(bar(bPdone + (cnt - 1) % kSB), ((cnt - 1) / kSB) & 1, 66, cnt UQ_PROF_SITE(0));
@@ -1207,6 +1225,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         fence_async_smem();
         warp_arrive(bar(bPfull + buf));   // P^T is written; it also tells the Q.K issuer that this slot's S^T is consumed
         if (st == 0) { UQ_TRACE(13, cnt) }
+        UQ_TRACE_CTA_T(3)
+        if (cnt == 0) { UQ_TRACE_CTA_T(2) }
         UQ_PROF_TB(5)
       }
       if (!ok) break;
@@ -1266,6 +1286,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   __syncthreads();
   if (*abort_flag || !*reinterpret_cast<volatile uint32_t*>(&redo[kRedoWords])) break;
   }
+  UQ_TRACE_CTA_T(4)
+  UQ_TRACE_CTA_V(5, cnt)
+  UQ_TRACE_CTA_V(6, seg_i)
   // ---- common exit: TMEM goes back before the CTA ends
   if (warp == kWarpMma) {
     tc_fence_after();
@@ -1352,6 +1375,11 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
 }  // namespace tc
 
 #ifdef UQ_TC_TRACE
+extern "C" int uqb_debug_tc_cta(unsigned long long* out1280) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out1280, tc::g_tc_cta, sizeof(unsigned long long) * 1280);
+  return (int)e;
+}
 extern "C" int uqb_debug_tc_trace(long long* out1024) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out1024, tc::g_tc_trace, sizeof(long long) * 1024);
