@@ -571,6 +571,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   }
   uint32_t* redo = reinterpret_cast<uint32_t*>(sm + C::oRedo);
   for (int i = tid; i <= kRedoWords; i += kThreads) redo[i] = 0u;
+  {
+    // the queries (B x K x Hq x D bf16, read once per segment by whichever CTA gets it) go to L2 now, a slice per CTA, while
+    // the set-up below runs: the first segment's conversion and every later one then find them there
+    const size_t lines = ((size_t)p.B * p.K * p.HQ * D * 2 + 127) / 128;
+    const char* qb = reinterpret_cast<const char*>(p.q);
+    for (size_t i = (size_t)blockIdx.x * kThreads + tid; i < lines; i += (size_t)gridDim.x * kThreads)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(qb + i * 128));
+  }
   for (int b = tid; b < p.B; b += kThreads) {   // tiles per sequence, then an in-place scan by one thread
     int off;
     const int n = uq_n_local(p, x, b, &off);
