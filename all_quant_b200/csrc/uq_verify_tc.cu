@@ -97,7 +97,7 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_NSG4_AT 32
 #endif
 #ifndef UQ_ABL
-#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no work in the softmax's common tile, 32 no V decode, 64 no scale relay
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no work in the softmax's common tile, 32 no V decode, 64 no scale relay, 128 / 256 / 512 softmax / V / relay reduced to their waits and arrivals
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
@@ -746,6 +746,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (ok && cnt >= kSB) ok = wait(bar(bSfull + buf), sp.phase ^ 1u, 44 + buf, cnt UQ_PROF_SITE(1));   // S^T of the tile that used this buffer is done: the A operand is free
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if ((UQ_ABL & 512) && cnt) { warp_arrive(bar(bKfull + buf)); warp_arrive(bar_raw_empty(stage)); continue; }
         tc_fence_after();
         if (kk == 0) { UQ_TRACE(1, cnt) }
         UQ_PROF_T0
@@ -815,6 +816,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (ok && cnt >= kVB) ok = wait(bar(bVdone + buf), vp.phase ^ 1u, 54 + buf, cnt UQ_PROF_SITE(1));   // O^T += of the tile that used this buffer is done
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if ((UQ_ABL & 256) && cnt) { warp_arrive(bar(bVfull + buf)); warp_arrive(bar_raw_empty(stage)); continue; }
         if (vw == 0 && lane == 0) { UQ_TRACE(3, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kOffVC;
@@ -1042,6 +1044,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             bool r = wait(bar(bSfull + buf), sph, 62 + buf, cnt UQ_PROF_SITE(0));
             r = __all_sync(0xffffffffu, r);
             if (!r) { ok = false; break; }
+            if (UQ_ABL & 128) { warp_arrive(bar(bPfull + buf)); if (++buf == kSB) { buf = 0; sph ^= 1u; } continue; }
             tc_fence_after();
             if (st == 0) { UQ_TRACE(9, cnt) }
             float pv[HW];
