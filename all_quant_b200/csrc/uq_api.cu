@@ -86,12 +86,14 @@ bool shape_ok(const UQParams& p) {
   return p.q && p.kc && p.ks && p.vc && p.vs && p.block_table && p.seq_lens && p.mo && p.ml;
 }
 
-cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s) {
+cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s, const int32_t* tree_mask = nullptr) {
   if (!shape_ok(p)) return cudaErrorInvalidValue;
+  if (tree_mask && p.K > 16) return cudaErrorInvalidValue;   // the reference's limit (uqmt/tree.py:135)
   if (!o_part && !p.out) return cudaErrorInvalidValue;
   if (p.B == 0) return cudaSuccess;
   UQLaunch x{};
   x.pos_offset = pos_offset;
+  x.tree_mask = tree_mask;
   x.G = p.HQ / p.HKV;
   x.rows = p.K * x.G;
   x.BM = uq_block_m(p.K, p.HQ, p.HKV);
@@ -168,6 +170,11 @@ int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const 
 int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, float* o_part, float* lse2_part, void* stream) {
   if (!p || !o_part || !lse2_part) return (int)cudaErrorInvalidValue;
   return (int)run(*p, pos_offset, o_part, lse2_part, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* stream) {
+  if (!p) return (int)cudaErrorInvalidValue;
+  return (int)run(*p, nullptr, nullptr, nullptr, reinterpret_cast<cudaStream_t>(stream), tree_mask);
 }
 
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16, void* stream) {

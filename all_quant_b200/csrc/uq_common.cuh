@@ -13,6 +13,7 @@
 // ---- what the host adds to UQParams for one launch -------------------------------------------------
 struct UQLaunch {
   const int32_t* pos_offset;  // [B] global position of shard-local key 0 (nullptr = 0)
+  const int32_t* tree_mask;   // [B, K] draft-visibility bitmasks of a tree-masked verify (nullptr = chain: draft j sees drafts 0..j)
   int ns_eff;                 // partial slots actually used per (sequence, kv head): <= p.nsplit
   int G;                      // Hq / Hkv
   int rows;                   // K * G query rows per (sequence, kv head)
@@ -33,6 +34,12 @@ UQ_DEV int uq_n_local(const UQParams& p, const UQLaunch& x, int b, int* off_out)
   long long nl = (long long)n - off;
   nl = nl < 0 ? 0 : (nl > cap ? cap : nl);
   return (int)nl;
+}
+
+// Does query (draft) j of sequence b see draft token t (the key at global position seq_len - K + t)?  Chain: t <= j.
+// Tree (reference uqmt/tree.py:9-12): bit t of tree_mask[b, j].
+UQ_DEV bool uq_sees_draft(const UQParams& p, const UQLaunch& x, int b, int j, int t) {
+  return x.tree_mask ? ((static_cast<unsigned>(__ldg(x.tree_mask + (size_t)b * p.K + j)) >> t) & 1u) != 0u : t <= j;
 }
 
 // ---- status record ------------------------------------------------------------------------------------

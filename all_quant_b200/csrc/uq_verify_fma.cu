@@ -99,8 +99,10 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
 #pragma unroll
         for (int r = 0; r < RC; r++) {
           const int rr = r0 + r;
-          const int lim = rr < x.rows ? n_glob - p.K + rr / x.G + 1 : 0;
-          p_s[r][tid] = (live && pos < lim) ? acc[r] * x.sc2 : -INFINITY;
+          // the committed prefix is visible to every row; a draft position to the rows whose query may attend it
+          const int td = pos - (n_glob - p.K);
+          const bool vis = live && rr < x.rows && pos < n_glob && (td < 0 || uq_sees_draft(p, x, b, rr / x.G, td));
+          p_s[r][tid] = vis ? acc[r] * x.sc2 : -INFINITY;
         }
       }
       __syncthreads();

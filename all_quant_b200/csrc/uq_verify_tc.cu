@@ -350,6 +350,20 @@ UQ_DEV float warp_fold(float* v, int lane) {
   return r;
 }
 
+// Which of the rows r0 .. r0 + n - 1 (row = draft j * G + head of the group) see draft token td of sequence b: bit i = row
+// r0 + i.  Out of line: it runs only in the one or two tiles of an item that hold the draft positions, and inlined it costs
+// the common tile registers.
+__device__ __noinline__ uint32_t draft_rows(const int32_t* tree_mask, int K, int b, int td, int r0, int n, int rows, int G) {
+  uint32_t m = 0u;
+  for (int i = 0; i < n; i++) {
+    const int r = r0 + i, j = r / G;
+    if (r >= rows) break;
+    const bool sees = tree_mask ? ((static_cast<unsigned>(__ldg(tree_mask + (size_t)b * K + j)) >> td) & 1u) != 0u : td <= j;
+    if (sees) m |= 1u << i;
+  }
+  return m;
+}
+
 // ---------------------------------------------------------------------------------------------- layout
 template <int D, int NT>
 struct Cfg {
@@ -395,7 +409,7 @@ struct Cfg {
   static constexpr int oMref = oMisc + 16;
   static constexpr int oWmax = oMref + 2 * NT * 4;
   static constexpr int oLsum = oWmax + 4 * NT * 4;
-  static constexpr int oFac = oLsum + NT * 4;
+  static constexpr int oFac = oLsum + 4 * NT * 4;        // (lsum: one partial per 32-key quarter and row, added in a fixed order)
   static constexpr int oFacO = oFac + NT * 4;            // per-row factor for O^T (row factor x V-reference factor)
   static constexpr int oWr = oFacO + NT * 4;             // [4] per-warp maxima of the keys' V reference bytes; [4..5] the segment's V reference byte (double buffered)
   static constexpr int oSfb = oWr + 32;                  // [2][NT][4] scale bytes of the two Q tiles (block-scaled path)
@@ -1006,7 +1020,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         }
       }
       // padding rows (no query behind them) get a reference of +1e30: their probabilities are 2^-inf = 0 without a select
-      if (st < NT) { mref[mcur * NT + st] = st < rows ? kNegBig : 1.0e30f; lsum[st] = 0.f; }
+      if (st < NT) { mref[mcur * NT + st] = st < rows ? kNegBig : 1.0e30f; }
       if (st == 0) wr[4 + mcur] = 0u;
       fence_async_smem();
       warp_arrive(bar(bQfull));
@@ -1025,7 +1039,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       // the common tiles
       int tmask;
       {
-        const int xq = n_glob - p.K - off - (kKeys - 1);
+        const int xq = n_glob - p.K - off - (kKeys - 1) - (x.tree_mask ? 1 : 0);
         tmask = min(n_loc / kKeys, xq < 0 ? 0 : xq / kKeys + 1);
       }
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
@@ -1092,14 +1106,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const int vref = (int)(rf >> 8);
         const float ck = C::kBS ? csc0 : csc0 * uq_scale_f32(rf & 0xFFu);   // block-scaled scores carry the keys' scales already
         // only a tile that reaches the end of the sequence or the draft positions needs masks (same answer in every thread)
-        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 > n_glob - p.K;
+        // (chain: draft token 0 is seen by every row, so the masks start at draft 1; a tree may hide draft 0 from some rows)
+        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 + (x.tree_mask ? 1 : 0) > n_glob - p.K;
         bool live = true;
-        int rmin = 0;   // rows r >= rmin see this key (causal limit among the drafts); none if past the end
+        uint32_t vmask = 0xFFFFFFFFu;   // bit i: row r0 + i sees this key
         if (need_mask) {
           const int key = t * kKeys + kk;
           live = key < n_loc;
-          if (!live) rmin = NT;
-          else { const int jmin = off + key - (n_glob - p.K); if (jmin > 0) rmin = jmin * G; }
+          const int td = off + key - (n_glob - p.K);   // >= 0: the key is draft token td
+          if (!live) vmask = 0u;
+          else if (td >= 0) vmask = draft_rows(x.tree_mask, p.K, sg.b, td, r0, HW, rows, G);
         }
         uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
         float pv[HW];
@@ -1110,7 +1126,6 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < HW; i++) {
             float xv = fmaf(pv[i], ck, (UQ_ABL & 4) ? -1.0f : -mrow[r0 + i]);
-            xv = (r0 + i >= rmin) ? xv : -INFINITY;
             xm = fmaxf(xm, xv);
             pv[i] = (UQ_ABL & 1) ? xv * 0.001f : fast_exp2(xv);
           }
@@ -1127,7 +1142,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
                 make_uint4(mul_f16x2(pack_f16x2(pv[8 * c], pv[8 * c + 1]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 2], pv[8 * c + 3]), vf),
                            mul_f16x2(pack_f16x2(pv[8 * c + 4], pv[8 * c + 5]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 6], pv[8 * c + 7]), vf));
         };
-        if (!(UQ_ABL & (8 | 16)) || cnt == c0) load_scores(s_addr, pv);
+        // scores of a masked tile: what a row does not see becomes -inf here, once (scale factors are positive, so it stays
+        // -inf; a dead key's score may be anything, NaN included)
+        auto load_masked = [&]() {
+          load_scores(s_addr, pv);
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < HW; i++) pv[i] = ((vmask >> i) & 1u) ? pv[i] : -INFINITY;
+          }
+        };
+        if (!(UQ_ABL & (8 | 16)) || cnt == c0) load_masked();
         else {
 #pragma unroll
           for (int i = 0; i < HW; i++) pv[i] = 0.5f;
@@ -1175,11 +1199,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           // ---- move the references (the first tile of a segment, then only on growth), rescale what was accumulated,
           // and redo this tile against the new references
           const float* mr = mref + mcur * NT;
-          if (!first) load_scores(s_addr, pv);   // (a first tile still holds the scores it loaded)
+          if (!first) load_masked();   // (a first tile still holds the scores it loaded)
           {
             float vv[HW];
 #pragma unroll
-            for (int i = 0; i < HW; i++) vv[i] = (!need_mask || r0 + i >= rmin) ? pv[i] * ck : -INFINITY;
+            for (int i = 0; i < HW; i++) vv[i] = pv[i] * ck;
             const float vmax = warp_fold<HW, true>(vv, lane);
             if ((lane & (32 / HW - 1)) == 0) wmax[quad * NT + r0 + warp_fold_row<HW>(lane)] = vmax;
           }
@@ -1223,7 +1247,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             }
           }
           mcur ^= 1;   // the next tile's rendezvous keeps fac / wmax / wr from being overwritten while still read
-          load_scores(s_addr, pv);
+          load_masked();
           probabilities(mref + mcur * NT);
           write_p((int)wr[4 + mcur]);
         }
@@ -1245,7 +1269,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       // ---- segment epilogue: row sums over the 128 keys, then O^T -> normalised partial
       {
         const float lw = warp_fold<HW, false>(l, lane);
-        if ((lane & (32 / HW - 1)) == 0) atomicAdd(&lsum[r0 + warp_fold_row<HW>(lane)], lw);
+        // one partial per warp (quarter of the keys) and row; the readers add the four in a fixed order, so that the result
+        // does not depend on which warp got there first
+        if ((lane & (32 / HW - 1)) == 0) lsum[quad * NT + r0 + warp_fold_row<HW>(lane)] = lw;
       }
       UQ_TRACE_SEG(6)
       ok = rendezvous(70, seg_i);
@@ -1271,7 +1297,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             for (int i = 0; i < HW; i++) {
               const int r = r0 + i;
               if (r < rows) {
-                const float lr = lsum[r];
+                const float lr = (lsum[r] + lsum[NT + r]) + (lsum[2 * NT + r] + lsum[3 * NT + r]);
                 bad |= !(fabsf(ov[i]) <= 3.0e38f) || !(lr <= 3.0e38f);
                 mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * __fdividef(osc, lr) : 0.f;
               }
@@ -1280,7 +1306,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         }
         // quick path: the segment's result is garbage then; the second pass computes it again on the careful path
         if (!careful && __any_sync(0xffffffffu, bad) && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
-        if (st < rows) { const float lr = lsum[st]; ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
+        if (st < rows) { const float lr = (lsum[st] + lsum[NT + st]) + (lsum[2 * NT + st] + lsum[3 * NT + st]); ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       }
       tc_fence_before();
       warp_arrive(bar(bEpi));

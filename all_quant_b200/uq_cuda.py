@@ -33,7 +33,7 @@ class UQParams(ctypes.Structure):
 
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
-           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_merge_launch", "uqb_last_status",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes")
 
@@ -56,6 +56,7 @@ def lib():
         L.uqb_append_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
         L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
         L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
+        L.uqb_tree_decode_launch.argtypes = [pp, vp, vp]
         L.uqb_last_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
         L.uqb_launch_count.restype = ctypes.c_ulonglong
         L.uqb_debug_events.argtypes = [vp, vp]
@@ -190,6 +191,69 @@ def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nspl
     bt = block_table.repeat_interleave(K, 0)
     sl = (seq_lens.repeat_interleave(K) - K + torch.arange(K, device=q.device).repeat(B) + 1).to(torch.int32)
     return e.decode(qs, kc, ks, vc, vs, bt, sl, nsplit, nwarps, stages, variant, mb, sm_scale, None, None, None, fmt, k_ts, v_ts).reshape(B, K, HQ, D)
+
+
+# ---- tree-masked verify (reference uqmt/tree.py) -------------------------------------------------------------------
+def chain_mask(K, B=None, device="cpu"):
+    """Bit t of entry j set for t <= j: the ordinary causal verify (reference uqmt/tree.py:27-29)."""
+    m = torch.tensor([(1 << (j + 1)) - 1 for j in range(K)], dtype=torch.int32, device=device)
+    return m if B is None else m.expand(B, K).contiguous()
+
+
+def parents_to_mask(parents):
+    """parents [..., K] (parents[j] < j, -1 = child of the committed prefix) -> int32 [..., K] ancestor-or-self
+    bitmasks (reference uqmt/tree.py:37-47)."""
+    p = torch.as_tensor(parents, dtype=torch.int64)
+    K = p.shape[-1]
+    m = torch.zeros_like(p)
+    for j in range(K):
+        par = p[..., j]
+        pm = torch.where(par >= 0, torch.gather(m, -1, par.clamp_min(0).unsqueeze(-1)).squeeze(-1), torch.zeros_like(par))
+        m[..., j] = pm | (1 << j)
+    return m.to(torch.int32)
+
+
+def star_mask(K, device="cpu"):
+    """Token 0 is the root draft, tokens 1..K-1 its children (reference uqmt/tree.py:32-34)."""
+    return parents_to_mask([-1] + [0] * (K - 1)).to(device)
+
+
+def uq_tree_decode(q, kc, ks, vc, vs, block_table, seq_lens, tree_mask=None, *, nsplit=None, sm_scale=None, out=None,
+                   workspace=None):
+    """Fused K-query verify with a per-sequence tree mask (reference uqmt/tree.py:130-166): the K tree tokens are the
+    last K cache positions; query j sees the committed prefix and tree token t iff bit t of tree_mask[b, j] is set.
+    tree_mask int32 [B,K] or [K] (broadcast), 1 <= K <= 16; None = chain = uq_decode_cuda.  Returns bf16 [B,K,Hq,D]."""
+    _need_cuda(q, kc, ks, vc, vs, block_table, seq_lens)
+    if q.dim() != 4 or q.dtype != torch.bfloat16:
+        raise RuntimeError("q must be bf16 [B,K,Hq,D]")
+    B, K, HQ, D = q.shape
+    if not 1 <= K <= 16:
+        raise RuntimeError("1 <= K <= 16")
+    if tree_mask is None:
+        return uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, nsplit=nsplit, sm_scale=sm_scale, out=out, workspace=workspace)
+    HKV = kc.shape[1]
+    sm_scale = sm_scale if sm_scale is not None else D ** -0.5
+    seq_lens = seq_lens.to(torch.int32)
+    block_table = block_table.to(torch.int32).contiguous()
+    q = q.contiguous()
+    tm = tree_mask.to(device=q.device, dtype=torch.int32)
+    tm = (tm.expand(B, K) if tm.dim() == 1 else tm).contiguous()
+    if nsplit is None:
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+    p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale)
+    L = lib()
+    n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
+    if workspace is None:
+        workspace = torch.empty(n_mo + n_ml, dtype=torch.float32, device=q.device)
+    if workspace.numel() < n_mo + n_ml:
+        raise RuntimeError("scratch too small")
+    if out is None:
+        out = torch.empty_like(q)
+    p.mo, p.ml, p.out = workspace.data_ptr(), workspace.data_ptr() + 4 * n_mo, out.data_ptr()
+    with torch.cuda.device(q.device):
+        err = L.uqb_tree_decode_launch(ctypes.byref(p), tm.data_ptr(), _stream(q))
+    _check(err, "uq_tree_decode_launch")
+    return out
 
 
 def uq_decode_static(q, kc, ks, vc, vs, block_table, seq_lens, out, *, nsplit=None, sm_scale=None):

@@ -56,6 +56,11 @@ int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const 
  * pos_offset == NULL means offset 0 (the shard is the whole context). */
 int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, float* o_part, float* lse2_part,
                               void* stream);
+/* Tree-masked verify (reference uqmt/tree.py:130-166 uq_tree_decode, oracle tree_reference :169-201; Triton only in the
+ * reference, no C++ entry point).  The K draft tokens of a sequence sit at its last K positions; query j sees the whole
+ * committed prefix and draft token t iff bit t of tree_mask[b*K + j] is set.  tree_mask: device int32 [B,K], K <= 16;
+ * NULL = the chain mask, i.e. uqb_decode_launch.  Everything else as uqb_decode_launch. */
+int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* stream);
 /* Log-sum-exp merge of R shards' partials: o_parts fp32 [R,rows,D], lse2_parts fp32 [R,rows]
  * -> out bf16 [rows,D]  (same arithmetic as the reference's in-GPU combine, cuda/uq_decode.cu:353-388). */
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16,

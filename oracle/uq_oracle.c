@@ -214,6 +214,78 @@ void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, cons
 }
 
 /*
+ * Tree-masked attention oracle (uqmt/tree.py:169-201).  Same caches and conventions as uqo_reference; the
+ * K draft tokens of sequence b sit at positions seq_len-K .. seq_len-1.  Query j sees every position
+ * below seq_len-K, and draft token t (position seq_len-K+t) iff bit t of tree_mask[b*K+j] is set.
+ * tree_mask = NULL is the chain mask (bit t set for t <= j): the ordinary causal op.  A row that sees
+ * nothing is zeros.
+ */
+void uqo_tree_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
+                        const int32_t* block_table, const int32_t* seq_lens, const int32_t* tree_mask, int B, int K,
+                        int HQ, int HKV, int D, int PAGE, int max_pages, float sm_scale, float* out) {
+  const int G = HQ / HKV, ng = D / 32;
+  memset(out, 0, sizeof(float) * (size_t)B * K * HQ * D);
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+  for (int b = 0; b < B; b++) {
+    for (int hk = 0; hk < HKV; hk++) {
+      const int n = seq_lens[b];
+      if (n <= 0) continue;
+      float* kd = (float*)malloc(sizeof(float) * (size_t)n * D);
+      float* vd = (float*)malloc(sizeof(float) * (size_t)n * D);
+      float* sc = (float*)malloc(sizeof(float) * (size_t)n);
+      unsigned char* vis = (unsigned char*)malloc((size_t)n);
+      for (int t = 0; t < n; t++) {
+        size_t row = ((size_t)block_table[(size_t)b * max_pages + t / PAGE] * HKV + hk) * PAGE + t % PAGE;
+        decode_row(kc + row * (D / 2), ks + row * ng, D, kd + (size_t)t * D);
+        decode_row(vc + row * (D / 2), vs + row * ng, D, vd + (size_t)t * D);
+      }
+      const int prefix = n - K;
+      for (int j = 0; j < K; j++) {
+        const uint32_t m = tree_mask ? (uint32_t)tree_mask[(size_t)b * K + j] : ((2u << j) - 1u);
+        int any = 0;
+        for (int t = 0; t < n; t++) {
+          vis[t] = t < prefix || (t >= prefix && ((m >> (t - prefix)) & 1u));
+          any |= vis[t];
+        }
+        if (!any) continue;
+        for (int g = 0; g < G; g++) {
+          const int h = hk * G + g;
+          const uint16_t* qr = q + (((size_t)b * K + j) * HQ + h) * D;
+          float qf[512];
+          for (int d = 0; d < D; d++) qf[d] = bf16_to_f32(qr[d]);
+          float mx = -INFINITY;
+          for (int t = 0; t < n; t++) {
+            if (!vis[t]) continue;
+            double acc = 0.0;
+            const float* kr = kd + (size_t)t * D;
+            for (int d = 0; d < D; d++) acc += (double)qf[d] * (double)kr[d];
+            float sv = (float)acc * sm_scale;
+            sc[t] = sv;
+            if (sv > mx) mx = sv;
+          }
+          double l = 0.0;
+          double od[512];
+          for (int d = 0; d < D; d++) od[d] = 0.0;
+          for (int t = 0; t < n; t++) {
+            if (!vis[t]) continue;
+            const double p = expf(sc[t] - mx);
+            l += p;
+            const float* vr = vd + (size_t)t * D;
+            for (int d = 0; d < D; d++) od[d] += p * (double)vr[d];
+          }
+          float* o = out + (((size_t)b * K + j) * HQ + h) * D;
+          for (int d = 0; d < D; d++) o[d] = (float)(od[d] / l);
+        }
+      }
+      free(kd);
+      free(vd);
+      free(sc);
+      free(vis);
+    }
+  }
+}
+
+/*
  * Merge of context-split partials (no reference twin; same math as the reference's in-GPU
  * split-KV combine, cuda/uq_decode.cu:353-388, in natural-log domain):
  *   out = sum_r exp(lse_r - max) * o_r / sum_r exp(lse_r - max);  all-(-inf) row -> 0.

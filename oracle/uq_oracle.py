@@ -40,6 +40,7 @@ def lib():
         L.uqo_append_kv.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
         L.uqo_reference.argtypes = [vp] * 9 + [i32] * 7 + [f32, vp, vp]
         L.uqo_merge.argtypes = [vp, vp, i32, sz, i32, vp]
+        L.uqo_tree_reference.argtypes = [vp] * 8 + [i32] * 7 + [f32, vp]
         _LIB = L
     return _LIB
 
@@ -110,6 +111,49 @@ def reference(q_bits, kc, ks, vc, vs, block_table, seq_lens, sm_scale=None, pos_
     lib().uqo_reference(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), _p(po), _p(nl),
                         B, K, HQ, HKV, D, PAGE, bt.shape[1], sm, _p(out), _p(lse))
     return (out, lse) if return_lse else out
+
+
+def chain_mask(K, B=None):
+    """Bit t of entry j set for t <= j: the ordinary causal verify (uqmt/tree.py:27-29)."""
+    m = np.array([(1 << (j + 1)) - 1 for j in range(K)], dtype=np.int32)
+    return m if B is None else np.ascontiguousarray(np.broadcast_to(m, (B, K)))
+
+
+def parents_to_mask(parents):
+    """parents [..., K] (parents[j] < j, -1 = child of the committed prefix) -> int32 [..., K] ancestor-or-self
+    bitmasks (uqmt/tree.py:37-47)."""
+    p = np.asarray(parents, dtype=np.int64)
+    K = p.shape[-1]
+    m = np.zeros_like(p)
+    for j in range(K):
+        par = p[..., j]
+        pm = np.where(par >= 0, np.take_along_axis(m, np.clip(par, 0, None)[..., None], -1)[..., 0], 0)
+        m[..., j] = pm | (1 << j)
+    return m.astype(np.int32)
+
+
+def star_mask(K):
+    """Token 0 is the root draft, tokens 1..K-1 its children (uqmt/tree.py:32-34)."""
+    return parents_to_mask([-1] + [0] * (K - 1))
+
+
+def tree_reference(q_bits, kc, ks, vc, vs, block_table, seq_lens, tree_mask=None, sm_scale=None):
+    """Tree-masked verify (uqmt/tree.py:169-201): tree_mask int32 [B,K] or [K] (broadcast), None = chain."""
+    q_bits = np.ascontiguousarray(q_bits, dtype=np.uint16)
+    B, K, HQ, D = q_bits.shape
+    _, HKV, PAGE, _ = kc.shape
+    bt = np.ascontiguousarray(block_table, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    tm = None
+    if tree_mask is not None:
+        tm = np.asarray(tree_mask, dtype=np.int32)
+        tm = np.ascontiguousarray(np.broadcast_to(tm, (B, K)))
+    kc, ks, vc, vs = (np.ascontiguousarray(a, dtype=np.uint8) for a in (kc, ks, vc, vs))
+    out = np.empty((B, K, HQ, D), np.float32)
+    sm = float(sm_scale) if sm_scale is not None else D ** -0.5
+    lib().uqo_tree_reference(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), _p(tm), B, K, HQ, HKV, D, PAGE,
+                             bt.shape[1], sm, _p(out))
+    return out
 
 
 def merge(o, lse):

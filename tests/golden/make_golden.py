@@ -7,7 +7,8 @@ Two kinds of fixture:
       repacked unchanged into one compressed file per case set.
   gen_*.npz   inputs and outputs of the reference's Python functions run here
       (uqmt.attn.quantize_fp4 / dequantize_fp4 / reference / build_paged_cache,
-       uqmt.vllm_adapter.append_kv), for the cases the frozen vectors do not cover.
+       uqmt.vllm_adapter.append_kv, uqmt.tree.tree_reference), for the cases the frozen vectors do not cover.
+`--tree-only` regenerates tree_cases.npz alone.
 """
 import os
 import sys
@@ -15,7 +16,8 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+_args = [a for a in sys.argv[1:] if not a.startswith("--")]
+REF = _args[0] if _args else "/root/reference"
 OUT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REF)
 from uqmt.attn import build_paged_cache, dequantize_fp4, quantize_fp4, reference  # noqa: E402
@@ -178,9 +180,48 @@ def gen_append():
          kc1=kc.numpy(), ks1=ks.numpy(), vc1=vc.numpy(), vs1=vs.numpy())
 
 
+def gen_tree():
+    """Tree-masked verify: answers of the reference's own oracle (uqmt/tree.py tree_reference) for chain, star and seeded
+    random parent trees, one case with a different tree per sequence.  One file, cases t0..tN."""
+    from uqmt.tree import chain_mask, parents_to_mask, star_mask, tree_reference
+    specs = [  # B, K, HQ, HKV, D, PAGE, seq_lens, seed, kind
+        (2, 4, 8, 2, 128, 64, [300, 129], 2001, "chain"),
+        (2, 8, 16, 2, 128, 64, [515, 70], 2002, "star"),
+        (3, 8, 16, 2, 128, 64, [400, 128, 9], 2003, "random"),     # K x G = 64 rows, a sequence of K + 1 tokens
+        (2, 6, 8, 4, 64, 16, [77, 200], 2004, "random"),
+        (2, 16, 4, 2, 128, 32, [260, 17], 2005, "random"),          # K = 16: the widest mask
+        (1, 5, 8, 2, 128, 64, [3], 2006, "random"),                 # fewer tokens than drafts
+    ]
+    arrs = {"n": np.array([len(specs)], np.int32)}
+    for i, (B, K, HQ, HKV, D, PAGE, lens, seed, kind) in enumerate(specs):
+        g = torch.Generator().manual_seed(seed)
+        T = max(max(lens), 1)
+        chan = torch.exp(0.5 * torch.randn(1, HKV, 1, D, generator=g))
+        k = torch.randn(B, HKV, T, D, generator=g) * chan
+        v = torch.randn(B, HKV, T, D, generator=g)
+        q = torch.randn(B, K, HQ, D, generator=g).bfloat16()
+        c = build_paged_cache(k, v, page_size=PAGE, seq_lens=lens, shuffle=True, generator=g)
+        if kind == "chain":
+            tm = chain_mask(K, B)
+        elif kind == "star":
+            tm = star_mask(K).expand(B, K).contiguous()
+        else:
+            rng = np.random.default_rng(seed)
+            tm = parents_to_mask(np.stack([[-1] + [int(rng.integers(-1, j)) for j in range(1, K)] for _ in range(B)]))
+        ref = tree_reference(q, c.kc, c.ks, c.vc, c.vs, c.block_table, c.seq_lens, tm)
+        arrs.update({f"t{i}_meta": np.array([B, K, HQ, HKV, D, PAGE], np.int32), f"t{i}_kc": c.kc.numpy(), f"t{i}_ks": c.ks.numpy(),
+                     f"t{i}_vc": c.vc.numpy(), f"t{i}_vs": c.vs.numpy(), f"t{i}_bt": c.block_table.numpy(), f"t{i}_sl": c.seq_lens.numpy(),
+                     f"t{i}_q": bits(q), f"t{i}_tm": tm.numpy().astype(np.int32), f"t{i}_ref": ref.numpy()})
+    save("tree_cases.npz", **arrs)
+
+
 if __name__ == "__main__":
+    if "--tree-only" in sys.argv:
+        gen_tree()
+        sys.exit(0)
     repack_cuda_vectors()
     repack_sycl_vectors()
     gen_codec()
     gen_cases()
     gen_append()
+    gen_tree()

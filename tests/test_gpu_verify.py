@@ -124,6 +124,15 @@ def test_late_outliers_take_the_second_pass():
         check_close(out.float().cpu().numpy() / mx, ref / mx, f"late outliers nsplit={nsplit}")
 
 
+def test_repeated_calls_are_bitwise_identical():
+    """No result depends on which warp or CTA got somewhere first: the same call gives the same bits."""
+    c = [x for x in CASES if x.name == "ref_cuda_main_K8"][0]
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    args = (dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt), dev(c.sl))
+    outs = [uq_cuda.uq_decode_cuda(q, *args, nsplit=4).clone() for _ in range(6)]
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
 def test_unserved_shapes_answer_invalid_value_before_any_work():
     c = [x for x in CASES if x.name == "ref_cuda_main_K1"][0]
     q = dev(c.q.view(np.int16), torch.bfloat16)
