@@ -413,8 +413,8 @@ def context_shard(block_table, rank, world, page_size):
 
 def uq_decode_context_split(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, *, group=None, nsplit=None, sm_scale=None,
                             partial_fn=None, merge_fn=None):
-    """Mode (b) on one rank: attention over this rank's context shard, an all-gather of the partials (o fp32 [B,K,Hq,D] and
-    lse2 fp32 [B,K,Hq] per rank: K*Hq*(D+1) floats per sequence) over `group`, then the log-sum-exp merge.  Every rank
+    """Mode (b) on one rank: attention over this rank's context shard, one all-gather of the partials (o fp32 [B,K,Hq,D] and
+    lse2 fp32 [B,K,Hq] per rank, packed: K*Hq*(D+1) floats per sequence) over `group`, then the log-sum-exp merge.  Every rank
     returns the full bf16 output.  partial_fn / merge_fn default to the CUDA entry points; the CPU tests of the host logic
     substitute the oracle for them."""
     import torch.distributed as dist
@@ -422,8 +422,12 @@ def uq_decode_context_split(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_
     merge_fn = merge_fn or uq_merge
     o, lse = partial_fn(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, nsplit=nsplit, sm_scale=sm_scale)
     world = dist.get_world_size(group)
-    o_all = torch.empty((world * o.shape[0],) + tuple(o.shape[1:]), dtype=o.dtype, device=o.device)       # ranks concatenated along dim 0
-    l_all = torch.empty((world * lse.shape[0],) + tuple(lse.shape[1:]), dtype=lse.dtype, device=lse.device)
-    dist.all_gather_into_tensor(o_all, o.contiguous(), group=group)
-    dist.all_gather_into_tensor(l_all, lse.contiguous(), group=group)
-    return merge_fn(o_all.view((world,) + tuple(o.shape)), l_all.view((world,) + tuple(lse.shape)))
+    # one collective instead of two: this rank's partials travel as one flat buffer (o, then lse2)
+    n_o, n_l = o.numel(), lse.numel()
+    mine = torch.cat([o.reshape(-1), lse.reshape(-1)])
+    both = torch.empty(world * (n_o + n_l), dtype=mine.dtype, device=mine.device)
+    dist.all_gather_into_tensor(both, mine, group=group)
+    both = both.view(world, n_o + n_l)
+    o_all = both[:, :n_o].contiguous().view((world,) + tuple(o.shape))
+    l_all = both[:, n_o:].contiguous().view((world,) + tuple(lse.shape))
+    return merge_fn(o_all, l_all)

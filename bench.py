@@ -281,7 +281,12 @@ def run_ours(args, cfg):
         raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    json_fd = 1
     if world > 1:
+        # the one JSON line must be alone on stdout: libraries of the multi-GPU run (NCCL's version banner) write there too,
+        # so stdout proper is kept aside for the line and everything else goes to stderr
+        json_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     K = args.kq
     B, HQ, HKV, D, PAGE, layers = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE", "layers"))
@@ -492,7 +497,7 @@ def run_ours(args, cfg):
         d = np.abs(got - ref0)
         line["parity"] = {"max_abs_err": float(d.max()), "mean_abs_err": float(d.mean()), "max_abs_ref": float(np.abs(ref0).max()),
                           "ok": bool(d.max() <= 1e-2 * np.abs(ref0).max() and d.mean() <= 1e-3), "checked": "sequence 0 vs CPU oracle"}
-    print(json.dumps(line))
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 
