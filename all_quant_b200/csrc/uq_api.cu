@@ -31,6 +31,7 @@ bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
 int uq_verify_tc_splits(const UQParams&, const UQLaunch&);
 cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, cudaStream_t);
 cudaError_t uq_merge_dispatch(const float*, const float*, int, size_t, int, void*, cudaStream_t);
+cudaError_t uq_merge_packed_dispatch(const float*, int, size_t, int, void*, cudaStream_t);
 
 namespace {
 
@@ -170,6 +171,12 @@ int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const 
 int uqb_decode_partial_launch(const UQParams* p, const int32_t* pos_offset, float* o_part, float* lse2_part, void* stream) {
   if (!p || !o_part || !lse2_part) return (int)cudaErrorInvalidValue;
   return (int)run(*p, pos_offset, o_part, lse2_part, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int uqb_merge_packed_launch(const float* packed, int R, size_t rows, int D, void* out_bf16, void* stream) {
+  cudaError_t e = uq_merge_packed_dispatch(packed, R, rows, D, out_bf16, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && rows > 0) g_launches += 1;
+  return (int)e;
 }
 
 int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* stream) {

@@ -94,25 +94,26 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
   }
 }
 
-// Merge of R shards: o [R, rows, D], lse2 [R, rows] -> bf16 [rows, D].
+// Merge of R shards: o [R, rows, D], lse2 [R, rows] -> bf16 [rows, D].  The shards may be apart by any stride (in floats):
+// rows * D and rows for two plain arrays, rows * (D + 1) for both when every shard is one packed buffer (o, then lse2).
 __global__ void __launch_bounds__(128) uq_merge_kernel(const float* __restrict__ o, const float* __restrict__ lse, int R, size_t rows, int D,
-                                                       __nv_bfloat16* __restrict__ out) {
+                                                       size_t o_stride, size_t l_stride, __nv_bfloat16* __restrict__ out) {
   const size_t row = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   float mx = -INFINITY;
-  for (int r = 0; r < R; r++) mx = fmaxf(mx, lse[(size_t)r * rows + row]);
+  for (int r = 0; r < R; r++) mx = fmaxf(mx, lse[(size_t)r * l_stride + row]);
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
   float den = 0.f;
   if (mx != -INFINITY) {
     for (int r = 0; r < R; r++) {
-      const float l = lse[(size_t)r * rows + row];
+      const float l = lse[(size_t)r * l_stride + row];
       if (l == -INFINITY) continue;
       const float w = exp2f(l - mx);
       den += w;
-      const float* src = o + ((size_t)r * rows + row) * D;
+      const float* src = o + (size_t)r * o_stride + row * D;
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const int d = lane + 32 * i;
@@ -143,6 +144,15 @@ cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_p
 cudaError_t uq_merge_dispatch(const float* o, const float* lse, int R, size_t rows, int D, void* out, cudaStream_t s) {
   if (!o || !lse || !out || R < 1 || D < 32 || D > 256 || D % 32) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
-  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, lse, R, rows, D, reinterpret_cast<__nv_bfloat16*>(out));
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, lse, R, rows, D, rows * D, rows, reinterpret_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError();
+}
+
+// packed [R][rows * D + rows]: shard r's partial outputs, then its lse2 values (what one all-gather of per-rank buffers gives)
+cudaError_t uq_merge_packed_dispatch(const float* packed, int R, size_t rows, int D, void* out, cudaStream_t s) {
+  if (!packed || !out || R < 1 || D < 32 || D > 256 || D % 32) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const size_t stride = rows * D + rows;
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(packed, packed + rows * D, R, rows, D, stride, stride, reinterpret_cast<__nv_bfloat16*>(out));
   return cudaGetLastError();
 }

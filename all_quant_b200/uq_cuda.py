@@ -33,7 +33,7 @@ class UQParams(ctypes.Structure):
 
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
-           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_last_status",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes")
 
@@ -57,6 +57,7 @@ def lib():
         L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
         L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
         L.uqb_tree_decode_launch.argtypes = [pp, vp, vp]
+        L.uqb_merge_packed_launch.argtypes = [vp, i, sz, i, vp, vp]
         L.uqb_last_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
         L.uqb_launch_count.restype = ctypes.c_ulonglong
         L.uqb_debug_events.argtypes = [vp, vp]
@@ -322,7 +323,8 @@ def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):
     _check(err, "uq_append_launch")
 
 
-def uq_decode_partial(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset=None, *, nsplit=None, sm_scale=None, workspace=None):
+def uq_decode_partial(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset=None, *, nsplit=None, sm_scale=None, workspace=None,
+                      into=None):
     """Attention over one context shard (the cache and block_table hold only this shard's pages; shard-local key 0 of
     sequence b is global position pos_offset[b]; seq_lens are global).  Returns (o fp32 [B,K,Hq,D] normalised,
     lse2 fp32 [B,K,Hq] in the log2 domain, -inf for rows that see nothing here).  Not in the reference."""
@@ -343,8 +345,12 @@ def uq_decode_partial(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset=None,
     if workspace.numel() < n_mo + n_ml:
         raise RuntimeError("scratch too small")
     p.mo, p.ml = workspace.data_ptr(), workspace.data_ptr() + 4 * n_mo
-    o = torch.empty(B, K, HQ, D, dtype=torch.float32, device=q.device)
-    lse = torch.empty(B, K, HQ, dtype=torch.float32, device=q.device)
+    if into is not None:   # one packed fp32 buffer of B*K*Hq*(D+1) floats: o, then lse2 (what uq_merge_packed takes)
+        n_o = B * K * HQ * D
+        o, lse = into[:n_o].view(B, K, HQ, D), into[n_o: n_o + B * K * HQ].view(B, K, HQ)
+    else:
+        o = torch.empty(B, K, HQ, D, dtype=torch.float32, device=q.device)
+        lse = torch.empty(B, K, HQ, dtype=torch.float32, device=q.device)
     po = None if pos_offset is None else pos_offset.to(torch.int32).contiguous()
     with torch.cuda.device(q.device):
         err = L.uqb_decode_partial_launch(ctypes.byref(p), None if po is None else po.data_ptr(), o.data_ptr(), lse.data_ptr(), _stream(q))
@@ -363,6 +369,17 @@ def uq_merge(o_parts, lse2_parts, out=None):
     with torch.cuda.device(o_parts.device):
         err = lib().uqb_merge_launch(o_parts.data_ptr(), lse2_parts.data_ptr(), R, rows, D, out.data_ptr(), _stream(o_parts))
     _check(err, "uq_merge_launch")
+    return out
+
+
+def uq_merge_packed(packed, rows, D, out):
+    """Merge of R shards whose partials are packed buffers (o [rows,D], then lse2 [rows]): packed fp32 [R, rows*(D+1)] ->
+    out bf16 [..., D] with rows rows.  Not in the reference."""
+    _need_cuda(packed, out)
+    packed = packed.contiguous()
+    with torch.cuda.device(packed.device):
+        err = lib().uqb_merge_packed_launch(packed.data_ptr(), packed.shape[0], rows, D, out.data_ptr(), _stream(packed))
+    _check(err, "uq_merge_packed_launch")
     return out
 
 
@@ -418,6 +435,17 @@ def uq_decode_context_split(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_
     returns the full bf16 output.  partial_fn / merge_fn default to the CUDA entry points; the CPU tests of the host logic
     substitute the oracle for them."""
     import torch.distributed as dist
+    if partial_fn is None and merge_fn is None:
+        # the CUDA path: the partial kernel writes this rank's packed buffer, one all-gather, the merge reads the gathered
+        # buffers where they are
+        B, K, HQ, D = q.shape
+        world = dist.get_world_size(group)
+        n = B * K * HQ * (D + 1)
+        mine = torch.empty(n, dtype=torch.float32, device=q.device)
+        uq_decode_partial(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, nsplit=nsplit, sm_scale=sm_scale, into=mine)
+        both = torch.empty(world * n, dtype=torch.float32, device=q.device)
+        dist.all_gather_into_tensor(both, mine, group=group)
+        return uq_merge_packed(both.view(world, n), B * K * HQ, D, torch.empty_like(q))
     partial_fn = partial_fn or uq_decode_partial
     merge_fn = merge_fn or uq_merge
     o, lse = partial_fn(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, nsplit=nsplit, sm_scale=sm_scale)

@@ -65,6 +65,9 @@ int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* st
  * -> out bf16 [rows,D]  (same arithmetic as the reference's in-GPU combine, cuda/uq_decode.cu:353-388). */
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16,
                      void* stream);
+/* The same merge when every shard's partials are one packed buffer, o [rows,D] followed by lse2 [rows] (what one
+ * all-gather of the ranks' buffers gives): packed fp32 [R][rows*D + rows].  No counterpart in the reference. */
+int uqb_merge_packed_launch(const float* packed, int R, size_t rows, int D, void* out_bf16, void* stream);
 
 /* ---- the launch for callers that may not allocate (no counterpart in the reference) ---------- */
 

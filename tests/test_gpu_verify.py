@@ -174,3 +174,15 @@ def test_context_split_partials_merge_to_the_unsplit_answer(R):
         ls_.append(l)
     out = uq_cuda.uq_merge(torch.stack(os_), torch.stack(ls_))
     check_close(out.float().cpu().numpy(), c.ref, f"merge R={R}")
+    # the packed form (what one all-gather of per-rank buffers gives): same shards, same bits
+    B, K, HQ, D = q.shape
+    n = B * K * HQ * (D + 1)
+    packed = torch.empty(R, n, dtype=torch.float32, device="cuda")
+    for r in range(R):
+        lo, hi = min(r * per, c.max_pages), min((r + 1) * per, c.max_pages)
+        bt = np.zeros((c.B, max(per, 1)), np.int32)
+        bt[:, : hi - lo] = c.bt[:, lo:hi]
+        off = np.full(c.B, lo * c.PAGE, np.int32)
+        uq_cuda.uq_decode_partial(q, dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(bt), dev(c.sl), dev(off), into=packed[r])
+    out2 = uq_cuda.uq_merge_packed(packed, B * K * HQ, D, torch.empty_like(q))
+    assert torch.equal(out2, out)
