@@ -78,7 +78,7 @@ int sm_count() {
 }
 
 bool shape_ok(const UQParams& p) {
-  if (p.fmt != 0) return false;   // NVFP4 is not served
+  if (p.fmt != 0 && p.fmt != 1) return false;   // 0 UltraQuant, 1 NVFP4 (CUDA-core kernel only)
   if (p.B < 0 || p.K < 1 || p.HQ < 1 || p.HKV < 1 || p.HQ % p.HKV) return false;
   if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
   if (p.PAGE < 1 || p.max_pages < 0) return false;
@@ -98,7 +98,9 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
   x.G = p.HQ / p.HKV;
   x.rows = p.K * x.G;
   x.BM = uq_block_m(p.K, p.HQ, p.HKV);
-  x.sc2 = p.sm_scale * 1.4426950408889634f;
+  // NVFP4 (reference cuda/uq_decode.cu:604,384): k_ts is folded into the softmax scale, v_ts multiplies the output
+  x.sc2 = p.sm_scale * (p.fmt == 1 ? p.k_ts : 1.f) * 1.4426950408889634f;
+  x.out_scale = p.fmt == 1 ? p.v_ts : 1.f;
   x.status = status_ptr();
   if (!x.status) return cudaErrorInitializationError;
   const int forced = forced_path();

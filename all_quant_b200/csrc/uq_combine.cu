@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
       }
     }
   }
-  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const float inv = (den > 0.f ? 1.f / den : 0.f) * x.out_scale;
   if (kPartialOut) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {

@@ -18,7 +18,8 @@ struct UQLaunch {
   int G;                      // Hq / Hkv
   int rows;                   // K * G query rows per (sequence, kv head)
   int BM;                     // row stride of the scratch (uq_block_m)
-  float sc2;                  // sm_scale * log2(e): scores live in the exp2 domain
+  float sc2;                  // sm_scale * log2(e) (times k_ts for an NVFP4 cache): scores live in the exp2 domain
+  float out_scale;            // multiplies the normalised output: 1, or v_ts for an NVFP4 cache
   unsigned int* status;       // this device's status record (4 words), see uq_report
 };
 
@@ -57,6 +58,14 @@ UQ_DEV void uq_report(unsigned int* status, unsigned code, unsigned bar, unsigne
 // (the reference's torch.exp2 does the same).
 UQ_DEV float uq_scale_f32(unsigned s) {
   return s == 0 ? __int_as_float(0x00400000) : (s == 255 ? __int_as_float(0x7f800000) : __int_as_float((int)(s << 23)));
+}
+
+// NVFP4 block scale: e4m3fn byte -> fp32 (reference uqmt/quant.py:139-147 reads it with torch's float8_e4m3fn -> float).
+// The low seven bits moved up by seven are an fp16 with the same mantissa and an exponent bias of 15 instead of 7, so one
+// conversion and a multiply by 2^8 give the value, subnormals included; 0x7f / 0xff are the format's NaN.
+UQ_DEV float uq_e4m3_f32(unsigned b) {
+  const float v = __half2float(__ushort_as_half((unsigned short)(((b & 0x80u) << 8) | ((b & 0x7fu) << 7)))) * 256.f;
+  return (b & 0x7fu) == 0x7fu ? __int_as_float(0x7fc00000) : v;
 }
 
 // e2m1 nibble -> exact fp32 value: (sign | code3 << 22) read as fp32 is value * 2^-126 (a denormal for

@@ -12,15 +12,20 @@
 //   phase 2  warp = row:     running max / sum in the exp2 domain, scores -> probabilities in place.
 //   phase 3  thread = channel pair: P.V with the value bytes read coalesced, decoded in registers.
 // Each (sequence, kv head, split) writes a normalised partial (o, m + log2 l) to the caller's scratch.
+//
+// FMT 0 is the UltraQuant cache (one UE8M0 scale byte per 32 channels).  FMT 1 is the NVFP4 cache (reference
+// uqmt/nvfp4.py:257-278, cuda/uq_decode.cu:604,384): one e4m3fn scale byte per 16 channels; the per-tensor scales
+// are not applied here: k_ts rides in the softmax scale and v_ts multiplies the combined output.
 #include "uq_common.cuh"
 
 namespace {
 
 constexpr int kTile = 128;   // keys per tile = threads per CTA
 
-template <int D, int RC>
+template <int D, int RC, int FMT>
 __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, const UQLaunch x) {
-  constexpr int NG = D / 32;            // scale groups per row
+  constexpr int NG = D / 32;            // 16-byte code groups per row
+  constexpr int NS = FMT ? D / 16 : D / 32;   // scale bytes per row
   constexpr int KPAR = 256 / D < 1 ? 1 : 256 / D;   // key phases in P.V: threads / (D/2) = 128 / (D/2)
   const int s = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -72,14 +77,16 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
           const size_t row = ((size_t)p.block_table[(size_t)b * p.max_pages + key / p.PAGE] * p.HKV + hk) * p.PAGE + key % p.PAGE;
           row_s[tid] = row;
           const uint4* codes = reinterpret_cast<const uint4*>(p.kc + row * (D / 2));
-          const uint8_t* sc = p.ks + row * NG;
+          const uint8_t* sc = p.ks + row * NS;
 #pragma unroll
           for (int g = 0; g < NG; g++) {
             const uint4 c4 = __ldg(codes + g);
-            const float scale = uq_scale_f32(__ldg(sc + g));
+            const float sc_lo = FMT ? uq_e4m3_f32(__ldg(sc + 2 * g)) : uq_scale_f32(__ldg(sc + g));
+            const float sc_hi = FMT ? uq_e4m3_f32(__ldg(sc + 2 * g + 1)) : sc_lo;
             const unsigned w[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
             for (int wi = 0; wi < 4; wi++) {
+              const float scale = wi < 2 ? sc_lo : sc_hi;
               float f[8];
 #pragma unroll
               for (int i = 0; i < 8; i++) f[i] = uq_e2m1_f32((w[wi] >> (4 * i)) & 0xFu) * scale;
@@ -138,7 +145,7 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
         for (int kk = kpar; kk < kend; kk += KPAR) {
           const size_t row = row_s[kk];
           const unsigned byte = __ldg(p.vc + row * (D / 2) + dbyte);
-          const float scale = uq_scale_f32(__ldg(p.vs + row * NG + dbyte / 16));
+          const float scale = FMT ? uq_e4m3_f32(__ldg(p.vs + row * NS + dbyte / 8)) : uq_scale_f32(__ldg(p.vs + row * NS + dbyte / 16));
           const float v0 = uq_e2m1_f32(byte & 0xFu) * scale, v1 = uq_e2m1_f32(byte >> 4) * scale;
 #pragma unroll
           for (int r = 0; r < RC; r++) {
@@ -188,14 +195,19 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
   }
 }
 
-template <int D>
-cudaError_t launch_d(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
+template <int D, int FMT>
+cudaError_t launch_f(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   const dim3 grid(x.ns_eff, p.HKV, p.B);
   if (x.rows <= 4)
-    uq_verify_fma_kernel<D, 4><<<grid, kTile, 0, s>>>(p, x);
+    uq_verify_fma_kernel<D, 4, FMT><<<grid, kTile, 0, s>>>(p, x);
   else
-    uq_verify_fma_kernel<D, 8><<<grid, kTile, 0, s>>>(p, x);
+    uq_verify_fma_kernel<D, 8, FMT><<<grid, kTile, 0, s>>>(p, x);
   return cudaGetLastError();
+}
+
+template <int D>
+cudaError_t launch_d(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
+  return p.fmt == 1 ? launch_f<D, 1>(p, x, s) : launch_f<D, 0>(p, x, s);
 }
 
 }  // namespace

@@ -1435,6 +1435,7 @@ extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
 #endif
 
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
+  if (p.fmt != 0) return false;   // the NVFP4 cache is served by the CUDA-core kernel
   if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
   if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;

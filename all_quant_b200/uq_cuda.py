@@ -121,6 +121,10 @@ class _Ext:
         if bt.dtype != torch.int32 or sl.dtype != torch.int32:
             raise RuntimeError("bt/sl must be int32")
         _need_cuda(kc, ks, vc, vs, bt, sl)
+        if int(fmt) in (0, 1):   # the kernels read D/32 (UltraQuant) or D/16 (NVFP4) scale bytes per row: refuse a cache of the other kind
+            per_row = q.shape[-1] // (16 if int(fmt) == 1 else 32)
+            if ks.shape[-1] != per_row or vs.shape[-1] != per_row:
+                raise RuntimeError(f"scale tensors hold {ks.shape[-1]} / {vs.shape[-1]} bytes per row, fmt={int(fmt)} needs {per_row}")
         p = _params(q, kc, ks, vc, vs, bt, sl, nsplit, sm_scale, variant, mb, fmt, k_ts, v_ts)
         L = lib()
         n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
@@ -165,7 +169,8 @@ def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nspl
                    sm_scale=None, out=None, fmt=0, k_ts=1.0, v_ts=1.0, workspace=None):
     """Fused K-query verify attention over the paged FP4 cache (reference cuda/uq_cuda.py:40-61).
 
-    q bf16 [B,K,Hq,D]; kc/vc uint8 [pages,Hkv,PAGE,D/2]; ks/vs uint8 [pages,Hkv,PAGE,D/32]; block_table
+    q bf16 [B,K,Hq,D]; kc/vc uint8 [pages,Hkv,PAGE,D/2]; ks/vs uint8 [pages,Hkv,PAGE,D/32] (fmt=1, the NVFP4 cache:
+    e4m3fn bytes [pages,Hkv,PAGE,D/16] and the per-tensor scales k_ts / v_ts, reference uqmt/nvfp4.py:257-278); block_table
     int [B,max_pages]; seq_lens int [B] including the K draft tokens.  Returns bf16 [B,K,Hq,D].
     fused=False is the reference's no-sharing mode: K independent single-query problems over B*K
     pseudo-sequences (the cache is read K times)."""

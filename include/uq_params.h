@@ -22,8 +22,8 @@ typedef struct UQParams {
   float sm_scale;
   int variant;                /* kernel selector of the reference (0..4): accepted, ignored */
   int mb;                     /* tuning hint of the reference: accepted, ignored */
-  int fmt;                    /* 0 = UE8M0 scale per 32 channels (served); 1 = NVFP4 (not served: invalid value) */
-  float k_ts, v_ts;           /* fmt 1 only */
+  int fmt;                    /* 0 = UE8M0 scale per 32 channels; 1 = NVFP4: e4m3fn scale per 16 channels (ks/vs [.., D/16]) */
+  float k_ts, v_ts;           /* fmt 1 only: k_ts scales the scores, v_ts the output (1.0 = none) */
 } UQParams;
 
 #endif

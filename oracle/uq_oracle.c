@@ -135,6 +135,32 @@ static void decode_row(const uint8_t* codes, const uint8_t* scales, int D, float
   }
 }
 
+/* NVFP4 row (uqmt/quant.py:139-147 dequantize_nvfp4, uqmt/nvfp4.py:206-208): e2m1 value times
+ * (e4m3fn scale of its 16-channel block, as fp32, times the per-tensor fp32 scale). */
+static float e4m3fn_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v = e == 0 ? ldexpf((float)m, -9) : ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  if (e == 15 && m == 7) v = NAN;
+  return (b & 0x80) ? -v : v;
+}
+/* All 256 e4m3fn bytes as fp32 (for the test that compares the table with torch.float8_e4m3fn). */
+void uqo_e4m3fn_table(float* out256) {
+  for (int b = 0; b < 256; b++) out256[b] = e4m3fn_to_f32((uint8_t)b);
+}
+
+static void decode_row_nvfp4(const uint8_t* codes, const uint8_t* scales, int D, float ts, float* out) {
+  static const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  for (int g = 0; g < D / 16; g++) {
+    const float sc = e4m3fn_to_f32(scales[g]) * ts;
+    for (int i = 0; i < 8; i++) {
+      const uint8_t b = codes[g * 8 + i];
+      const float lo = grid[b & 7], hi = grid[(b >> 4) & 7];
+      out[g * 16 + 2 * i] = ((b & 8) ? -lo : lo) * sc;
+      out[g * 16 + 2 * i + 1] = ((b & 0x80) ? -hi : hi) * sc;
+    }
+  }
+}
+
 /*
  * Attention oracle (uqmt/attn.py:402-422, frozen twin tools/gen_vectors.py:45-65).
  *   q bf16 bits [B,K,HQ,D]; caches as in cuda/uq_decode.h:3-6; out fp32 [B,K,HQ,D].
@@ -147,11 +173,11 @@ static void decode_row(const uint8_t* codes, const uint8_t* scales, int D, float
  * seq_lens are always GLOBAL lengths (they include the K draft tokens).
  * n_local[b] (NULL = whole sequence) is the number of keys this cache holds for sequence b.
  */
-void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
-                   const int32_t* block_table, const int32_t* seq_lens, const int32_t* pos_offset,
-                   const int32_t* n_local, int B, int K, int HQ, int HKV, int D, int PAGE, int max_pages,
-                   float sm_scale, float* out, float* lse_out) {
-  const int G = HQ / HKV, ng = D / 32;
+static void reference_impl(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
+                           const int32_t* block_table, const int32_t* seq_lens, const int32_t* pos_offset,
+                           const int32_t* n_local, int B, int K, int HQ, int HKV, int D, int PAGE, int max_pages,
+                           float sm_scale, float* out, float* lse_out, int fmt, float k_ts, float v_ts) {
+  const int G = HQ / HKV, ng = fmt ? D / 16 : D / 32;
   memset(out, 0, sizeof(float) * (size_t)B * K * HQ * D);
   if (lse_out)
     for (size_t i = 0; i < (size_t)B * K * HQ; i++) lse_out[i] = -INFINITY;
@@ -167,8 +193,13 @@ void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, cons
       float* sc = (float*)malloc(sizeof(float) * (size_t)n);
       for (int t = 0; t < n; t++) {
         size_t row = ((size_t)block_table[(size_t)b * max_pages + t / PAGE] * HKV + hk) * PAGE + t % PAGE;
-        decode_row(kc + row * (D / 2), ks + row * ng, D, kd + (size_t)t * D);
-        decode_row(vc + row * (D / 2), vs + row * ng, D, vd + (size_t)t * D);
+        if (fmt) {
+          decode_row_nvfp4(kc + row * (D / 2), ks + row * ng, D, k_ts, kd + (size_t)t * D);
+          decode_row_nvfp4(vc + row * (D / 2), vs + row * ng, D, v_ts, vd + (size_t)t * D);
+        } else {
+          decode_row(kc + row * (D / 2), ks + row * ng, D, kd + (size_t)t * D);
+          decode_row(vc + row * (D / 2), vs + row * ng, D, vd + (size_t)t * D);
+        }
       }
       for (int j = 0; j < K; j++) {
         int lim = n_glob - K + j + 1 - off;
@@ -211,6 +242,23 @@ void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, cons
       free(sc);
     }
   }
+}
+
+void uqo_reference(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
+                   const int32_t* block_table, const int32_t* seq_lens, const int32_t* pos_offset,
+                   const int32_t* n_local, int B, int K, int HQ, int HKV, int D, int PAGE, int max_pages,
+                   float sm_scale, float* out, float* lse_out) {
+  reference_impl(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset, n_local, B, K, HQ, HKV, D, PAGE, max_pages, sm_scale, out,
+                 lse_out, 0, 1.0f, 1.0f);
+}
+
+/* NVFP4 attention oracle (uqmt/nvfp4.py:257-278 reference_nvfp4): scale bytes e4m3fn [pages,Hkv,PAGE,D/16], per-tensor
+ * fp32 scales k_ts / v_ts; dequantise, then the same attention as above. */
+void uqo_reference_nvfp4(const uint16_t* q, const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs,
+                         const int32_t* block_table, const int32_t* seq_lens, int B, int K, int HQ, int HKV, int D, int PAGE,
+                         int max_pages, float sm_scale, float k_ts, float v_ts, float* out) {
+  reference_impl(q, kc, ks, vc, vs, block_table, seq_lens, NULL, NULL, B, K, HQ, HKV, D, PAGE, max_pages, sm_scale, out, NULL, 1,
+                 k_ts, v_ts);
 }
 
 /*

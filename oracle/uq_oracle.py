@@ -41,6 +41,8 @@ def lib():
         L.uqo_reference.argtypes = [vp] * 9 + [i32] * 7 + [f32, vp, vp]
         L.uqo_merge.argtypes = [vp, vp, i32, sz, i32, vp]
         L.uqo_tree_reference.argtypes = [vp] * 8 + [i32] * 7 + [f32, vp]
+        L.uqo_e4m3fn_table.argtypes = [vp]
+        L.uqo_reference_nvfp4.argtypes = [vp] * 7 + [i32] * 7 + [f32, f32, f32, vp]
         _LIB = L
     return _LIB
 
@@ -153,6 +155,29 @@ def tree_reference(q_bits, kc, ks, vc, vs, block_table, seq_lens, tree_mask=None
     sm = float(sm_scale) if sm_scale is not None else D ** -0.5
     lib().uqo_tree_reference(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), _p(tm), B, K, HQ, HKV, D, PAGE,
                              bt.shape[1], sm, _p(out))
+    return out
+
+
+def e4m3fn_table():
+    """fp32 value of every e4m3fn byte (NaN at 0x7f / 0xff)."""
+    out = np.empty(256, np.float32)
+    lib().uqo_e4m3fn_table(_p(out))
+    return out
+
+
+def reference_nvfp4(q_bits, kc, ks, vc, vs, block_table, seq_lens, k_ts=1.0, v_ts=1.0, sm_scale=None):
+    """NVFP4 cache (uqmt/nvfp4.py:257-278): ks / vs are e4m3fn bytes [pages,Hkv,PAGE,D/16], k_ts / v_ts the per-tensor
+    fp32 scales.  q_bits uint16 [B,K,Hq,D] -> out fp32 [B,K,Hq,D]."""
+    q_bits = np.ascontiguousarray(q_bits, dtype=np.uint16)
+    B, K, HQ, D = q_bits.shape
+    _, HKV, PAGE, _ = kc.shape
+    bt = np.ascontiguousarray(block_table, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    kc, ks, vc, vs = (np.ascontiguousarray(a, dtype=np.uint8) for a in (kc, ks, vc, vs))
+    out = np.empty((B, K, HQ, D), np.float32)
+    sm = float(sm_scale) if sm_scale is not None else D ** -0.5
+    lib().uqo_reference_nvfp4(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), B, K, HQ, HKV, D, PAGE, bt.shape[1],
+                              sm, float(k_ts), float(v_ts), _p(out))
     return out
 
 

@@ -19,16 +19,22 @@ class Case:
         self.q = z[f"q_K{K}"]
         self.ref = z[f"ref_K{K}"]
         self.sm_scale = float(z["sm_scale"]) if "sm_scale" in z else self.D ** -0.5
+        # NVFP4 sets carry the per-tensor scales; their scale arrays are e4m3fn bytes per 16 channels
+        self.fmt = 1 if "ts" in z else 0
+        self.k_ts, self.v_ts = (float(z["ts"][0]), float(z["ts"][1])) if "ts" in z else (1.0, 1.0)
 
     def __repr__(self):
         return self.name
 
 
 def load_cases(pattern="*"):
+    """Attention cases of the fixtures matching `pattern`; the NVFP4 sets only when the pattern names them."""
     out = []
     for f in sorted(glob.glob(os.path.join(GOLDEN, pattern + ".npz"))):
         base = os.path.basename(f)[:-4]
         if base in ("gen_codec", "gen_append", "tree_cases"):
+            continue
+        if base.startswith("nvfp4_") and not pattern.startswith("nvfp4_"):
             continue
         z = np.load(f)
         for K in z["Ks"]:

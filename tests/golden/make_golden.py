@@ -8,7 +8,9 @@ Two kinds of fixture:
   gen_*.npz   inputs and outputs of the reference's Python functions run here
       (uqmt.attn.quantize_fp4 / dequantize_fp4 / reference / build_paged_cache,
        uqmt.vllm_adapter.append_kv, uqmt.tree.tree_reference), for the cases the frozen vectors do not cover.
-`--tree-only` regenerates tree_cases.npz alone.
+  nvfp4_cuda_<set>.npz   the reference's frozen NVFP4 vectors (cuda/vectors_nvfp4), repacked the same way; the scale
+      arrays are e4m3fn bytes [pages,Hkv,PAGE,D/16] and `ts` holds the per-tensor scales (k_ts, v_ts).
+`--tree-only` regenerates tree_cases.npz alone, `--nvfp4-only` the nvfp4_cuda_* files alone.
 """
 import os
 import sys
@@ -29,26 +31,30 @@ def save(name, **arrs):
     print(name, {k: getattr(v, "shape", v) for k, v in arrs.items()})
 
 
-def repack_cuda_vectors():
-    d = os.path.join(REF, "cuda", "vectors")
+def repack_cuda_vectors(sub="vectors", prefix="ref_cuda_", group=32):
+    d = os.path.join(REF, "cuda", sub)
     sets = {}
     for line in open(os.path.join(d, "manifest.txt")):
         t = line.split()
         name, K = t[1], int(t[2])
         B, HQ, HKV, D, PAGE, pages, max_pages = map(int, t[3:10])
         s = sets.setdefault(name, dict(meta=np.array([B, HQ, HKV, D, PAGE, pages, max_pages], np.int32), Ks=[]))
+        if group == 16:   # NVFP4 manifest: two more columns, the per-tensor scales
+            s["ts"] = np.array([float(t[10]), float(t[11])], np.float64)
         s["Ks"].append(K)
     for name, s in sets.items():
         B, HQ, HKV, D, PAGE, pages, max_pages = (int(x) for x in s["meta"])
         f = lambda suf, dt: np.fromfile(os.path.join(d, f"{name}_{suf}.bin"), dtype=dt)
         arrs = dict(meta=s["meta"], Ks=np.array(s["Ks"], np.int32),
-                    kc=f("kc", np.uint8).reshape(pages, HKV, PAGE, D // 2), ks=f("ks", np.uint8).reshape(pages, HKV, PAGE, D // 32),
-                    vc=f("vc", np.uint8).reshape(pages, HKV, PAGE, D // 2), vs=f("vs", np.uint8).reshape(pages, HKV, PAGE, D // 32),
+                    kc=f("kc", np.uint8).reshape(pages, HKV, PAGE, D // 2), ks=f("ks", np.uint8).reshape(pages, HKV, PAGE, D // group),
+                    vc=f("vc", np.uint8).reshape(pages, HKV, PAGE, D // 2), vs=f("vs", np.uint8).reshape(pages, HKV, PAGE, D // group),
                     bt=f("bt", np.int32).reshape(B, max_pages), sl=f("sl", np.int32))
         for K in s["Ks"]:
             arrs[f"q_K{K}"] = f(f"K{K}_q", np.uint16).reshape(B, K, HQ, D)
             arrs[f"ref_K{K}"] = f(f"K{K}_ref", np.float32).reshape(B, K, HQ, D)
-        save(f"ref_cuda_{name}.npz", **arrs)
+        if "ts" in s:
+            arrs["ts"] = s["ts"]
+        save(f"{prefix}{name}.npz", **arrs)
 
 
 SYCL_KEEP = ("b2k16_d128_p32", "b3k2_d64_p16", "b4k3_d128_p64_g1", "edge_short_k4", "b1k8_d128_p64")
@@ -216,10 +222,14 @@ def gen_tree():
 
 
 if __name__ == "__main__":
+    if "--nvfp4-only" in sys.argv:
+        repack_cuda_vectors("vectors_nvfp4", "nvfp4_cuda_", 16)
+        sys.exit(0)
     if "--tree-only" in sys.argv:
         gen_tree()
         sys.exit(0)
     repack_cuda_vectors()
+    repack_cuda_vectors("vectors_nvfp4", "nvfp4_cuda_", 16)
     repack_sycl_vectors()
     gen_codec()
     gen_cases()

@@ -138,6 +138,8 @@ def test_unserved_shapes_answer_invalid_value_before_any_work():
     q = dev(c.q.view(np.int16), torch.bfloat16)
     args = (dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt), dev(c.sl))
     with pytest.raises(RuntimeError, match="InvalidValue"):
+        uq_cuda.uq_decode_cuda(q, *args, fmt=2)
+    with pytest.raises(RuntimeError, match="scale"):   # an NVFP4 call needs D/16 scale bytes per row
         uq_cuda.uq_decode_cuda(q, *args, fmt=1)
     with pytest.raises(RuntimeError, match="InvalidValue"):
         uq_cuda.uq_decode_cuda(q, *args, nsplit=129)

@@ -1,0 +1,123 @@
+"""NVFP4 cache (fmt = 1: e2m1 codes, one e4m3fn scale byte per 16 channels, per-tensor fp32 scales k_ts / v_ts).
+
+The known answers are the reference's own frozen vectors (cuda/vectors_nvfp4, repacked into golden/nvfp4_cuda_*.npz):
+the oracle is pinned to them on the CPU, and the CUDA-core kernel is compared with them through the C ABI on a GPU."""
+import numpy as np
+import pytest
+import torch
+
+from tests.cases import check_close, check_harness_rule, load_cases
+from oracle import uq_oracle as O
+
+CASES = load_cases("nvfp4_cuda_*")
+
+
+def test_fixture_set_is_complete():
+    assert len(CASES) == 13
+    assert {c.name.split("_K")[0] for c in CASES} == {f"nvfp4_cuda_{s}" for s in ("main", "gqa8_p128", "d64_p32", "p16_g4", "edge_short")}
+    for c in CASES:
+        assert c.fmt == 1 and c.ks.shape[-1] == c.D // 16 and c.vs.shape[-1] == c.D // 16
+
+
+def test_e4m3fn_table_matches_torch():
+    want = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    got = O.e4m3fn_table()
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(got[ok], want[ok])
+
+
+@pytest.mark.parametrize("c", CASES, ids=repr)
+def test_oracle_reproduces_the_reference_vectors(c):
+    out = O.reference_nvfp4(c.q, c.kc, c.ks, c.vc, c.vs, c.bt, c.sl, c.k_ts, c.v_ts, c.sm_scale)
+    assert np.abs(out - c.ref).max() <= 1e-5 * max(1.0, np.abs(c.ref).max())
+
+
+def test_unit_tensor_scales_and_power_of_two_blocks_equal_the_ultraquant_answer():
+    """A cache whose e4m3fn scales are powers of two, equal within each 32-channel block, is the same tensor as the
+    UltraQuant cache with the matching UE8M0 bytes: both oracles must give the same answer."""
+    rng = np.random.default_rng(5)
+    B, K, HQ, HKV, D, PAGE, pages = 2, 3, 4, 2, 64, 16, 6
+    kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    e = rng.integers(-3, 3, (2, pages, HKV, PAGE, D // 32))
+    ue = (e + 127).astype(np.uint8)
+    e4 = np.repeat(((e + 7) << 3).astype(np.uint8), 2, axis=-1)      # exponent field only: 2^e
+    bt = np.arange(pages, dtype=np.int32).reshape(B, pages // B)
+    sl = np.array([40, 33], np.int32)
+    q = O.bf16_bits(rng.standard_normal((B, K, HQ, D)).astype(np.float32))
+    a = O.reference(q, kc, ue[0], vc, ue[1], bt, sl)
+    b = O.reference_nvfp4(q, kc, e4[0], vc, e4[1], bt, sl, 1.0, 1.0)
+    assert np.array_equal(a, b)
+
+
+# ---------------------------------------------------------------------------------------------------- GPU
+def _dev(c):
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    q = torch.from_numpy(c.q.view(np.int16)).cuda().view(torch.bfloat16)
+    return q, t(c.kc), t(c.ks), t(c.vc), t(c.vs), t(c.bt), t(c.sl)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("c", CASES, ids=repr)
+def test_kernel_matches_the_reference_vectors(c):
+    from all_quant_b200 import uq_cuda
+    q, kc, ks, vc, vs, bt, sl = _dev(c)
+    for nsplit in (None, 1, 3):
+        out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, nsplit=nsplit, sm_scale=c.sm_scale, fmt=1, k_ts=c.k_ts, v_ts=c.v_ts)
+        torch.cuda.synchronize()
+        assert uq_cuda.last_path() == 1          # the CUDA-core kernel: the tensor-core kernel takes fmt 0 only
+        assert uq_cuda.last_status()[0] == 0
+        got = out.float().cpu().numpy()
+        check_close(got, c.ref, f"{c} nsplit={nsplit}")
+        check_harness_rule(got, c.ref, f"{c} nsplit={nsplit}")
+
+
+@pytest.mark.gpu
+def test_unfused_mode_and_tensor_scales():
+    from all_quant_b200 import uq_cuda
+    c = [x for x in CASES if x.name == "nvfp4_cuda_main_K4"][0]
+    q, kc, ks, vc, vs, bt, sl = _dev(c)
+    out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fused=False, fmt=1, k_ts=c.k_ts, v_ts=c.v_ts)
+    check_close(out.float().cpu().numpy(), c.ref, "unfused")
+    # other tensor scales: the oracle is the judge
+    for k_ts, v_ts in ((2.0 * c.k_ts, 0.5 * c.v_ts), (0.25 * c.k_ts, 1.5 * c.v_ts)):   # outputs stay of order one: the rule's mean bound is absolute
+        want = O.reference_nvfp4(c.q, c.kc, c.ks, c.vc, c.vs, c.bt, c.sl, k_ts, v_ts)
+        out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fmt=1, k_ts=k_ts, v_ts=v_ts)
+        check_close(out.float().cpu().numpy(), want, f"k_ts={k_ts} v_ts={v_ts}")
+
+
+@pytest.mark.gpu
+def test_larger_nvfp4_call_against_the_oracle():
+    """Longer contexts than the frozen vectors hold, D = 256 included (the reference ships no NVFP4 vector for it)."""
+    from all_quant_b200 import uq_cuda
+    rng = np.random.default_rng(11)
+    for D, PAGE, K, HQ, HKV in ((128, 64, 8, 16, 2), (256, 32, 2, 8, 4), (64, 128, 5, 6, 2)):
+        B, ctx = 2, 1500
+        npg = -(-ctx // PAGE)
+        pages = B * npg
+        kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+        vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+        # scale bytes: exponent fields 4..10 with any mantissa, sign clear (what an amax / 6 scale can be)
+        ks = (rng.integers(4, 11, (pages, HKV, PAGE, D // 16)) << 3 | rng.integers(0, 8, (pages, HKV, PAGE, D // 16))).astype(np.uint8)
+        vs = (rng.integers(4, 11, (pages, HKV, PAGE, D // 16)) << 3 | rng.integers(0, 8, (pages, HKV, PAGE, D // 16))).astype(np.uint8)
+        bt = rng.permutation(pages).astype(np.int32).reshape(B, npg)
+        sl = np.array([ctx, ctx - 777], np.int32)
+        qf = rng.standard_normal((B, K, HQ, D)).astype(np.float32)
+        qb = O.bf16_bits(qf)
+        k_ts, v_ts = 0.05, 0.7
+        want = O.reference_nvfp4(qb, kc, ks, vc, vs, bt, sl, k_ts, v_ts)
+        t = lambda a: torch.from_numpy(a).cuda()
+        q = torch.from_numpy(qb.view(np.int16)).cuda().view(torch.bfloat16)
+        out = uq_cuda.uq_decode_cuda(q, t(kc), t(ks), t(vc), t(vs), t(bt), t(sl), fmt=1, k_ts=k_ts, v_ts=v_ts)
+        assert uq_cuda.last_path() == 1
+        check_close(out.float().cpu().numpy(), want, f"D={D}")
+
+
+@pytest.mark.gpu
+def test_unknown_format_is_refused():
+    from all_quant_b200 import uq_cuda
+    c = CASES[0]
+    q, kc, ks, vc, vs, bt, sl = _dev(c)
+    with pytest.raises(RuntimeError):
+        uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fmt=2)
