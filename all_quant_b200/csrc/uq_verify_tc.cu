@@ -296,6 +296,16 @@ UQ_DEV uint32_t pow2_f16x2(int e) {
   const uint32_t b = e >= -14 ? (uint32_t)(e + 15) << 10 : (e >= -24 ? 1u << (e + 24) : 0u);
   return b | (b << 16);
 }
+// NVFP4: two e4m3fn scale bytes (the two 16-channel blocks of a 32-channel group) as fp16 pairs.  The byte's low seven bits
+// moved up by seven are an fp16 with the same mantissa and an exponent bias of 15 instead of 7: one multiply by 2^8 gives
+// the value, subnormals included (exact: fp16 holds every e4m3fn value).  The code times the scale, at most 6 x 448 with
+// five significant bits, is exact in fp16 as well.  (0x7f, the format's NaN, reads as 480 here; no quantiser writes it.)
+UQ_DEV void e4m3_pair_f16x2(uint32_t two_bytes, uint32_t& lo, uint32_t& hi) {
+  const uint32_t a = ((two_bytes & 0x80u) << 8) | ((two_bytes & 0x7Fu) << 7);
+  const uint32_t b = ((two_bytes & 0x8000u)) | ((two_bytes & 0x7F00u) >> 1);
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(a | (a << 16)), "r"(0x5C005C00u));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(b | (b << 16)), "r"(0x5C005C00u));
+}
 // the D/32 scale bytes of one key (2, 4 or 8 bytes, contiguous) as one 64-bit value, byte g = group g
 template <int G>
 UQ_DEV unsigned long long load_scales(const uint8_t* p) {
@@ -365,22 +375,23 @@ __device__ __noinline__ uint32_t draft_rows(const int32_t* tree_mask, int K, int
 }
 
 // ---------------------------------------------------------------------------------------------- layout
-template <int D, int NT>
+template <int D, int NT, int FMT = 0>
 struct Cfg {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64 / 128 / 256");
   static_assert(NT == 16 || NT == 32 || NT == 64, "rows padded to 16 / 32 / 64");
   static constexpr int kRawStages = raw_stages(D), kSB = ring_sb(D), kVB = ring_vb(D);
   static constexpr int kCodeRow = D / 2;                 // bytes of codes per key
-  static constexpr int kGroups = D / 32;                 // scale bytes per key
+  static constexpr int kGroups = D / 32;                 // 32-channel groups per key: one UE8M0 scale byte each (FMT 0)
+  static constexpr int kScaleB = FMT ? D / 16 : D / 32;  // scale bytes per key (NVFP4: one e4m3fn byte per 16 channels)
   static constexpr int kChunks = kCodeRow / 16;          // 16-byte chunks per code row = scale groups
   static constexpr int kRowsPer128 = 128 / kCodeRow;     // code rows per 128 bytes: the TMA swizzle (32 / 64 / 128 B) XORs the chunk index with (row / this)
   // head_dim 128: S^T comes from a block-scaled contraction (kind::mxf8f6f4, one UE8M0 scale per 32 channels: the cache's own
   // format), so the K codes are never decoded.  The TMA unpacks them into the layout that instruction reads (16 codes = 8
   // bytes, then 8 bytes of padding: 128 bytes per key), the scale bytes go to TMEM as they are, and Q is two e4m3 tiles
   // (leading bits + remainder, each with a scale per row and 32 channels).
-  static constexpr bool kBS = block_scaled(D);
+  static constexpr bool kBS = block_scaled(D) && FMT == 0;   // (NVFP4 scales are not powers of two: it takes the fp16 route at every head_dim)
   static constexpr int kRawCodes = kKeys * kCodeRow;
-  static constexpr int kRawScales = kKeys * kGroups;
+  static constexpr int kRawScales = kKeys * kScaleB;
   static constexpr int kRawK = kBS ? kKeys * D : kRawCodes;   // K codes of a tile as they sit in shared memory
   static constexpr int kOffVC = kRawK;                        // offsets within a raw stage: V codes, K scales, V scales
   static constexpr int kOffKS = kOffVC + kRawCodes;
@@ -517,10 +528,10 @@ struct Walker {
 };
 
 // ---------------------------------------------------------------------------------------------- kernel
-template <int D, int NT>
+template <int D, int NT, int FMT>
 __global__ void __launch_bounds__(cta_threads(NT), 1)
 uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_vc) {
-  using C = Cfg<D, NT>;
+  using C = Cfg<D, NT, FMT>;
   // declared 1024-byte aligned (swizzled tiles need it) and used without any integer arithmetic on the pointer, so that the
   // compiler keeps every access in the shared state space (ld.shared / st.shared instead of generic loads and stores)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -636,7 +647,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // ================================================================= producer
     const int ppt = kKeys / p.PAGE;   // pages per tile
     UQ_PROF_DECL
-    const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kGroups;
+    const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kScaleB;
     while (ok && wk.next(sg)) {
       if (!take()) continue;
       int off;
@@ -661,8 +672,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
           tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
           tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
-          bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
-          bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kGroups, page_bytes_scales, fb);
+          bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
         }
       }
     }
@@ -765,9 +776,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (kk == 0) { UQ_TRACE(1, cnt) }
         UQ_PROF_T0
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage;
-        const unsigned long long sc = load_scales<C::kGroups>(raw + C::kOffKS + kk * C::kGroups);
-        const uint32_t kref = C::kBS ? 127u : max_byte<C::kGroups>(sc);
-        const uint32_t vref = max_byte<C::kGroups>(load_scales<C::kGroups>(raw + C::kOffVS + kk * C::kGroups));
+        // NVFP4: the block scales are bounded (e4m3fn), a key's fp16 values carry them whole and both references stay at 2^0
+        unsigned long long sc = 0;
+        uint32_t kref = 127u, vref = 127u;
+        if constexpr (FMT == 0) {
+          sc = load_scales<C::kGroups>(raw + C::kOffKS + kk * C::kGroups);
+          if (!C::kBS) kref = max_byte<C::kGroups>(sc);
+          vref = max_byte<C::kGroups>(load_scales<C::kGroups>(raw + C::kOffVS + kk * C::kGroups));
+        }
         reinterpret_cast<uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk] = (uint16_t)(kref | (vref << 8));   // for the softmax threads of this key
         if constexpr (C::kBS) {
           // block-scaled: nothing to decode.  The contraction wants the scale bytes of key 32 j + l (one 32-bit word: byte b =
@@ -789,9 +805,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(krow + (((g0 + g) ^ swz) << 4));
 #pragma unroll
           for (int g = 0; g < GN; g++) {
-            const uint32_t m = pow2_f16x2((int)((uint32_t)(sc >> (8 * (g0 + g))) & 0xFFu) - (int)kref);
+            uint32_t m, m2;
+            if constexpr (FMT == 0) m = m2 = pow2_f16x2((int)((uint32_t)(sc >> (8 * (g0 + g))) & 0xFFu) - (int)kref);
+            else e4m3_pair_f16x2(*reinterpret_cast<const uint16_t*>(raw + C::kOffKS + kk * C::kScaleB + 2 * (g0 + g)), m, m2);
             uint32_t o[16];
-            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
+            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m2, o + 8); decode8_f16(c4[g].w, m2, o + 12);
             tmem_st16(lane_addr + C::cK + buf * C::kKCols + (g0 + g) * 16, o);
           }
         }
@@ -836,8 +854,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const uint8_t* raw = sm + C::oRaw + stage * C::kRawStage + C::kOffVC;
         uint8_t* vt = sm + C::oV + buf * C::kVTile;
         const bool live = t * kKeys + kk < n_loc;   // keys past the end of the sequence contribute exact zeros
-        const unsigned long long sc = load_scales<C::kGroups>(sm + C::oRaw + stage * C::kRawStage + C::kOffVS + kk * C::kGroups);
-        const int vref = (int)max_byte<C::kGroups>(sc);
+        unsigned long long sc = 0;
+        int vref = 127;
+        if constexpr (FMT == 0) {
+          sc = load_scales<C::kGroups>(sm + C::oRaw + stage * C::kRawStage + C::kOffVS + kk * C::kGroups);
+          vref = (int)max_byte<C::kGroups>(sc);
+        }
+        const uint8_t* vsc = sm + C::oRaw + stage * C::kRawStage + C::kOffVS + kk * C::kScaleB;   // (NVFP4: read per group below)
         const uint8_t* vcode = raw + kk * C::kCodeRow;
         const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
 #pragma unroll
@@ -850,9 +873,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int g = 0; g < GN; g++) {
             const int gg = g0 + g;
-            const uint32_t m = live ? pow2_f16x2((int)((uint32_t)(sc >> (8 * gg)) & 0xFFu) - vref) : 0u;   // multiplier 0: keys past the end decode to zeros
+            uint32_t m, m2;   // multiplier 0: keys past the end decode to zeros
+            if constexpr (FMT == 0) m = m2 = live ? pow2_f16x2((int)((uint32_t)(sc >> (8 * gg)) & 0xFFu) - vref) : 0u;
+            else {
+              e4m3_pair_f16x2(*reinterpret_cast<const uint16_t*>(vsc + 2 * gg), m, m2);
+              if (!live) m = m2 = 0u;
+            }
             uint32_t o[16];
-            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m, o + 8); decode8_f16(c4[g].w, m, o + 12);
+            decode8_f16(c4[g].x, m, o); decode8_f16(c4[g].y, m, o + 4); decode8_f16(c4[g].z, m2, o + 8); decode8_f16(c4[g].w, m2, o + 12);
             // output chunk 4gg + w (8 channels) of the key's row: 64-channel half (4gg + w) >> 3, slot ((4gg + w) & 7) ^ (key & 7)
             uint8_t* vrow = vt + (gg >> 1) * C::kVHalf + kk * 128;
 #pragma unroll
@@ -1381,10 +1409,10 @@ bool make_unpack_map(CUtensorMap* map, const uint8_t* base, int channels, int pa
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, int NT>
+template <int D, int NT, int FMT>
 cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
-  using C = Cfg<D, NT>;
-  auto kern = uq_verify_tc_kernel<D, NT>;
+  using C = Cfg<D, NT, FMT>;
+  auto kern = uq_verify_tc_kernel<D, NT, FMT>;
   static bool ready[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1435,12 +1463,12 @@ extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
 #endif
 
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
-  if (p.fmt != 0) return false;   // the NVFP4 cache is served by the CUDA-core kernel
+  if (p.fmt != 0 && p.fmt != 1) return false;
   if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
   if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
   if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
-  if (tc::block_scaled(p.D) && (reinterpret_cast<uintptr_t>(p.kc) & 31)) return false;   // the unpacking tensor map wants 32-byte alignment
+  if (p.fmt == 0 && tc::block_scaled(p.D) && (reinterpret_cast<uintptr_t>(p.kc) & 31)) return false;   // the unpacking tensor map wants 32-byte alignment
   if ((long long)p.max_pages * p.PAGE >= (1ll << 30)) return false;
   return tc::encode_fn() != nullptr;
 }
@@ -1456,18 +1484,18 @@ int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) {
   return std::max(1, std::min(p.nsplit, span));
 }
 
-template <int D>
+template <int D, int FMT>
 static cudaError_t dispatch_rows(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
-  if (x.rows <= 16) return tc::launch<D, 16>(p, x, s);
-  if (x.rows <= 32) return tc::launch<D, 32>(p, x, s);
-  return tc::launch<D, 64>(p, x, s);
+  if (x.rows <= 16) return tc::launch<D, 16, FMT>(p, x, s);
+  if (x.rows <= 32) return tc::launch<D, 32, FMT>(p, x, s);
+  return tc::launch<D, 64, FMT>(p, x, s);
 }
 
 cudaError_t uq_verify_tc_dispatch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   switch (p.D) {
-    case 64: return dispatch_rows<64>(p, x, s);
-    case 128: return dispatch_rows<128>(p, x, s);
-    case 256: return dispatch_rows<256>(p, x, s);
+    case 64: return p.fmt == 1 ? dispatch_rows<64, 1>(p, x, s) : dispatch_rows<64, 0>(p, x, s);
+    case 128: return p.fmt == 1 ? dispatch_rows<128, 1>(p, x, s) : dispatch_rows<128, 0>(p, x, s);
+    case 256: return p.fmt == 1 ? dispatch_rows<256, 1>(p, x, s) : dispatch_rows<256, 0>(p, x, s);
   }
   return cudaErrorInvalidValue;
 }

@@ -59,14 +59,16 @@ def _dev(c):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("path", ["tc", "fma"])
 @pytest.mark.parametrize("c", CASES, ids=repr)
-def test_kernel_matches_the_reference_vectors(c):
+def test_kernel_matches_the_reference_vectors(c, path, monkeypatch):
     from all_quant_b200 import uq_cuda
+    monkeypatch.setenv("UQ_B200_CFG", f"path={path}")
     q, kc, ks, vc, vs, bt, sl = _dev(c)
     for nsplit in (None, 1, 3):
         out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, nsplit=nsplit, sm_scale=c.sm_scale, fmt=1, k_ts=c.k_ts, v_ts=c.v_ts)
         torch.cuda.synchronize()
-        assert uq_cuda.last_path() == 1          # the CUDA-core kernel: the tensor-core kernel takes fmt 0 only
+        assert uq_cuda.last_path() == {"fma": 1, "tc": 2}[path]
         assert uq_cuda.last_status()[0] == 0
         got = out.float().cpu().numpy()
         check_close(got, c.ref, f"{c} nsplit={nsplit}")
@@ -88,9 +90,12 @@ def test_unfused_mode_and_tensor_scales():
 
 
 @pytest.mark.gpu
-def test_larger_nvfp4_call_against_the_oracle():
-    """Longer contexts than the frozen vectors hold, D = 256 included (the reference ships no NVFP4 vector for it)."""
+@pytest.mark.parametrize("path", ["tc", "fma"])
+def test_larger_nvfp4_call_against_the_oracle(path, monkeypatch):
+    """Longer contexts than the frozen vectors hold, D = 256 included (the reference ships no NVFP4 vector for it); scale
+    bytes over the whole exponent range of the format, subnormals included."""
     from all_quant_b200 import uq_cuda
+    monkeypatch.setenv("UQ_B200_CFG", f"path={path}")
     rng = np.random.default_rng(11)
     for D, PAGE, K, HQ, HKV in ((128, 64, 8, 16, 2), (256, 32, 2, 8, 4), (64, 128, 5, 6, 2)):
         B, ctx = 2, 1500
@@ -98,19 +103,21 @@ def test_larger_nvfp4_call_against_the_oracle():
         pages = B * npg
         kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
         vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
-        # scale bytes: exponent fields 4..10 with any mantissa, sign clear (what an amax / 6 scale can be)
+        # scale bytes: K exponent fields 4..10 with any mantissa, sign clear (what an amax / 6 scale can be);
+        # V any finite non-negative byte (0x00..0x7e: zero, subnormals, up to 448), mostly small so that outputs stay of order one
         ks = (rng.integers(4, 11, (pages, HKV, PAGE, D // 16)) << 3 | rng.integers(0, 8, (pages, HKV, PAGE, D // 16))).astype(np.uint8)
-        vs = (rng.integers(4, 11, (pages, HKV, PAGE, D // 16)) << 3 | rng.integers(0, 8, (pages, HKV, PAGE, D // 16))).astype(np.uint8)
+        vs = rng.integers(0, 0x48, (pages, HKV, PAGE, D // 16)).astype(np.uint8)
+        vs[rng.random(vs.shape) < 0.01] = 0x7e
         bt = rng.permutation(pages).astype(np.int32).reshape(B, npg)
         sl = np.array([ctx, ctx - 777], np.int32)
         qf = rng.standard_normal((B, K, HQ, D)).astype(np.float32)
         qb = O.bf16_bits(qf)
-        k_ts, v_ts = 0.05, 0.7
+        k_ts, v_ts = 0.05, 0.02
         want = O.reference_nvfp4(qb, kc, ks, vc, vs, bt, sl, k_ts, v_ts)
         t = lambda a: torch.from_numpy(a).cuda()
         q = torch.from_numpy(qb.view(np.int16)).cuda().view(torch.bfloat16)
         out = uq_cuda.uq_decode_cuda(q, t(kc), t(ks), t(vc), t(vs), t(bt), t(sl), fmt=1, k_ts=k_ts, v_ts=v_ts)
-        assert uq_cuda.last_path() == 1
+        assert uq_cuda.last_path() == {"fma": 1, "tc": 2}[path] and uq_cuda.last_status()[0] == 0
         check_close(out.float().cpu().numpy(), want, f"D={D}")
 
 
