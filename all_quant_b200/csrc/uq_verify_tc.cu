@@ -22,6 +22,8 @@
 //   P.V issue 1 warp       8 tcgen05.mma per tile (one thread)
 // The key's reference scales 2^(ref-127) are applied in fp32 by the softmax threads that own the key (K's to the score,
 // V's to the probability, relative to a running reference of the segment so that P fits fp16).
+// FMT = 1 is the NVFP4 cache (reference cuda/uq_decode.h:28-29: one e4m3fn scale byte per 16 channels): the two decode
+// roles multiply the converted codes by the block scale itself (exact in fp16) and the keys' references stay at 2^0.
 // Work is a flat list of 128-key tiles over all (sequence, kv head) items, cut into equal chunks, one per CTA;
 // a chunk that crosses items yields several segments, each written to its own partial slot.
 //

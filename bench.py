@@ -73,8 +73,13 @@ def shard_plan(cfg, rank, world):
     return plan
 
 
+def scale_bytes(cfg):
+    """Scale bytes per cache row: one UE8M0 byte per 32 channels, or (--fmt 1, NVFP4) one e4m3fn byte per 16."""
+    return cfg["D"] // (16 if cfg.get("fmt", 0) == 1 else 32)
+
+
 def local_kv_bytes(cfg, plan):
-    return int(plan["local"].sum() * plan["hkv"] * 2 * (cfg["D"] // 2 + cfg["D"] // 32))
+    return int(plan["local"].sum() * plan["hkv"] * 2 * (cfg["D"] // 2 + scale_bytes(cfg)))
 
 
 def peaks():
@@ -87,7 +92,7 @@ def peaks():
 
 
 def kv_bytes(cfg, seq_lens):
-    return int(sum(int(n) for n in seq_lens) * cfg["HKV"] * 2 * (cfg["D"] // 2 + cfg["D"] // 32))
+    return int(sum(int(n) for n in seq_lens) * cfg["HKV"] * 2 * (cfg["D"] // 2 + scale_bytes(cfg)))
 
 
 # ------------------------------------------------------------------------------------------------ clocks
@@ -159,8 +164,11 @@ def build_case(cfg, plan, K, seed, device, copies=2):
     perm = torch.randperm(pages, generator=g, device=device).to(torch.int32)
     bt = torch.zeros(B, width, dtype=torch.int32, device=device)
     kc = torch.empty(pages, hkv, PAGE, D // 2, dtype=torch.uint8, device=device)
-    ks = torch.empty(pages, hkv, PAGE, D // 32, dtype=torch.uint8, device=device)
+    ks = torch.empty(pages, hkv, PAGE, scale_bytes(cfg), dtype=torch.uint8, device=device)
     vc, vs = torch.empty_like(kc), torch.empty_like(ks)
+    nvfp4 = cfg.get("fmt", 0) == 1
+    # NVFP4: fixed per-tensor scales that put a block maximum of 32 (K) / 8 (V) at the top of the e4m3fn range
+    k_ts, v_ts = (32.0 / (6 * 448), 8.0 / (6 * 448)) if nvfp4 else (1.0, 1.0)
     new_k, new_v, new_slots = [], [], []
     first = 0
     for b in range(B):
@@ -173,7 +181,12 @@ def build_case(cfg, plan, K, seed, device, copies=2):
         k = torch.randn(n, hkv, D, generator=g, device=device) * chan
         v = torch.randn(n, hkv, D, generator=g, device=device)
         slots = bt[b].long()[pos // PAGE] * PAGE + pos % PAGE
-        uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots)
+        if nvfp4:   # the library's append kernel writes the UltraQuant format only: this cache is encoded here, in torch
+            pg, at = slots // PAGE, slots % PAGE
+            kc[pg, :, at], ks[pg, :, at] = nvfp4_encode(k, k_ts)
+            vc[pg, :, at], vs[pg, :, at] = nvfp4_encode(v, v_ts)
+        else:
+            uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots)
         # the K newest tokens of the sequence (global positions len-K .. len-1) that fall into this shard
         lo = max(0, int(plan["lens"][b]) - K - off)
         if lo < n:
@@ -187,19 +200,34 @@ def build_case(cfg, plan, K, seed, device, copies=2):
     for _ in range(copies - 1):   # identical bytes at other addresses, so consecutive calls never hit L2
         caches.append(tuple(t.clone() for t in (kc, ks, vc, vs)))
     cat = lambda xs: torch.cat(xs).contiguous() if xs else None
-    return dict(q=q, bt=bt.contiguous(), sl=sl, po=po, caches=caches, new_k=cat(new_k), new_v=cat(new_v), new_slots=cat(new_slots))
+    return dict(q=q, bt=bt.contiguous(), sl=sl, po=po, caches=caches, new_k=cat(new_k), new_v=cat(new_v), new_slots=cat(new_slots),
+                k_ts=k_ts, v_ts=v_ts)
+
+
+def nvfp4_encode(x, ts):
+    """fp32 [..., D] -> (e2m1 code bytes [..., D/2], e4m3fn scale bytes [..., D/16]) for the per-tensor scale ts: the NVFP4
+    recipe (block scale = e4m3fn(block amax / 6 / ts), codes = nearest e2m1 to x / (scale * ts)).  Data preparation of
+    the benchmark only; the answers are checked against the CPU oracle on the same bytes."""
+    import torch
+    D = x.shape[-1]
+    xg = x.float().reshape(*x.shape[:-1], D // 16, 16)
+    s8 = (xg.abs().amax(-1, keepdim=True) / 6.0 / ts).clamp(2.0 ** -9, 448.0).to(torch.float8_e4m3fn)
+    y = (xg / (s8.float() * ts)).clamp(-6.0, 6.0).reshape(*x.shape[:-1], D)
+    edges = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=x.device)
+    code = torch.bucketize(y.abs(), edges).to(torch.uint8) | ((y < 0).to(torch.uint8) << 3)
+    return code[..., 0::2] | (code[..., 1::2] << 4), s8.view(torch.uint8).squeeze(-1)
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
-def cpu_sample(case_np, steps, warmup):
-    """Times the CPU oracle on sequence 0 (all KV heads, full context) of one layer."""
+def cpu_sample(case_np, steps, warmup, nvfp4=None):
+    """Times the CPU oracle on sequence 0 (all KV heads, full context) of one layer; nvfp4 = (k_ts, v_ts) for an NVFP4 cache."""
     from oracle import uq_oracle as O
     q, kc, ks, vc, vs, bt, sl = case_np
     ts = []
     out = None
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        out = O.reference(q[:1], kc, ks, vc, vs, bt[:1], sl[:1])
+        out = O.reference_nvfp4(q[:1], kc, ks, vc, vs, bt[:1], sl[:1], *nvfp4) if nvfp4 else O.reference(q[:1], kc, ks, vc, vs, bt[:1], sl[:1])
         if i >= warmup:
             ts.append(time.perf_counter() - t0)
     return float(np.mean(ts)), out, O.max_threads()
@@ -226,8 +254,15 @@ def run_reference_arm(args, cfg):
     chan = np.exp(0.5 * rng.standard_normal((1, HKV, 1, D))).astype(np.float32)
     k = rng.standard_normal((npg, HKV, PAGE, D)).astype(np.float32) * chan
     v = rng.standard_normal((npg, HKV, PAGE, D)).astype(np.float32)
-    kc, ks = O.quantize_fp4(k)
-    vc, vs = O.quantize_fp4(v)
+    nvfp4 = cfg.get("fmt", 0) == 1
+    if nvfp4:   # the time does not depend on the values: random codes, scale bytes around one
+        kc, vc = (rng.integers(0, 256, (npg, HKV, PAGE, D // 2), dtype=np.uint8) for _ in range(2))
+        ks, vs = (rng.integers(0x30, 0x40, (npg, HKV, PAGE, D // 16)).astype(np.uint8) for _ in range(2))
+        ref = lambda *a: O.reference_nvfp4(*a, 0.05, 0.05)
+    else:
+        kc, ks = O.quantize_fp4(k)
+        vc, vs = O.quantize_fp4(v)
+        ref = O.reference
     bt = rng.permutation(npg).astype(np.int32).reshape(1, npg)
     inv = np.empty(npg, np.int64)
     inv[bt[0]] = np.arange(npg)
@@ -237,7 +272,7 @@ def run_reference_arm(args, cfg):
     steps = max(1, args.steps)
     # keep the whole run within a few minutes: at most ~90 s of timed CPU work
     t0 = time.perf_counter()
-    O.reference(q, kc, ks, vc, vs, bt, sl)
+    ref(q, kc, ks, vc, vs, bt, sl)
     one = time.perf_counter() - t0
     frac_heads = HKV
     while frac_heads > 1 and one * frac_heads / HKV * (steps + args.warmup) > 90.0:
@@ -248,7 +283,7 @@ def run_reference_arm(args, cfg):
     ts = []
     for i in range(args.warmup + steps):
         t0 = time.perf_counter()
-        O.reference(q2, kc2, ks2, vc2, vs2, bt, sl)
+        ref(q2, kc2, ks2, vc2, vs2, bt, sl)
         if i >= args.warmup:
             ts.append(time.perf_counter() - t0)
     # fraction of one step the sample covers: its tokens x heads over all sequences, heads and layers
@@ -303,6 +338,7 @@ def run_ours(args, cfg):
     by_step = kv_bytes(cfg, plan["lens"]) * layers * (world if mode == "replicas" else 1)   # one step, all ranks
     cache_bytes = sum(t.numel() for t in caches[0])
     lib = uq_cuda.lib()
+    fmt = cfg.get("fmt", 0)
 
     def step(i, qq=q, btt=bt, sll=sl, oo=out):
         o = None
@@ -313,7 +349,7 @@ def run_ours(args, cfg):
             if mode == "context":
                 o = uq_cuda.uq_decode_context_split(qq, kc, ks, vc, vs, btt, sll, po, nsplit=nsplit)
             else:
-                o = uq_cuda.uq_decode_cuda(qq, kc, ks, vc, vs, btt, sll, nsplit=nsplit, workspace=ws, out=oo)
+                o = uq_cuda.uq_decode_cuda(qq, kc, ks, vc, vs, btt, sll, nsplit=nsplit, workspace=ws, out=oo, fmt=fmt, k_ts=case["k_ts"], v_ts=case["v_ts"])
         return o
 
     def barrier():
@@ -487,7 +523,7 @@ def run_ours(args, cfg):
             "clocks": clk.summary(), "device_status": list(status)}
     # ---- CPU baseline beside it (N = 1 only), and a parity check of sequence 0 for free
     if world == 1 and not args.no_cpu:
-        t_seq, ref0, cores = cpu_sample(case_to_numpy(case), steps=2, warmup=1)
+        t_seq, ref0, cores = cpu_sample(case_to_numpy(case), steps=2, warmup=1, nvfp4=(case["k_ts"], case["v_ts"]) if fmt == 1 else None)
         scale = float(plan["lens"].sum()) / float(plan["lens"][0]) * layers
         t_step = t_seq * scale
         line["cpu_baseline"] = {"value": by_step / t_step / 1e12, "unit": "TB/s", "cores": cores, "kind": "port", "us_per_layer_call": t_step * 1e6 / layers,
@@ -512,10 +548,16 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS))
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (profiler captures use a shorter one; the JSON says so)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--fmt", type=int, default=0, choices=[0, 1], help="cache format: 0 UltraQuant (the headline), 1 NVFP4 (configurations 1 and 3)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.steps <= 0:
         args.steps = 200 if cfg["layers"] == 1 else 10
+    if args.fmt == 1:
+        if cfg["append"] or cfg["shard"] == "context":
+            raise SystemExit("--fmt 1 (NVFP4) runs configurations 1 and 3: the append kernel and the context split serve the UltraQuant cache")
+        cfg["fmt"] = 1
+        cfg["name"] += " NVFP4 cache (e4m3fn scale per 16 channels)"
     if args.ctx:
         cfg["ctx"] = args.ctx
         cfg["name"] += f" (context overridden to {args.ctx})"
