@@ -24,7 +24,8 @@ __device__ unsigned int g_uq_status[4];
 constexpr size_t kStaticScratchFloats = (size_t)24 * 1024 * 1024 / sizeof(float);
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
-cudaError_t uq_append_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, cudaStream_t);
+cudaError_t uq_append_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, cudaStream_t, int flags, float c);
+cudaError_t uq_fwht_dispatch(const void*, void*, long long, int, int, cudaStream_t);
 cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
@@ -165,8 +166,19 @@ int uqb_decode_launch_ws(const UQParams* p, void* workspace, int nwarps, int sta
 
 int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value, const int64_t* slots,
                       int T, int HKV, int D, int PAGE, int dtype, void* stream) {
-  cudaError_t e = uq_append_dispatch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, reinterpret_cast<cudaStream_t>(stream));
+  return uqb_append_ex_launch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, 0, 0.f, stream);
+}
+
+int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value, const int64_t* slots,
+                         int T, int HKV, int D, int PAGE, int dtype, int flags, float c, void* stream) {
+  cudaError_t e = uq_append_dispatch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, reinterpret_cast<cudaStream_t>(stream), flags, c);
   if (e == cudaSuccess && T > 0) g_launches += 1;
+  return (int)e;
+}
+
+int uqb_fwht_launch(const void* x, void* out, long long rows, int D, int dtype, void* stream) {
+  cudaError_t e = uq_fwht_dispatch(x, out, rows, D, dtype, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && rows > 0) g_launches += 1;
   return (int)e;
 }
 

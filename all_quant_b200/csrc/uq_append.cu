@@ -6,6 +6,15 @@
 // channels of each 128-channel slab, so a scale group is eight lanes and the group maximum is three
 // shuffles.  HBM traffic is the input row plus D/2 + D/32 bytes out: the kernel is launch-latency
 // sized for a decode step, so key and value go in one launch.
+//
+// Two options of the reference's configurable quantiser ride in the same kernel (flags):
+//   1  the key row is rotated by the orthonormal Walsh-Hadamard transform over head_dim before it is encoded
+//      (reference uqmt/quant.py:84-98 fwht; K and Q rotated alike leave q.k unchanged, V is not rotated): the same
+//      butterfly order in fp32 (stages 1 and 2 in the lane's registers, 4..64 by shuffles, 128 across the two slabs of
+//      head_dim 256), one division by (float)sqrt(D), and for a 16-bit input the rounding to that type which the
+//      reference's function applies to its result.  uq_fwht_kernel is the same transform alone, for the queries.
+//   2  the 'paper' scale rule E = round(log2(c * amax)) (half to even), values clipped at +-6
+//      (reference uqmt/quant.py:52-60, quantize_on_write's rule argument :197-206) instead of ceil(log2(amax / 6)).
 #include "uq_common.cuh"
 
 namespace {
@@ -18,15 +27,57 @@ template <>
 UQ_DEV float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <>
 UQ_DEV float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T>
+UQ_DEV T from_f32(float v);
+template <>
+UQ_DEV float from_f32<float>(float v) { return v; }
+template <>
+UQ_DEV __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+UQ_DEV __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+constexpr int kRotateK = 1, kPaperRule = 2;
+
+// Orthonormal Walsh-Hadamard transform of one row of D = 64 / 128 / 256 values held by a warp: lane l owns channels
+// 128 s + 4 l .. + 3 of slab s (lanes 16.. hold zeros at D = 64).  Stage h pairs (i, i + h) -> (a + b, a - b), h ascending.
+UQ_DEV void warp_fwht(float (&x)[2][4], int D, int lane) {
+#pragma unroll
+  for (int s = 0; s < 2; s++) {
+    float a = x[s][0], b = x[s][1], c = x[s][2], d = x[s][3];
+    x[s][0] = a + b; x[s][1] = a - b; x[s][2] = c + d; x[s][3] = c - d;            // h = 1
+    a = x[s][0]; b = x[s][1]; c = x[s][2]; d = x[s][3];
+    x[s][0] = a + c; x[s][2] = a - c; x[s][1] = b + d; x[s][3] = b - d;            // h = 2
+  }
+  const int within = D < 128 ? D : 128;
+  for (int m = 1; 4 * m < within; m <<= 1) {                                       // h = 4 m
+#pragma unroll
+    for (int s = 0; s < 2; s++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float p = __shfl_xor_sync(0xffffffffu, x[s][i], m);
+        x[s][i] = (lane & m) ? p - x[s][i] : x[s][i] + p;
+      }
+  }
+  if (D == 256) {                                                                  // h = 128
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float a = x[0][i], b = x[1][i]; x[0][i] = a + b; x[1][i] = a - b; }
+  }
+  const float div = (float)sqrt((double)D);
+#pragma unroll
+  for (int s = 0; s < 2; s++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) x[s][i] = __fdiv_rn(x[s][i], div);
+}
 
 // Scale exponent of a group: clamp(ceil(log2(max(amax, 1e-30) / 6)), -127, 127), evaluated as the
 // reference evaluates it in fp32.  log2 is taken in double and rounded to fp32: that reproduces the
 // correctly rounded fp32 log2 of the reference's CPU kernels, including the points a few ulp above a
 // power of two where the fp32 result rounds down to the integer and ceil() does not step up.
-UQ_DEV int group_exponent(float amax) {
+UQ_DEV int group_exponent(float amax, bool paper, float c) {
   amax = fmaxf(amax, 1e-30f);
-  const float r = __fdiv_rn(amax, 6.0f);
-  float e = ceilf((float)log2((double)r));
+  float e;
+  if (paper) e = rintf((float)log2((double)__fmul_rn(c, amax)));   // torch.round: half to even
+  else e = ceilf((float)log2((double)__fdiv_rn(amax, 6.0f)));
   e = fminf(fmaxf(e, -127.0f), 127.0f);
   return (int)e;
 }
@@ -44,7 +95,8 @@ UQ_DEV unsigned encode_e2m1(float x, float scale) {
 template <typename T>
 __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
                                                         uint8_t* __restrict__ vs, const T* __restrict__ key, const T* __restrict__ value,
-                                                        const int64_t* __restrict__ slots, int T_tok, int HKV, int D, int PAGE, int nstream) {
+                                                        const int64_t* __restrict__ slots, int T_tok, int HKV, int D, int PAGE, int nstream,
+                                                        int flags, float c) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int total = T_tok * HKV * nstream;
@@ -59,18 +111,31 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
   const T* src = (stream == 0 ? key : value) + ((size_t)t * HKV + h) * D;
   uint8_t* codes = (stream == 0 ? kc : vc) + row * (D / 2);
   uint8_t* scales = (stream == 0 ? ks : vs) + row * (D / 32);
-  for (int base = 0; base < D; base += 128) {
-    const int ch = base + lane * 4;
-    const bool live = ch < D;   // D = 64: lanes 16..31 idle
-    float x[4] = {0.f, 0.f, 0.f, 0.f};
-    if (live) {
+  float xs[2][4];
 #pragma unroll
-      for (int i = 0; i < 4; i++) x[i] = to_f32<T>(src[ch + i]);
-    }
+  for (int sl = 0; sl < 2; sl++) {
+    const int ch = sl * 128 + lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) xs[sl][i] = ch < D ? to_f32<T>(src[ch + i]) : 0.f;
+  }
+  if ((flags & kRotateK) && stream == 0) {
+    warp_fwht(xs, D, lane);
+#pragma unroll
+    for (int sl = 0; sl < 2; sl++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) xs[sl][i] = to_f32<T>(from_f32<T>(xs[sl][i]));   // the reference's transform returns its input's type
+  }
+  const bool paper = (flags & kPaperRule) != 0;
+#pragma unroll
+  for (int sl = 0; sl < 2; sl++) {
+    const int ch = sl * 128 + lane * 4;
+    if (sl * 128 >= D) break;
+    const bool live = ch < D;   // D = 64: lanes 16..31 idle
+    const float* x = xs[sl];
     float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
     for (int m = 1; m < 8; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-    const int e = group_exponent(amax);
+    const int e = group_exponent(amax, paper, c);
     // 2^e as fp32; e = -127 is the denormal 2^-127
     const float scale = e == -127 ? __int_as_float(0x00400000) : __int_as_float((e + 127) << 23);
     if (live) {
@@ -82,23 +147,60 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
   }
 }
 
+// The transform alone (the queries of a cache whose keys were rotated): one warp per row, out may be x.
+template <typename T>
+__global__ void __launch_bounds__(128) uq_fwht_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows, int D) {
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float xs[2][4];
+#pragma unroll
+  for (int sl = 0; sl < 2; sl++) {
+    const int ch = sl * 128 + lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) xs[sl][i] = ch < D ? to_f32<T>(x[row * D + ch + i]) : 0.f;
+  }
+  warp_fwht(xs, D, lane);
+#pragma unroll
+  for (int sl = 0; sl < 2; sl++) {
+    const int ch = sl * 128 + lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (ch < D) out[row * D + ch + i] = from_f32<T>(xs[sl][i]);
+  }
+}
+
 }  // namespace
 
-// dtype: 0 fp32, 1 bf16, 2 fp16.  value/vc/vs may be null (single-stream form).
+cudaError_t uq_fwht_dispatch(const void* x, void* out, long long rows, int D, int dtype, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (!x || !out || rows < 0 || !(D == 64 || D == 128 || D == 256) || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
+  const long long blocks = (rows + 3) / 4;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidValue;
+  switch (dtype) {
+    case 0: uq_fwht_kernel<float><<<(int)blocks, 128, 0, s>>>((const float*)x, (float*)out, rows, D); break;
+    case 1: uq_fwht_kernel<__nv_bfloat16><<<(int)blocks, 128, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, D); break;
+    default: uq_fwht_kernel<__half><<<(int)blocks, 128, 0, s>>>((const __half*)x, (__half*)out, rows, D); break;
+  }
+  return cudaGetLastError();
+}
+
+// dtype: 0 fp32, 1 bf16, 2 fp16.  value/vc/vs may be null (single-stream form).  flags: 1 rotate the keys, 2 'paper' rule with constant c.
 cudaError_t uq_append_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
-                               const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, cudaStream_t s) {
+                               const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, cudaStream_t s, int flags, float c) {
   if (T == 0) return cudaSuccess;   // nothing to write; empty tensors may come with null pointers
   if (!kc || !ks || !key || !slots) return cudaErrorInvalidValue;
   const bool two = value != nullptr;
   if (two && (!vc || !vs)) return cudaErrorInvalidValue;
   if (!(D == 64 || D == 128 || D == 256) || PAGE <= 0 || HKV <= 0 || T < 0 || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
+  if ((flags & ~3) || ((flags & 2) && !(c > 0.f))) return cudaErrorInvalidValue;
   const int nstream = two ? 2 : 1;
   const long long warps = (long long)T * HKV * nstream;
   const int blocks = (int)((warps + 3) / 4);
   switch (dtype) {
-    case 0: uq_append_kernel<float><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, nstream); break;
-    case 1: uq_append_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, slots, T, HKV, D, PAGE, nstream); break;
-    default: uq_append_kernel<__half><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, nstream); break;
+    case 0: uq_append_kernel<float><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, nstream, flags, c); break;
+    case 1: uq_append_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, slots, T, HKV, D, PAGE, nstream, flags, c); break;
+    default: uq_append_kernel<__half><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, nstream, flags, c); break;
   }
   return cudaGetLastError();
 }

@@ -33,7 +33,7 @@ class UQParams(ctypes.Structure):
 
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
-           "uqb_has_sm90", "uqb_append_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes")
 
@@ -54,6 +54,8 @@ def lib():
         L.uqb_decode_launch.argtypes = [pp, i, i, vp]
         L.uqb_decode_launch_ws.argtypes = [pp, vp, i, i, vp]
         L.uqb_append_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
+        L.uqb_append_ex_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ctypes.c_float, vp]
+        L.uqb_fwht_launch.argtypes = [vp, vp, ctypes.c_longlong, i, i, vp]
         L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
         L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
         L.uqb_tree_decode_launch.argtypes = [pp, vp, vp]
@@ -291,10 +293,39 @@ def uq_decode_static(q, kc, ks, vc, vs, block_table, seq_lens, out, *, nsplit=No
 _DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 
-def append_kv(kc, ks, vc, vs, key, value, slot_mapping):
+PAPER_C = 0.156   # the constant of the 'paper' scale rule (reference uqmt/quant.py:35)
+
+
+def _rule_flags(rule, c, rotate_k=False):
+    if rule not in ("ceil", "paper"):
+        raise ValueError(rule)
+    return (1 if rotate_k else 0) | (2 if rule == "paper" else 0), float(PAPER_C if c is None else c)
+
+
+def fwht(x, out=None):
+    """Orthonormal Walsh-Hadamard transform along the last axis (reference uqmt/quant.py:84-98), D in {64,128,256}: what the
+    queries of a cache with rotated keys go through (rotate_kq, :105-107).  Same dtype out as in; `out` may be `x`."""
+    _need_cuda(x)
+    if x.dtype not in _DTYPE:
+        raise RuntimeError("x must be fp32, bf16 or fp16")
+    x = x.contiguous()
+    out = torch.empty_like(x) if out is None else out
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out must be contiguous with x's shape and dtype")
+    D = x.shape[-1]
+    with torch.cuda.device(x.device):
+        err = lib().uqb_fwht_launch(x.data_ptr(), out.data_ptr(), x.numel() // max(1, D), D, _DTYPE[x.dtype], _stream(x))
+    _check(err, "uq_fwht_launch")
+    return out
+
+
+def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule="ceil", c=None):
     """Quantize new key/value [T,Hkv,D] and write them at flat slots (slot = physical_page * PAGE + offset):
     the cache-append hook of an engine (reference uqmt/vllm_adapter.py:48-59).  One kernel launch for both streams;
-    bytes identical to the reference encoder.  Negative slots are skipped."""
+    bytes identical to the reference encoder.  Negative slots are skipped.
+    rotate_k: the keys go through the orthonormal Hadamard transform first (feed the verify call fwht(q));
+    rule / c: the scale rule of the reference's configurable quantiser (uqmt/quant.py:52-70), 'ceil' or 'paper'."""
+    flags, c = _rule_flags(rule, c, rotate_k)
     _need_cuda(kc, ks, vc, vs, key, value, slot_mapping)
     if key.dtype not in _DTYPE or value.dtype != key.dtype:
         raise RuntimeError("key/value must both be fp32, bf16 or fp16")
@@ -305,17 +336,15 @@ def append_kv(kc, ks, vc, vs, key, value, slot_mapping):
         if not t.is_contiguous() or t.dtype != torch.uint8:
             raise RuntimeError("cache tensors must be contiguous uint8")
     with torch.cuda.device(key.device):
-        err = lib().uqb_append_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
-                                      slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], _stream(key))
+        err = lib().uqb_append_ex_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                         slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], flags, c, _stream(key))
     _check(err, "uq_append_launch")
 
 
 def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):
     """Quantize x [N,Hkv,D] and scatter into `code` [pages,Hkv,PAGE,D/2] / `scale` [pages,Hkv,PAGE,D/32] at flat
-    slots [N] (reference uqmt/quant.py:197-206).  Only the reference's default rule "ceil" (the cache's own
-    encoder) is served."""
-    if rule != "ceil":
-        raise NotImplementedError("only rule='ceil' (the UltraQuant cache encoder) is served")
+    slots [N] (reference uqmt/quant.py:197-206); rule 'ceil' (the cache's own encoder) or 'paper' with constant c."""
+    flags, c = _rule_flags(rule, c)
     _need_cuda(x, code, scale, slots)
     if x.dtype not in _DTYPE:
         raise RuntimeError("x must be fp32, bf16 or fp16")
@@ -323,8 +352,8 @@ def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):
     x = x.contiguous()
     sl = slots.to(torch.int64).contiguous()
     with torch.cuda.device(x.device):
-        err = lib().uqb_append_launch(code.data_ptr(), scale.data_ptr(), None, None, x.data_ptr(), None, sl.data_ptr(),
-                                      N, HKV, D, code.shape[2], _DTYPE[x.dtype], _stream(x))
+        err = lib().uqb_append_ex_launch(code.data_ptr(), scale.data_ptr(), None, None, x.data_ptr(), None, sl.data_ptr(),
+                                         N, HKV, D, code.shape[2], _DTYPE[x.dtype], flags, c, _stream(x))
     _check(err, "uq_append_launch")
 
 

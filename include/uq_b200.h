@@ -45,6 +45,20 @@ int uqb_has_sm90(void);
 int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                       const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, void* stream);
 
+/* The same with the options of the reference's configurable quantiser (reference uqmt/quant.py):
+ *   flags & 1   the KEY rows are rotated by the orthonormal Walsh-Hadamard transform over head_dim before they are
+ *               encoded (fwht, uqmt/quant.py:84-98: the transform in fp32, its result rounded to the input's type);
+ *               values are never rotated.  The queries of such a cache go through uqb_fwht_launch first.
+ *   flags & 2   scale rule 'paper': E = round(log2(c * amax)), half to even, values clipped at +-6
+ *               (scale_exponent, uqmt/quant.py:52-60; quantize_on_write(rule="paper", c), :197-206); c > 0.
+ * flags = 0 is uqb_append_launch.  Bit-exact with quantize(fwht(key), rule, c) of the reference's CPU functions. */
+int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
+                         const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, int flags, float c, void* stream);
+
+/* Orthonormal Walsh-Hadamard transform along the last axis of x [rows, D] (D in {64,128,256}; dtype as above),
+ * out may be x: the reference's fwht (uqmt/quant.py:84-98, rotate_kq :105-107) for the queries. */
+int uqb_fwht_launch(const void* x, void* out, long long rows, int D, int dtype, void* stream);
+
 /* ---- context-split partials and their merge (no counterpart in the reference) ---------------- */
 
 /* Attention of all queries over ONE SHARD of each sequence's context.  The cache and block_table in

@@ -43,15 +43,22 @@ int uqo_max_threads(void) {
  *   byte  = e + 127
  * Packing: low nibble = even element.
  */
-static void encode_group(const float* x, uint8_t* packed16, uint8_t* scale) {
+static void encode_group_rule(const float* x, uint8_t* packed16, uint8_t* scale, int rule, float c) {
   float amax = 0.0f;
   for (int i = 0; i < 32; i++) {
     float a = fabsf(x[i]);
     if (a > amax) amax = a;
   }
   if (!(amax >= 1e-30f)) amax = 1e-30f;
-  float r = amax / 6.0f;
-  float e = ceilf((float)log2((double)r));
+  float e;
+  if (rule == 0) {
+    float r = amax / 6.0f;
+    e = ceilf((float)log2((double)r));
+  } else {
+    /* 'paper' rule (uqmt/quant.py:52-60): round(log2(c * amax)), torch.round = half to even; values then clip at +-6 */
+    float r = c * amax;
+    e = rintf((float)log2((double)r));
+  }
   if (e < -127.0f) e = -127.0f;
   if (e > 127.0f) e = 127.0f;
   float sc = (float)ldexp(1.0, (int)e); /* exp2(e) in fp32; 2^-127 is a representable denormal */
@@ -71,6 +78,34 @@ static void encode_group(const float* x, uint8_t* packed16, uint8_t* scale) {
   }
   for (int i = 0; i < 16; i++) packed16[i] = (uint8_t)(codes[2 * i] | (codes[2 * i + 1] << 4));
   *scale = (uint8_t)((int)e + 127);
+}
+
+static void encode_group(const float* x, uint8_t* packed16, uint8_t* scale) { encode_group_rule(x, packed16, scale, 0, 0.0f); }
+
+/* The configurable quantiser (uqmt/quant.py:63-70 quantize): rule 0 = 'ceil' (the cache's own encoder), 1 = 'paper' with constant c. */
+void uqo_quantize_rule(const float* x, size_t n_groups, int rule, float c, uint8_t* packed, uint8_t* scales) {
+#pragma omp parallel for schedule(static)
+  for (long long g = 0; g < (long long)n_groups; g++) encode_group_rule(x + g * 32, packed + g * 16, scales + g, rule, c);
+}
+
+/* Orthonormal fast Walsh-Hadamard transform of each row of n values, n a power of two (uqmt/quant.py:84-98 fwht): stages
+ * h = 1, 2, 4, ...: within blocks of 2h, (a, b) = (x[i], x[i + h]) -> (a + b, a - b); then every value divided by
+ * (float)sqrt(n), all in fp32. */
+void uqo_fwht(const float* x, size_t rows, int n, float* out) {
+  const float div = (float)sqrt((double)n);
+#pragma omp parallel for schedule(static)
+  for (long long r = 0; r < (long long)rows; r++) {
+    float* y = out + r * n;
+    memcpy(y, x + r * n, sizeof(float) * (size_t)n);
+    for (int h = 1; h < n; h *= 2)
+      for (int b0 = 0; b0 < n; b0 += 2 * h)
+        for (int i = b0; i < b0 + h; i++) {
+          const float a = y[i], b = y[i + h];
+          y[i] = a + b;
+          y[i + h] = a - b;
+        }
+    for (int i = 0; i < n; i++) y[i] = y[i] / div;
+  }
 }
 
 /* x: n_groups*32 floats -> packed n_groups*16 bytes, scales n_groups bytes. */

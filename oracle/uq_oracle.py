@@ -41,6 +41,8 @@ def lib():
         L.uqo_reference.argtypes = [vp] * 9 + [i32] * 7 + [f32, vp, vp]
         L.uqo_merge.argtypes = [vp, vp, i32, sz, i32, vp]
         L.uqo_tree_reference.argtypes = [vp] * 8 + [i32] * 7 + [f32, vp]
+        L.uqo_quantize_rule.argtypes = [vp, ctypes.c_size_t, i32, f32, vp, vp]
+        L.uqo_fwht.argtypes = [vp, ctypes.c_size_t, i32, vp]
         L.uqo_e4m3fn_table.argtypes = [vp]
         L.uqo_reference_nvfp4.argtypes = [vp] * 7 + [i32] * 7 + [f32, f32, f32, vp]
         _LIB = L
@@ -75,6 +77,27 @@ def quantize_fp4(x):
     scales = np.empty(x.shape[:-1] + (D // 32,), np.uint8)
     lib().uqo_quantize_fp4(_p(x), x.size // 32, _p(packed), _p(scales))
     return packed, scales
+
+
+def quantize(x, rule="ceil", c=0.156):
+    """The configurable quantiser (uqmt/quant.py:63-70): rule 'ceil' = quantize_fp4, 'paper' = round(log2(c * amax))."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    D = x.shape[-1]
+    assert D % 32 == 0 and rule in ("ceil", "paper")
+    packed = np.empty(x.shape[:-1] + (D // 2,), np.uint8)
+    scales = np.empty(x.shape[:-1] + (D // 32,), np.uint8)
+    lib().uqo_quantize_rule(_p(x), x.size // 32, 0 if rule == "ceil" else 1, float(c), _p(packed), _p(scales))
+    return packed, scales
+
+
+def fwht(x):
+    """Orthonormal Walsh-Hadamard transform along the last axis (uqmt/quant.py:84-98), fp32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[-1]
+    assert n & (n - 1) == 0
+    out = np.empty_like(x)
+    lib().uqo_fwht(_p(x), x.size // n, n, _p(out))
+    return out
 
 
 def dequantize_fp4(packed, scales):

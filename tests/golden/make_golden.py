@@ -10,7 +10,8 @@ Two kinds of fixture:
        uqmt.vllm_adapter.append_kv, uqmt.tree.tree_reference), for the cases the frozen vectors do not cover.
   nvfp4_cuda_<set>.npz   the reference's frozen NVFP4 vectors (cuda/vectors_nvfp4), repacked the same way; the scale
       arrays are e4m3fn bytes [pages,Hkv,PAGE,D/16] and `ts` holds the per-tensor scales (k_ts, v_ts).
-`--tree-only` regenerates tree_cases.npz alone, `--nvfp4-only` the nvfp4_cuda_* files alone.
+`--tree-only` regenerates tree_cases.npz alone, `--nvfp4-only` the nvfp4_cuda_* files alone, `--rotate-only` gen_rotate.npz
+(uqmt.quant.fwht and the 'paper' scale rule of uqmt.quant.quantize) alone.
 """
 import os
 import sys
@@ -186,6 +187,29 @@ def gen_append():
          kc1=kc.numpy(), ks1=ks.numpy(), vc1=vc.numpy(), vs1=vs.numpy())
 
 
+def gen_rotate():
+    """The engine-side options of the append: uqmt.quant.fwht (orthonormal Hadamard of K and Q) and the 'paper' scale rule
+    of uqmt.quant.quantize, on seeded rows with a wide range of magnitudes, zero rows and exact powers of two included."""
+    from uqmt.quant import PAPER_C, fwht, quantize
+    g = torch.Generator().manual_seed(77)
+    arrs = {"c": np.float32(PAPER_C)}
+    for D in (64, 128, 256):
+        x = torch.randn(24, 2, D, generator=g) * torch.exp(2.0 * torch.randn(24, 2, 1, generator=g))
+        x[3] = 0.0
+        x[5] = torch.exp2(torch.randint(-6, 6, (2, D), generator=g).float())
+        xr = fwht(x)
+        arrs[f"d{D}_x"] = x.numpy()
+        arrs[f"d{D}_fwht"] = xr.numpy()
+        for name, src in (("plain", x), ("rot", xr)):
+            for rule in ("ceil", "paper"):
+                p, sc = quantize(src, rule, PAPER_C)
+                arrs[f"d{D}_{name}_{rule}_codes"], arrs[f"d{D}_{name}_{rule}_scales"] = p.numpy(), sc.numpy()
+        q = torch.randn(6, 4, D, generator=g).bfloat16()
+        arrs[f"d{D}_q"] = q.view(torch.int16).numpy().view(np.uint16)
+        arrs[f"d{D}_q_fwht"] = fwht(q).view(torch.int16).numpy().view(np.uint16)
+    save("gen_rotate.npz", **arrs)
+
+
 def gen_tree():
     """Tree-masked verify: answers of the reference's own oracle (uqmt/tree.py tree_reference) for chain, star and seeded
     random parent trees, one case with a different tree per sequence.  One file, cases t0..tN."""
@@ -225,6 +249,9 @@ if __name__ == "__main__":
     if "--nvfp4-only" in sys.argv:
         repack_cuda_vectors("vectors_nvfp4", "nvfp4_cuda_", 16)
         sys.exit(0)
+    if "--rotate-only" in sys.argv:
+        gen_rotate()
+        sys.exit(0)
     if "--tree-only" in sys.argv:
         gen_tree()
         sys.exit(0)
@@ -235,3 +262,4 @@ if __name__ == "__main__":
     gen_cases()
     gen_append()
     gen_tree()
+    gen_rotate()
