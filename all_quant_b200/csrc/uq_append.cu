@@ -73,11 +73,17 @@ UQ_DEV void warp_fwht(float (&x)[2][4], int D, int lane) {
 // reference evaluates it in fp32.  log2 is taken in double and rounded to fp32: that reproduces the
 // correctly rounded fp32 log2 of the reference's CPU kernels, including the points a few ulp above a
 // power of two where the fp32 result rounds down to the integer and ceil() does not step up.
+// The double-precision log2 is slow on this part, and it only matters where the fp32 value lies within rounding
+// distance of the point that decides the integer (an integer for ceil, a half for round): log2f (1 ulp, at most 2e-5 for
+// |log2| <= 150) settles every other input, and the rare group closer than 1e-3 to a deciding point takes the double.
 UQ_DEV int group_exponent(float amax, bool paper, float c) {
   amax = fmaxf(amax, 1e-30f);
-  float e;
-  if (paper) e = rintf((float)log2((double)__fmul_rn(c, amax)));   // torch.round: half to even
-  else e = ceilf((float)log2((double)__fdiv_rn(amax, 6.0f)));
+  const float r = paper ? __fmul_rn(c, amax) : __fdiv_rn(amax, 6.0f);
+  float t = log2f(r);
+  const float frac = t - floorf(t);
+  const bool near = paper ? fabsf(frac - 0.5f) < 1e-3f : (frac < 1e-3f || frac > 1.0f - 1e-3f);
+  if (near) t = (float)log2((double)r);
+  float e = paper ? rintf(t) : ceilf(t);   // rintf = torch.round: half to even
   e = fminf(fmaxf(e, -127.0f), 127.0f);
   return (int)e;
 }

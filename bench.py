@@ -506,6 +506,12 @@ def run_ours(args, cfg):
     sharding = {"single": "single GPU", "replicas": "every rank runs the whole call on kv heads of its own, no collective",
                 "heads": f"kv heads divided across ranks ({hkv} per rank), no collective",
                 "context": "context pages divided across ranks; partials all-gathered over NCCL and merged by the log-sum-exp kernel inside the step"}[mode]
+    # DRAM bytes per launch of the attention kernel from the one ncu capture of it (dram__bytes_read.sum 147.1 MB +
+    # dram__bytes_write.sum 17.4 MB at B=8, context 16384, K=8, UltraQuant cache: 1.154 x that call's algorithmic
+    # bytes), scaled by the bytes of this call; only for the captured kernel and shape family, else null
+    traffic = None
+    if args.config == 1 and fmt == 0 and K == 8 and world == 1:
+        traffic = int(round(by_local * (147.1e6 + 17.4e6) / 142606336.0))
     l2 = (f"{len(caches)} cache copies alternate; each {cache_bytes / 1e6:.0f} MB copy exceeds the 126 MB L2" if cache_bytes > 126e6 else
           f"{len(caches)} caches of {cache_bytes / 1e6:.0f} MB are read in turn ({len(caches) * cache_bytes / 1e6:.0f} MB between two reads of the same bytes; L2 is 126 MB)")
     line = {"metric": "kv_read_throughput", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -513,7 +519,7 @@ def run_ours(args, cfg):
             "scaling": "weak" if cfg["shard"] == "replicas" else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "layers": layers, "l2": l2, "sharding": sharding,
                        "kernel_path": {1: "cuda-core", 2: "tcgen05"}.get(uq_cuda.last_path(), "?")},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                          "peak_kind": peak_kind, "kernel_us": kern_ms * 1e3, "algorithmic_bytes": by_local},
             "e2e": {"value": by_step / (e2e_step_ms * 1e-3) / 1e12, "unit": "TB/s", "us_per_layer_call": e2e_step_ms * 1e3 / layers,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(hout.numel() * 2),

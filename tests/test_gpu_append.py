@@ -11,7 +11,7 @@ from tests.cases import load
 pytestmark = pytest.mark.gpu
 
 
-def encode_on_gpu(x, dtype=torch.float32):
+def encode_on_gpu(x, dtype=torch.float32, rule="ceil", c=None):
     """x fp32 numpy [N, D] -> (packed, scales) via quantize_on_write into a fresh one-head cache."""
     N, D = x.shape
     PAGE = 64
@@ -19,7 +19,7 @@ def encode_on_gpu(x, dtype=torch.float32):
     code = torch.zeros(pages, 1, PAGE, D // 2, dtype=torch.uint8, device="cuda")
     scale = torch.zeros(pages, 1, PAGE, D // 32, dtype=torch.uint8, device="cuda")
     xt = torch.from_numpy(x).cuda().to(dtype).reshape(N, 1, D)
-    uq_cuda.quantize_on_write(xt, code, scale, torch.arange(N, device="cuda"))
+    uq_cuda.quantize_on_write(xt, code, scale, torch.arange(N, device="cuda"), rule=rule, c=c)
     torch.cuda.synchronize()
     return code.reshape(-1, D // 2)[:N].cpu().numpy(), scale.reshape(-1, D // 32)[:N].cpu().numpy()
 
@@ -40,6 +40,32 @@ def test_encoder_ties_specials_and_every_scale_boundary():
     p, s = encode_on_gpu(x[:n].reshape(n // 2, 64))  # two groups per row of a D=64 cache
     assert np.array_equal(s.reshape(-1), z["g32_scales"][:n].reshape(-1))
     assert np.array_equal(p.reshape(n, 16), z["g32_packed"][:n])
+
+
+@pytest.mark.parametrize("rule", ["ceil", "paper"])
+def test_scale_exponent_around_its_deciding_points(rule):
+    """Group maxima a few ulp either side of every point where the exponent steps (6 * 2^n for 'ceil', 2^(n + 1/2) / c for
+    'paper'), plus a dense random sweep: the kernel's fp32 shortcut for the logarithm must never change the byte."""
+    c = 0.156
+    n = np.arange(-100, 101, dtype=np.float64)
+    centre = (6.0 * 2.0 ** n) if rule == "ceil" else (2.0 ** (n + 0.5) / np.float64(np.float32(c)))
+    centre = centre.astype(np.float32)
+    amax = []
+    for k in range(-6, 7):
+        a = centre.copy()
+        for _ in range(abs(k)):
+            a = np.nextafter(a, np.float32(np.inf if k > 0 else 0), dtype=np.float32)
+        amax.append(a)
+    rng = np.random.default_rng(21)
+    amax.append(np.exp2(rng.uniform(-100, 100, 40000)).astype(np.float32))
+    amax = np.concatenate(amax)
+    amax = amax[: amax.size // 2 * 2]
+    x = (rng.uniform(-1, 1, (amax.size, 32)).astype(np.float32)) * amax[:, None]
+    x[:, 7] = amax * np.where(rng.random(amax.size) < 0.5, -1, 1).astype(np.float32)     # the group's maximum itself
+    want_p, want_s = O.quantize(x, rule, c)
+    p, s = encode_on_gpu(x.reshape(-1, 64), rule=rule, c=c)
+    assert np.array_equal(s.reshape(-1), want_s.reshape(-1))
+    assert np.array_equal(p.reshape(-1, 16), want_p)
 
 
 def test_append_kv_matches_reference_fixture():
