@@ -88,6 +88,8 @@ bool shape_ok(const UQParams& p) {
   return p.q && p.kc && p.ks && p.vc && p.vs && p.block_table && p.seq_lens && p.mo && p.ml;
 }
 
+cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s);
+
 cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s, const int32_t* tree_mask = nullptr) {
   if (!shape_ok(p)) return cudaErrorInvalidValue;
   if (tree_mask && p.K > 16) return cudaErrorInvalidValue;   // the reference's limit (uqmt/tree.py:135)
@@ -96,14 +98,45 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
   UQLaunch x{};
   x.pos_offset = pos_offset;
   x.tree_mask = tree_mask;
+  x.k_first = 0;
+  x.k_total = p.K;
+  x.len_cut = 0;
+  x.status = status_ptr();
+  if (!x.status) return cudaErrorInitializationError;
+  // More query rows than the tensor-core kernel takes in one launch (K * group > 64, up to the 128 of uq_block_m): the
+  // drafts are run as chunks of consecutive drafts, each a verify call of its own on the sequence cut after the chunk
+  // (see UQLaunch), sharing the caller's scratch one after the other.  Plain causal calls only: a tree may hide an
+  // earlier chunk's draft from a later query, which the cut does not express.
+  const int G = p.HQ / p.HKV;
+  const int per = G <= 64 ? 64 / G : 0;   // drafts per chunk
+  if (!tree_mask && p.K * G > 64 && per >= 1 && forced_path() != 1) {
+    UQParams pc = p;
+    pc.K = per;
+    UQLaunch xc = x;
+    xc.G = G;
+    xc.rows = per * G;
+    if (uq_verify_tc_serves(pc, xc)) {
+      for (int k0 = 0; k0 < p.K; k0 += per) {
+        pc.K = std::min(per, p.K - k0);
+        xc.k_first = k0;
+        xc.len_cut = p.K - k0 - pc.K;
+        cudaError_t e = run_one(pc, xc, o_part, lse_part, s);
+        if (e != cudaSuccess) return e;
+      }
+      return cudaSuccess;
+    }
+  }
+  return run_one(p, x, o_part, lse_part, s);
+}
+
+// One launch of a verify kernel and its combine; x carries the caller's pointers and the draft chunk.
+cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s) {
   x.G = p.HQ / p.HKV;
   x.rows = p.K * x.G;
   x.BM = uq_block_m(p.K, p.HQ, p.HKV);
   // NVFP4 (reference cuda/uq_decode.cu:604,384): k_ts is folded into the softmax scale, v_ts multiplies the output
   x.sc2 = p.sm_scale * (p.fmt == 1 ? p.k_ts : 1.f) * 1.4426950408889634f;
   x.out_scale = p.fmt == 1 ? p.v_ts : 1.f;
-  x.status = status_ptr();
-  if (!x.status) return cudaErrorInitializationError;
   const int forced = forced_path();
   bool tc = forced != 1 && uq_verify_tc_serves(p, x);
   if (forced == 2 && !tc) return cudaErrorInvalidValue;

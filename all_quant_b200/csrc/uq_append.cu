@@ -36,6 +36,31 @@ UQ_DEV __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_
 template <>
 UQ_DEV __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
+// four consecutive channels of a row as fp32: one 16-byte (fp32) or 8-byte (16-bit types) load when the row is aligned for it
+template <typename T>
+UQ_DEV void load4(const T* p, bool vec, float* out);
+template <>
+UQ_DEV void load4<float>(const float* p, bool vec, float* out) {
+  if (vec) { const float4 v = __ldg(reinterpret_cast<const float4*>(p)); out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w; }
+  else { for (int i = 0; i < 4; i++) out[i] = p[i]; }
+}
+template <>
+UQ_DEV void load4<__nv_bfloat16>(const __nv_bfloat16* p, bool vec, float* out) {
+  if (vec) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+    out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+  } else { for (int i = 0; i < 4; i++) out[i] = __bfloat162float(p[i]); }
+}
+template <>
+UQ_DEV void load4<__half>(const __half* p, bool vec, float* out) {
+  if (vec) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+  } else { for (int i = 0; i < 4; i++) out[i] = __half2float(p[i]); }
+}
+
 constexpr int kRotateK = 1, kPaperRule = 2;
 
 // Orthonormal Walsh-Hadamard transform of one row of D = 64 / 128 / 256 values held by a warp: lane l owns channels
@@ -90,8 +115,10 @@ UQ_DEV int group_exponent(float amax, bool paper, float c) {
 
 // e2m1 code of y = x / 2^e: nearest of {0,.5,1,1.5,2,3,4,6}, ties to the smaller magnitude (the
 // reference's first-index argmin), sign bit from (y < 0) whatever the magnitude.
-UQ_DEV unsigned encode_e2m1(float x, float scale) {
-  float y = __fdiv_rn(x, scale);
+// The division by the power-of-two scale is a multiplication by its reciprocal 2^-e, which is exact for every e in
+// [-127, 127] (2^127 and the denormal 2^-127 are both fp32 values): the same real quotient, so the same rounding.
+UQ_DEV unsigned encode_e2m1(float x, float inv_scale) {
+  float y = __fmul_rn(x, inv_scale);
   y = fminf(fmaxf(y, -6.0f), 6.0f);
   const float a = fabsf(y);
   unsigned c = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
@@ -112,17 +139,20 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
   const int t = warp / (nstream * HKV);
   const int64_t slot = slots[t];
   if (slot < 0) return;
-  const int64_t page = slot / PAGE, off = slot % PAGE;
+  int64_t page, off;
+  if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }   // the common case without a 64-bit division
+  else { page = slot / PAGE; off = slot % PAGE; }
   const size_t row = ((size_t)page * HKV + h) * PAGE + off;
   const T* src = (stream == 0 ? key : value) + ((size_t)t * HKV + h) * D;
   uint8_t* codes = (stream == 0 ? kc : vc) + row * (D / 2);
   uint8_t* scales = (stream == 0 ? ks : vs) + row * (D / 32);
+  const bool vec = ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) == 0;   // (rows are multiples of 64 channels)
   float xs[2][4];
 #pragma unroll
   for (int sl = 0; sl < 2; sl++) {
     const int ch = sl * 128 + lane * 4;
-#pragma unroll
-    for (int i = 0; i < 4; i++) xs[sl][i] = ch < D ? to_f32<T>(src[ch + i]) : 0.f;
+    if (ch < D) load4<T>(src + ch, vec, xs[sl]);
+    else xs[sl][0] = xs[sl][1] = xs[sl][2] = xs[sl][3] = 0.f;
   }
   if ((flags & kRotateK) && stream == 0) {
     warp_fwht(xs, D, lane);
@@ -142,8 +172,8 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 #pragma unroll
     for (int m = 1; m < 8; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
     const int e = group_exponent(amax, paper, c);
-    // 2^e as fp32; e = -127 is the denormal 2^-127
-    const float scale = e == -127 ? __int_as_float(0x00400000) : __int_as_float((e + 127) << 23);
+    // 1 / 2^e as fp32; e = 127 gives the denormal 2^-127
+    const float scale = e == 127 ? __int_as_float(0x00400000) : __int_as_float((127 - e) << 23);   // 2^-e
     if (live) {
       const unsigned c0 = encode_e2m1(x[0], scale), c1 = encode_e2m1(x[1], scale);
       const unsigned c2 = encode_e2m1(x[2], scale), c3 = encode_e2m1(x[3], scale);

@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
   const int h = row % p.HQ, j = (row / p.HQ) % p.K, b = row / (p.HQ * p.K);
   const int hk = h / x.G, r = j * x.G + (h % x.G);
   const int D = p.D;
+  const size_t orow = uq_draft_row(x, b, j) * p.HQ + h;   // the row of the caller's [B, K, HQ] arrays (a chunk of drafts writes its own rows)
   const size_t slot0 = uq_slot(p, b, hk, 0);
   // The slots' log-sum-exps are read lane-parallel (slot s by lane s mod 32: up to four per lane for nsplit <= 128), so the
   // row's maximum, weights and denominator cost a few loads instead of a serial chain of nsplit of them.
@@ -81,11 +82,11 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int d = lane + 32 * i;
-      if (d < D) o_part[(size_t)row * D + d] = acc[i] * inv;
+      if (d < D) o_part[orow * D + d] = acc[i] * inv;
     }
-    if (lane == 0) lse_part[row] = den > 0.f ? mx + log2f(den) : -INFINITY;
+    if (lane == 0) lse_part[orow] = den > 0.f ? mx + log2f(den) : -INFINITY;
   } else {
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * D;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + orow * D;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int d = lane + 32 * i;

@@ -20,15 +20,24 @@ struct UQLaunch {
   int BM;                     // row stride of the scratch (uq_block_m)
   float sc2;                  // sm_scale * log2(e) (times k_ts for an NVFP4 cache): scores live in the exp2 domain
   float out_scale;            // multiplies the normalised output: 1, or v_ts for an NVFP4 cache
+  // A call with more query rows than one launch takes is run as chunks of consecutive drafts: this launch holds drafts
+  // k_first .. k_first + p.K - 1 of the caller's k_total (rows of q and out are indexed by the caller's draft number), and
+  // the len_cut = k_total - k_first - p.K drafts after the chunk do not exist for it: chunk draft j then sees the keys
+  // below (seq_len - len_cut) - p.K + j + 1 = seq_len - k_total + (k_first + j) + 1, the whole call's limit for that draft.
+  int k_first, k_total, len_cut;
   unsigned int* status;       // this device's status record (4 words), see uq_report
 };
 
 // Scratch slot (b, hk, s): rows are r = j * G + g (draft j, head g of the group), row stride BM.
 UQ_DEV size_t uq_slot(const UQParams& p, int b, int hk, int s) { return ((size_t)b * p.HKV + hk) * p.nsplit + s; }
 
+// Sequence length as this launch sees it, and the row of q / out that belongs to (sequence b, this launch's draft j).
+UQ_DEV int uq_seq_len(const UQParams& p, const UQLaunch& x, int b) { return p.seq_lens[b] - x.len_cut; }
+UQ_DEV size_t uq_draft_row(const UQLaunch& x, int b, int j) { return (size_t)b * x.k_total + x.k_first + j; }
+
 // Keys of sequence b held by this cache (whole context, or one shard of it).
 UQ_DEV int uq_n_local(const UQParams& p, const UQLaunch& x, int b, int* off_out) {
-  const int n = p.seq_lens[b];
+  const int n = uq_seq_len(p, x, b);
   const int off = x.pos_offset ? x.pos_offset[b] : 0;
   *off_out = off;
   long long cap = (long long)p.max_pages * p.PAGE;

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
 
   int off;
   const int n_loc = uq_n_local(p, x, b, &off);
-  const int n_glob = p.seq_lens[b];
+  const int n_glob = uq_seq_len(p, x, b);
   const int n_pages = (n_loc + p.PAGE - 1) / p.PAGE;
   const int pps = (n_pages + x.ns_eff - 1) / x.ns_eff;
   const int k0 = min(s * pps, n_pages) * p.PAGE;
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(kTile) uq_verify_fma_kernel(const UQParams p, 
       float v = 0.f;
       if (r < x.rows) {
         const int j = r / x.G, g = r % x.G;
-        v = __bfloat162float(q[(((size_t)b * p.K + j) * p.HQ + hk * x.G + g) * D + d]);
+        v = __bfloat162float(q[(uq_draft_row(x, b, j) * p.HQ + hk * x.G + g) * D + d]);
       }
       q_s[i / D][d] = v;
     }

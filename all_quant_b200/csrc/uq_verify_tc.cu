@@ -95,6 +95,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_TB(n)
 #endif
 
+#ifndef UQ_V64
+#define UQ_V64 4   // V-decode warps at 64 rows
+#endif
 #ifndef UQ_NSG4_AT
 #define UQ_NSG4_AT 32
 #endif
@@ -108,7 +111,7 @@ constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 __host__ __device__ constexpr int softmax_groups(int NT) { return NT >= UQ_NSG4_AT ? 4 : 2; }
 // With fewer than 64 rows the V decode is the longest role and the CTA has warps to spare: eight V warps, each thread
 // half of its key's scale groups; with 64 rows the softmax is, and issue slots are what it lacks: four V warps.
-__host__ __device__ constexpr int v_warps(int NT) { return NT < 64 ? 8 : 4; }
+__host__ __device__ constexpr int v_warps(int NT) { return NT < 64 ? 8 : UQ_V64; }
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 8 + v_warps(NT)) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
 __host__ __device__ constexpr bool block_scaled(int D) { return D == 128; }          // Q.K straight from the e2m1 codes and scale bytes (see Cfg::kBS)
@@ -949,7 +952,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       const bool careful = pass == 1 || ord >= 32 * kRedoWords;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
-      const int n_glob = p.seq_lens[sg.b];
+      const int n_glob = uq_seq_len(p, x, sg.b);
       // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
       // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
       // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
@@ -966,7 +969,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; j++) qv[j] = 0.f;
           if (i < kItems && n < rows) {
-            const uint4* src = reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + 2 * a;
+            const uint4* src = reinterpret_cast<const uint4*>(qg + ((uq_draft_row(x, sg.b, n / G)) * p.HQ + sg.hk * G + n % G) * D) + 2 * a;
             const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
             const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
@@ -1019,7 +1022,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         uint32_t amax = 0;   // bf16 magnitudes compare as integers
         for (int i = st; i < rows * (D / 8); i += kSm) {
           const int n = i / (D / 8), a = i % (D / 8);
-          const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + ((uq_draft_row(x, sg.b, n / G)) * p.HQ + sg.hk * G + n % G) * D) + a);
           const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int j = 0; j < 4; j++) amax = max(amax, max(w4[j] & 0x7FFFu, (w4[j] >> 16) & 0x7FFFu));
@@ -1040,7 +1043,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           const int n = i / (D / 8), a = i % (D / 8);
           uint4 w = make_uint4(0, 0, 0, 0);
           if (n < rows) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + (((size_t)sg.b * p.K + n / G) * p.HQ + sg.hk * G + n % G) * D) + a);
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(qg + ((uq_draft_row(x, sg.b, n / G)) * p.HQ + sg.hk * G + n % G) * D) + a);
             w.x = pack_f16x2(__uint_as_float(v.x << 16) * qf, __uint_as_float(v.x & 0xFFFF0000u) * qf);
             w.y = pack_f16x2(__uint_as_float(v.y << 16) * qf, __uint_as_float(v.y & 0xFFFF0000u) * qf);
             w.z = pack_f16x2(__uint_as_float(v.z << 16) * qf, __uint_as_float(v.z & 0xFFFF0000u) * qf);

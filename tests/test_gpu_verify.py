@@ -104,6 +104,34 @@ def test_scale_extremes():
     check_close(out.float().cpu().numpy() / mx, ref / mx, "scale extremes")
 
 
+@pytest.mark.parametrize("K,HQ,HKV,D", [(16, 16, 2, 128), (12, 16, 2, 128), (8, 32, 2, 64), (16, 8, 1, 256), (13, 14, 2, 128)])
+def test_more_than_64_query_rows_run_as_draft_chunks_on_the_tensor_core_kernel(K, HQ, HKV, D):
+    """K * group between 65 and 128 rows: consecutive drafts are verified in chunks of at most 64 rows, each chunk against
+    the sequence cut after it; answers follow the oracle, short sequences (fewer tokens than drafts) included."""
+    rng = np.random.default_rng(K * 100 + HQ)
+    B, PAGE = 3, 32
+    sl = np.array([900, 5, 333], np.int32)       # 5 < K: some drafts see nothing or only part of the tokens
+    npg = -(-int(sl.max()) // PAGE)
+    pages = B * npg
+    k = rng.standard_normal((pages, HKV, PAGE, D)).astype(np.float32) * np.exp(0.5 * rng.standard_normal((1, HKV, 1, D))).astype(np.float32)
+    v = rng.standard_normal((pages, HKV, PAGE, D)).astype(np.float32)
+    kc, ks = O.quantize_fp4(k)
+    vc, vs = O.quantize_fp4(v)
+    bt = rng.permutation(pages).astype(np.int32).reshape(B, npg)
+    qb = O.bf16_bits(rng.standard_normal((B, K, HQ, D)).astype(np.float32))
+    ref = O.reference(qb, kc, ks, vc, vs, bt, sl)
+    q = dev(qb.view(np.int16), torch.bfloat16)
+    args = (dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl))
+    for nsplit in (None, 2):
+        out = uq_cuda.uq_decode_cuda(q, *args, nsplit=nsplit)
+        assert uq_cuda.last_path() == 2 and uq_cuda.last_status() == (0, 0, 0, 0)
+        check_close(out.float().cpu().numpy(), ref, f"K={K} nsplit={nsplit}")
+    # the context-split form writes its partial rows through the same mapping
+    o, lse = uq_cuda.uq_decode_partial(q, *args)
+    merged = uq_cuda.uq_merge(o.unsqueeze(0), lse.unsqueeze(0))
+    check_close(merged.float().cpu().numpy(), ref, f"K={K} partial")
+
+
 def test_late_outliers_take_the_second_pass():
     """Keys whose scores (and V scales) dwarf those of a segment's first tile arrive late in every sequence: the quick path
     marks the segment and the careful pass redoes it; outputs follow the oracle on the same bytes."""
