@@ -105,11 +105,11 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
   if (!x.status) return cudaErrorInitializationError;
   // More query rows than the tensor-core kernel takes in one launch (K * group > 64, up to the 128 of uq_block_m): the
   // drafts are run as chunks of consecutive drafts, each a verify call of its own on the sequence cut after the chunk
-  // (see UQLaunch), sharing the caller's scratch one after the other.  Plain causal calls only: a tree may hide an
-  // earlier chunk's draft from a later query, which the cut does not express.
+  // (see UQLaunch), sharing the caller's scratch one after the other.  A tree-masked call is chunked without the cut: its
+  // masks decide which of the caller's drafts a query sees, whichever chunk they belong to.
   const int G = p.HQ / p.HKV;
   const int per = G <= 64 ? 64 / G : 0;   // drafts per chunk
-  if (!tree_mask && p.K * G > 64 && per >= 1 && forced_path() != 1) {
+  if (p.K * G > 64 && per >= 1 && forced_path() != 1) {
     UQParams pc = p;
     pc.K = per;
     UQLaunch xc = x;
@@ -119,7 +119,7 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
       for (int k0 = 0; k0 < p.K; k0 += per) {
         pc.K = std::min(per, p.K - k0);
         xc.k_first = k0;
-        xc.len_cut = p.K - k0 - pc.K;
+        xc.len_cut = tree_mask ? 0 : p.K - k0 - pc.K;
         cudaError_t e = run_one(pc, xc, o_part, lse_part, s);
         if (e != cudaSuccess) return e;
       }

@@ -24,6 +24,7 @@ struct UQLaunch {
   // k_first .. k_first + p.K - 1 of the caller's k_total (rows of q and out are indexed by the caller's draft number), and
   // the len_cut = k_total - k_first - p.K drafts after the chunk do not exist for it: chunk draft j then sees the keys
   // below (seq_len - len_cut) - p.K + j + 1 = seq_len - k_total + (k_first + j) + 1, the whole call's limit for that draft.
+  // (A tree-masked call is chunked with len_cut = 0: bit t of tree_mask[b, k_first + j] decides about each of the k_total drafts.)
   int k_first, k_total, len_cut;
   unsigned int* status;       // this device's status record (4 words), see uq_report
 };

@@ -368,10 +368,11 @@ UQ_DEV float warp_fold(float* v, int lane) {
 // Which of the rows r0 .. r0 + n - 1 (row = draft j * G + head of the group) see draft token td of sequence b: bit i = row
 // r0 + i.  Out of line: it runs only in the one or two tiles of an item that hold the draft positions, and inlined it costs
 // the common tile registers.
-__device__ __noinline__ uint32_t draft_rows(const int32_t* tree_mask, int K, int b, int td, int r0, int n, int rows, int G) {
+// (j_first: the caller's number of this launch's draft 0, K the caller's draft count, when a tree-masked call runs as chunks.)
+__device__ __noinline__ uint32_t draft_rows(const int32_t* tree_mask, int K, int b, int td, int r0, int n, int rows, int G, int j_first) {
   uint32_t m = 0u;
   for (int i = 0; i < n; i++) {
-    const int r = r0 + i, j = r / G;
+    const int r = r0 + i, j = r / G + j_first;
     if (r >= rows) break;
     const bool sees = tree_mask ? ((static_cast<unsigned>(__ldg(tree_mask + (size_t)b * K + j)) >> td) & 1u) != 0u : td <= j;
     if (sees) m |= 1u << i;
@@ -953,6 +954,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int n_glob = uq_seq_len(p, x, sg.b);
+      // draft positions counted back from the end: this launch's own drafts, or, for a chunk of a tree-masked call (which
+      // is not cut: any query may be given any draft by its mask), all of the caller's
+      const int Kq = x.tree_mask ? x.k_total : p.K, j_first = x.tree_mask ? x.k_first : 0;
       // ---- query tile in fp16, natural channel order, 128-byte swizzle, two 64-channel halves.  The tile is scaled by a
       // power of two so that its largest magnitude lies in [1, 2) (bf16 queries of any range fit fp16 this way; entries
       // below 2^-24 of the largest vanish); the power goes back into the softmax scale.
@@ -1072,7 +1076,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       // the common tiles
       int tmask;
       {
-        const int xq = n_glob - p.K - off - (kKeys - 1) - (x.tree_mask ? 1 : 0);
+        const int xq = n_glob - Kq - off - (kKeys - 1) - (x.tree_mask ? 1 : 0);
         tmask = min(n_loc / kKeys, xq < 0 ? 0 : xq / kKeys + 1);
       }
       for (int t = sg.t0; ok && t < sg.t1; t++, cnt++) {
@@ -1140,15 +1144,15 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const float ck = C::kBS ? csc0 : csc0 * uq_scale_f32(rf & 0xFFu);   // block-scaled scores carry the keys' scales already
         // only a tile that reaches the end of the sequence or the draft positions needs masks (same answer in every thread)
         // (chain: draft token 0 is seen by every row, so the masks start at draft 1; a tree may hide draft 0 from some rows)
-        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 + (x.tree_mask ? 1 : 0) > n_glob - p.K;
+        const bool need_mask = t * kKeys + kKeys - 1 >= n_loc || off + t * kKeys + kKeys - 1 + (x.tree_mask ? 1 : 0) > n_glob - Kq;
         bool live = true;
         uint32_t vmask = 0xFFFFFFFFu;   // bit i: row r0 + i sees this key
         if (need_mask) {
           const int key = t * kKeys + kk;
           live = key < n_loc;
-          const int td = off + key - (n_glob - p.K);   // >= 0: the key is draft token td
+          const int td = off + key - (n_glob - Kq);   // >= 0: the key is draft token td
           if (!live) vmask = 0u;
-          else if (td >= 0) vmask = draft_rows(x.tree_mask, p.K, sg.b, td, r0, HW, rows, G);
+          else if (td >= 0) vmask = draft_rows(x.tree_mask, Kq, sg.b, td, r0, HW, rows, G, j_first);
         }
         uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
         float pv[HW];
