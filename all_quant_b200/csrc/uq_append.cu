@@ -15,6 +15,8 @@
 //      reference's function applies to its result.  uq_fwht_kernel is the same transform alone, for the queries.
 //   2  the 'paper' scale rule E = round(log2(c * amax)) (half to even), values clipped at +-6
 //      (reference uqmt/quant.py:52-60, quantize_on_write's rule argument :197-206) instead of ceil(log2(amax / 6)).
+#include <cuda_fp8.h>
+
 #include "uq_common.cuh"
 
 namespace {
@@ -183,6 +185,57 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
   }
 }
 
+// NVFP4 append (reference uqmt/quant.py:125-136 quantize_nvfp4 with the tensor scale given; the byte view and the paged
+// cache of uqmt/nvfp4.py:200-254): a block is 16 channels = four lanes; its scale is e4m3fn(clamp(amax / 6 / ts, 2^-9, 448))
+// (two fp32 divisions, the hardware's round-to-nearest-even conversion), the codes are the nearest e2m1 values to
+// x / (float(scale) * ts) clipped at +-6.  Same warp layout as the UltraQuant kernel; scale bytes [.., D/16].
+template <typename T>
+__global__ void __launch_bounds__(128) uq_append_nvfp4_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
+                                                              uint8_t* __restrict__ vs, const T* __restrict__ key, const T* __restrict__ value,
+                                                              const int64_t* __restrict__ slots, int T_tok, int HKV, int D, int PAGE, float k_ts,
+                                                              float v_ts) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T_tok * HKV * 2) return;
+  const int stream = warp & 1;
+  const int h = (warp >> 1) % HKV;
+  const int t = warp / (2 * HKV);
+  const int64_t slot = slots[t];
+  if (slot < 0) return;
+  const int64_t page = slot / PAGE, off = slot % PAGE;
+  const size_t row = ((size_t)page * HKV + h) * PAGE + off;
+  const T* src = (stream == 0 ? key : value) + ((size_t)t * HKV + h) * D;
+  uint8_t* codes = (stream == 0 ? kc : vc) + row * (D / 2);
+  uint8_t* scales = (stream == 0 ? ks : vs) + row * (D / 16);
+  const float ts = stream == 0 ? k_ts : v_ts;
+  const bool vec = ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) == 0;
+  for (int base = 0; base < D; base += 128) {
+    const int ch = base + lane * 4;
+    const bool live = ch < D;   // D = 64: lanes 16..31 idle
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) load4<T>(src + ch, vec, x);
+    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float r = __fdiv_rn(__fdiv_rn(amax, 6.0f), ts);
+    r = fminf(fmaxf(r, 0.001953125f), 448.0f);   // (NaN inputs are not reproduced: here they vanish from the maximum, torch carries them into the scale)
+    const unsigned sb = (unsigned)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+    const float sf = __fmul_rn(uq_e4m3_f32(sb), ts);
+    if (live) {
+      unsigned c[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float y = __fdiv_rn(x[i], sf);
+        y = fminf(fmaxf(y, -6.0f), 6.0f);
+        const float a = fabsf(y);
+        c[i] = ((a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f)) | (y < 0.0f ? 8u : 0u);
+      }
+      *reinterpret_cast<uint16_t*>(codes + ch / 2) = (uint16_t)(c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12));
+      if ((lane & 3) == 0) scales[ch / 16] = (uint8_t)sb;
+    }
+  }
+}
+
 // The transform alone (the queries of a cache whose keys were rotated): one warp per row, out may be x.
 template <typename T>
 __global__ void __launch_bounds__(128) uq_fwht_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows, int D) {
@@ -217,6 +270,22 @@ cudaError_t uq_fwht_dispatch(const void* x, void* out, long long rows, int D, in
     case 0: uq_fwht_kernel<float><<<(int)blocks, 128, 0, s>>>((const float*)x, (float*)out, rows, D); break;
     case 1: uq_fwht_kernel<__nv_bfloat16><<<(int)blocks, 128, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, D); break;
     default: uq_fwht_kernel<__half><<<(int)blocks, 128, 0, s>>>((const __half*)x, (__half*)out, rows, D); break;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t uq_append_nvfp4_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
+                                     const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, cudaStream_t s) {
+  if (T == 0) return cudaSuccess;
+  if (!kc || !ks || !vc || !vs || !key || !value || !slots) return cudaErrorInvalidValue;
+  if (!(D == 64 || D == 128 || D == 256) || PAGE <= 0 || HKV <= 0 || T < 0 || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
+  if (!(k_ts > 0.f) || !(v_ts > 0.f)) return cudaErrorInvalidValue;
+  const long long warps = (long long)T * HKV * 2;
+  const int blocks = (int)((warps + 3) / 4);
+  switch (dtype) {
+    case 0: uq_append_nvfp4_kernel<float><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, k_ts, v_ts); break;
+    case 1: uq_append_nvfp4_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, slots, T, HKV, D, PAGE, k_ts, v_ts); break;
+    default: uq_append_nvfp4_kernel<__half><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, k_ts, v_ts); break;
   }
   return cudaGetLastError();
 }

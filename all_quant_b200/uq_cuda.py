@@ -33,7 +33,7 @@ class UQParams(ctypes.Structure):
 
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
-           "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_append_nvfp4_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes")
 
@@ -56,6 +56,7 @@ def lib():
         L.uqb_append_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
         L.uqb_append_ex_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ctypes.c_float, vp]
         L.uqb_fwht_launch.argtypes = [vp, vp, ctypes.c_longlong, i, i, vp]
+        L.uqb_append_nvfp4_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, ctypes.c_float, ctypes.c_float, vp]
         L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
         L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
         L.uqb_tree_decode_launch.argtypes = [pp, vp, vp]
@@ -339,6 +340,27 @@ def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule=
         err = lib().uqb_append_ex_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
                                          slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], flags, c, _stream(key))
     _check(err, "uq_append_launch")
+
+
+def append_kv_nvfp4(kc, ks, vc, vs, key, value, slot_mapping, k_ts, v_ts):
+    """The append for an NVFP4 cache (fmt=1): key/value [T,Hkv,D] -> e2m1 codes and one e4m3fn scale byte per 16 channels
+    (ks/vs [pages,Hkv,PAGE,D/16]) for the per-tensor scales k_ts / v_ts, which the decode call takes as well.  Bytes
+    identical to the reference's quantize_nvfp4(x, tensor_scale) (uqmt/quant.py:125-136); one kernel launch."""
+    _need_cuda(kc, ks, vc, vs, key, value, slot_mapping)
+    if key.dtype not in _DTYPE or value.dtype != key.dtype:
+        raise RuntimeError("key/value must both be fp32, bf16 or fp16")
+    T, HKV, D = key.shape
+    if ks.shape[-1] != D // 16 or vs.shape[-1] != D // 16:
+        raise RuntimeError(f"an NVFP4 cache has {D // 16} scale bytes per row")
+    key, value = key.contiguous(), value.contiguous()
+    slots = slot_mapping.to(torch.int64).contiguous()
+    for t in (kc, ks, vc, vs):
+        if not t.is_contiguous() or t.dtype != torch.uint8:
+            raise RuntimeError("cache tensors must be contiguous uint8")
+    with torch.cuda.device(key.device):
+        err = lib().uqb_append_nvfp4_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                            slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], float(k_ts), float(v_ts), _stream(key))
+    _check(err, "uq_append_nvfp4_launch")
 
 
 def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):

@@ -181,10 +181,8 @@ def build_case(cfg, plan, K, seed, device, copies=2):
         k = torch.randn(n, hkv, D, generator=g, device=device) * chan
         v = torch.randn(n, hkv, D, generator=g, device=device)
         slots = bt[b].long()[pos // PAGE] * PAGE + pos % PAGE
-        if nvfp4:   # the library's append kernel writes the UltraQuant format only: this cache is encoded here, in torch
-            pg, at = slots // PAGE, slots % PAGE
-            kc[pg, :, at], ks[pg, :, at] = nvfp4_encode(k, k_ts)
-            vc[pg, :, at], vs[pg, :, at] = nvfp4_encode(v, v_ts)
+        if nvfp4:
+            uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, k, v, slots, k_ts, v_ts)
         else:
             uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots)
         # the K newest tokens of the sequence (global positions len-K .. len-1) that fall into this shard
@@ -202,20 +200,6 @@ def build_case(cfg, plan, K, seed, device, copies=2):
     cat = lambda xs: torch.cat(xs).contiguous() if xs else None
     return dict(q=q, bt=bt.contiguous(), sl=sl, po=po, caches=caches, new_k=cat(new_k), new_v=cat(new_v), new_slots=cat(new_slots),
                 k_ts=k_ts, v_ts=v_ts)
-
-
-def nvfp4_encode(x, ts):
-    """fp32 [..., D] -> (e2m1 code bytes [..., D/2], e4m3fn scale bytes [..., D/16]) for the per-tensor scale ts: the NVFP4
-    recipe (block scale = e4m3fn(block amax / 6 / ts), codes = nearest e2m1 to x / (scale * ts)).  Data preparation of
-    the benchmark only; the answers are checked against the CPU oracle on the same bytes."""
-    import torch
-    D = x.shape[-1]
-    xg = x.float().reshape(*x.shape[:-1], D // 16, 16)
-    s8 = (xg.abs().amax(-1, keepdim=True) / 6.0 / ts).clamp(2.0 ** -9, 448.0).to(torch.float8_e4m3fn)
-    y = (xg / (s8.float() * ts)).clamp(-6.0, 6.0).reshape(*x.shape[:-1], D)
-    edges = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=x.device)
-    code = torch.bucketize(y.abs(), edges).to(torch.uint8) | ((y < 0).to(torch.uint8) << 3)
-    return code[..., 0::2] | (code[..., 1::2] << 4), s8.view(torch.uint8).squeeze(-1)
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm

@@ -55,6 +55,13 @@ int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const 
 int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                          const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, int flags, float c, void* stream);
 
+/* The append for an NVFP4 cache (UQParams.fmt = 1): codes as above, one e4m3fn scale byte per 16 channels (ks / vs
+ * [pages, HKV, PAGE, D/16]) for the per-tensor fp32 scales k_ts / v_ts (> 0), which the caller keeps and passes to the
+ * decode launch.  Bit-exact with the reference's quantiser quantize_nvfp4(x, tensor_scale) (uqmt/quant.py:125-136; paged
+ * cache uqmt/nvfp4.py:229-254); the reference has no kernel for it.  key and value both required. */
+int uqb_append_nvfp4_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
+                            const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, void* stream);
+
 /* Orthonormal Walsh-Hadamard transform along the last axis of x [rows, D] (D in {64,128,256}; dtype as above),
  * out may be x: the reference's fwht (uqmt/quant.py:84-98, rotate_kq :105-107) for the queries. */
 int uqb_fwht_launch(const void* x, void* out, long long rows, int D, int dtype, void* stream);

@@ -152,6 +152,60 @@ void uqo_append_kv(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const flo
   }
 }
 
+static float e4m3fn_to_f32(uint8_t b);
+
+/*
+ * NVFP4 quantiser (uqmt/quant.py:125-136 quantize_nvfp4, tensor_scale given): per block of 16 values
+ *   s    = e4m3fn(clamp(amax / 6 / ts, 2^-9, 448))      two fp32 divisions, round to nearest even
+ *   y    = clamp(x / (float(s) * ts), -6, 6)
+ *   code = nearest e2m1 value, ties to the smaller magnitude, sign bit from y < 0 (the same _encode as the UE8M0 format)
+ */
+static uint8_t f32_to_e4m3fn(float x) { /* 2^-9 <= x <= 448, round to nearest even */
+  if (x < 0.015625f) {                  /* below the smallest normal 2^-6: multiples of 2^-9 */
+    int q = (int)rintf(x * 512.0f);
+    return (uint8_t)q;                  /* q = 8 is 0x08 = 2^-6 itself */
+  }
+  int e;
+  float m = frexpf(x, &e);              /* x = m * 2^e, m in [0.5, 1) */
+  int q = (int)rintf(m * 16.0f);        /* 8 .. 16 */
+  e -= 1;
+  if (q == 16) { q = 8; e += 1; }
+  return (uint8_t)(((e + 7) << 3) | (q - 8));
+}
+
+void uqo_quantize_nvfp4(const float* x, size_t n_blocks, float ts, uint8_t* packed, uint8_t* scales) {
+#pragma omp parallel for schedule(static)
+  for (long long g = 0; g < (long long)n_blocks; g++) {
+    const float* xb = x + g * 16;
+    float amax = 0.0f;
+    for (int i = 0; i < 16; i++) {
+      float a = fabsf(xb[i]);
+      if (a > amax) amax = a;
+    }
+    float r = amax / 6.0f / ts;
+    if (!(r >= 0.001953125f)) r = 0.001953125f;
+    if (r > 448.0f) r = 448.0f;
+    const uint8_t sb = f32_to_e4m3fn(r);
+    const float sf = e4m3fn_to_f32(sb) * ts;
+    uint8_t codes[16];
+    for (int i = 0; i < 16; i++) {
+      float y = xb[i] / sf;
+      if (y < -6.0f) y = -6.0f;
+      if (y > 6.0f) y = 6.0f;
+      float a = fabsf(y);
+      int best = 0;
+      float bd = fabsf(a - kGrid[0]);
+      for (int c = 1; c < 8; c++) {
+        float d = fabsf(a - kGrid[c]);
+        if (d < bd) { bd = d; best = c; }
+      }
+      codes[i] = (uint8_t)(best | ((y < 0.0f) ? 8 : 0));
+    }
+    for (int i = 0; i < 8; i++) packed[g * 8 + i] = (uint8_t)(codes[2 * i] | (codes[2 * i + 1] << 4));
+    scales[g] = sb;
+  }
+}
+
 static inline float bf16_to_f32(uint16_t h) {
   uint32_t u = (uint32_t)h << 16;
   float f;

@@ -43,6 +43,7 @@ def lib():
         L.uqo_tree_reference.argtypes = [vp] * 8 + [i32] * 7 + [f32, vp]
         L.uqo_quantize_rule.argtypes = [vp, ctypes.c_size_t, i32, f32, vp, vp]
         L.uqo_fwht.argtypes = [vp, ctypes.c_size_t, i32, vp]
+        L.uqo_quantize_nvfp4.argtypes = [vp, ctypes.c_size_t, f32, vp, vp]
         L.uqo_e4m3fn_table.argtypes = [vp]
         L.uqo_reference_nvfp4.argtypes = [vp] * 7 + [i32] * 7 + [f32, f32, f32, vp]
         _LIB = L
@@ -179,6 +180,18 @@ def tree_reference(q_bits, kc, ks, vc, vs, block_table, seq_lens, tree_mask=None
     lib().uqo_tree_reference(_p(q_bits), _p(kc), _p(ks), _p(vc), _p(vs), _p(bt), _p(sl), _p(tm), B, K, HQ, HKV, D, PAGE,
                              bt.shape[1], sm, _p(out))
     return out
+
+
+def quantize_nvfp4(x, ts):
+    """x [..., D] -> (codes uint8 [..., D/2], e4m3fn scale bytes uint8 [..., D/16]) for the per-tensor scale ts
+    (uqmt/quant.py:125-136 with tensor_scale given; uqmt/nvfp4.py:200-203 for the byte view)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    D = x.shape[-1]
+    assert D % 16 == 0
+    packed = np.empty(x.shape[:-1] + (D // 2,), np.uint8)
+    scales = np.empty(x.shape[:-1] + (D // 16,), np.uint8)
+    lib().uqo_quantize_nvfp4(_p(x), x.size // 16, float(ts), _p(packed), _p(scales))
+    return packed, scales
 
 
 def e4m3fn_table():

@@ -11,7 +11,7 @@ Two kinds of fixture:
   nvfp4_cuda_<set>.npz   the reference's frozen NVFP4 vectors (cuda/vectors_nvfp4), repacked the same way; the scale
       arrays are e4m3fn bytes [pages,Hkv,PAGE,D/16] and `ts` holds the per-tensor scales (k_ts, v_ts).
 `--tree-only` regenerates tree_cases.npz alone, `--nvfp4-only` the nvfp4_cuda_* files alone, `--rotate-only` gen_rotate.npz
-(uqmt.quant.fwht and the 'paper' scale rule of uqmt.quant.quantize) alone.
+(uqmt.quant.fwht and the 'paper' scale rule of uqmt.quant.quantize) and gen_nvfp4_quant.npz (uqmt.quant.quantize_nvfp4) alone.
 """
 import os
 import sys
@@ -210,6 +210,24 @@ def gen_rotate():
     save("gen_rotate.npz", **arrs)
 
 
+def gen_nvfp4_quant():
+    """uqmt.quant.quantize_nvfp4 with a given tensor scale (the NVFP4 append's encoder) on seeded rows: wide magnitudes, zero
+    rows, rows far below and far above the range the tensor scale covers (scale bytes at both clamps)."""
+    from uqmt.quant import quantize_nvfp4
+    g = torch.Generator().manual_seed(99)
+    arrs = {}
+    for D in (64, 128, 256):
+        x = torch.randn(32, 2, D, generator=g) * torch.exp(2.0 * torch.randn(32, 2, 1, generator=g))
+        x[3] = 0.0
+        x[5] *= 1e-7
+        x[7] *= 1e4
+        ts = 32.0 / (6 * 448)
+        p, s, _ = quantize_nvfp4(x, ts)
+        arrs[f"d{D}_x"], arrs[f"d{D}_codes"], arrs[f"d{D}_scales"] = x.numpy(), p.numpy(), s.view(torch.uint8).numpy()
+        arrs[f"d{D}_ts"] = np.float64(ts)
+    save("gen_nvfp4_quant.npz", **arrs)
+
+
 def gen_tree():
     """Tree-masked verify: answers of the reference's own oracle (uqmt/tree.py tree_reference) for chain, star and seeded
     random parent trees, one case with a different tree per sequence.  One file, cases t0..tN."""
@@ -251,6 +269,7 @@ if __name__ == "__main__":
         sys.exit(0)
     if "--rotate-only" in sys.argv:
         gen_rotate()
+        gen_nvfp4_quant()
         sys.exit(0)
     if "--tree-only" in sys.argv:
         gen_tree()
@@ -263,3 +282,4 @@ if __name__ == "__main__":
     gen_append()
     gen_tree()
     gen_rotate()
+    gen_nvfp4_quant()

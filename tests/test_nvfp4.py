@@ -128,3 +128,80 @@ def test_unknown_format_is_refused():
     q, kc, ks, vc, vs, bt, sl = _dev(c)
     with pytest.raises(RuntimeError):
         uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fmt=2)
+
+
+# ---------------------------------------------------------------------------------------------------- the NVFP4 append
+QZ = None
+
+
+def _qz():
+    global QZ
+    if QZ is None:
+        from tests.cases import load
+        QZ = load("gen_nvfp4_quant")
+    return QZ
+
+
+@pytest.mark.parametrize("D", (64, 128, 256))
+def test_oracle_nvfp4_quantiser_matches_the_reference_bytes(D):
+    z = _qz()
+    codes, scales = O.quantize_nvfp4(z[f"d{D}_x"], float(z[f"d{D}_ts"]))
+    assert np.array_equal(codes, z[f"d{D}_codes"])
+    assert np.array_equal(scales, z[f"d{D}_scales"])
+    assert scales.min() == 0x01 and scales.max() == 0x7e      # both clamps of the scale are in the fixture
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", (64, 128, 256))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_nvfp4_append_kernel_bit_exact(D, dtype):
+    from all_quant_b200 import uq_cuda
+    z = _qz()
+    x = torch.from_numpy(z[f"d{D}_x"]).to(dtype)
+    ts = float(z[f"d{D}_ts"])
+    if dtype == torch.float32:
+        want_c, want_s = z[f"d{D}_codes"], z[f"d{D}_scales"]
+    else:   # 16-bit input: the oracle (pinned above) on the rounded values
+        want_c, want_s = O.quantize_nvfp4(x.float().numpy(), ts)
+    T, HKV, _ = x.shape
+    PAGE, pages = 16, 3
+    kc = torch.zeros(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device="cuda")
+    ks = torch.zeros(pages, HKV, PAGE, D // 16, dtype=torch.uint8, device="cuda")
+    vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
+    slots = torch.from_numpy(np.random.default_rng(4).permutation(pages * PAGE)[:T].astype(np.int64)).cuda()
+    uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, x.cuda(), x.cuda(), slots, ts, ts)
+    pg, at = (slots // PAGE).cpu(), (slots % PAGE).cpu()
+    for codes, scales in ((kc, ks), (vc, vs)):
+        assert np.array_equal(codes.cpu()[pg, :, at].numpy(), want_c)
+        assert np.array_equal(scales.cpu()[pg, :, at].numpy(), want_s)
+
+
+@pytest.mark.gpu
+def test_nvfp4_append_then_decode_follows_the_oracle():
+    """A cache written by the NVFP4 append and read by the verify call, against the oracle on the same float data."""
+    from all_quant_b200 import uq_cuda
+    rng = np.random.default_rng(17)
+    B, K, HQ, HKV, D, PAGE, ctx = 2, 4, 8, 2, 128, 64, 600
+    npg = -(-ctx // PAGE)
+    k = rng.standard_normal((B * ctx, HKV, D)).astype(np.float32) * 2.0
+    v = rng.standard_normal((B * ctx, HKV, D)).astype(np.float32)
+    k_ts, v_ts = 16.0 / (6 * 448), 8.0 / (6 * 448)
+    bt = rng.permutation(B * npg).astype(np.int32).reshape(B, npg)
+    pos = np.tile(np.arange(ctx), B)
+    slots = bt[np.repeat(np.arange(B), ctx), pos // PAGE].astype(np.int64) * PAGE + pos % PAGE
+    kc = torch.zeros(B * npg, HKV, PAGE, D // 2, dtype=torch.uint8, device="cuda")
+    ks = torch.zeros(B * npg, HKV, PAGE, D // 16, dtype=torch.uint8, device="cuda")
+    vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
+    uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), torch.from_numpy(slots).cuda(), k_ts, v_ts)
+    # the same bytes from the oracle's quantiser, scattered on the host
+    kcw, ksw = O.quantize_nvfp4(k, k_ts)
+    vcw, vsw = O.quantize_nvfp4(v, v_ts)
+    pg, at = slots // PAGE, slots % PAGE
+    assert np.array_equal(kc.cpu().numpy()[pg, :, at], kcw) and np.array_equal(ks.cpu().numpy()[pg, :, at], ksw)
+    assert np.array_equal(vc.cpu().numpy()[pg, :, at], vcw) and np.array_equal(vs.cpu().numpy()[pg, :, at], vsw)
+    qb = O.bf16_bits(rng.standard_normal((B, K, HQ, D)).astype(np.float32))
+    sl = np.full(B, ctx, np.int32)
+    want = O.reference_nvfp4(qb, kc.cpu().numpy(), ks.cpu().numpy(), vc.cpu().numpy(), vs.cpu().numpy(), bt, sl, k_ts, v_ts)
+    q = torch.from_numpy(qb.view(np.int16)).cuda().view(torch.bfloat16)
+    out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, torch.from_numpy(bt).cuda(), torch.from_numpy(sl).cuda(), fmt=1, k_ts=k_ts, v_ts=v_ts)
+    check_close(out.float().cpu().numpy(), want, "append + decode")
