@@ -1,5 +1,5 @@
-"""Generates the fixtures in this directory.  Needs the reference checkout (default /root/reference,
-or argv[1]); the tests themselves never read the reference, only the .npz files written here.
+"""Generates the fixtures in this directory.  Needs the reference checkout: its path is argv[1] or the environment
+variable UQ_REFERENCE; the tests themselves never read the reference, only the .npz files written here.
 
 Two kinds of fixture:
   ref_cuda_<set>.npz / ref_sycl_<case>.npz   the reference's own frozen known-answer vectors
@@ -20,7 +20,9 @@ import numpy as np
 import torch
 
 _args = [a for a in sys.argv[1:] if not a.startswith("--")]
-REF = _args[0] if _args else "/root/reference"
+REF = _args[0] if _args else os.environ.get("UQ_REFERENCE")
+if not REF:
+    raise SystemExit("usage: make_golden.py <path of the reference checkout> [--tree-only | --nvfp4-only | --rotate-only]")
 OUT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REF)
 from uqmt.attn import build_paged_cache, dequantize_fp4, quantize_fp4, reference  # noqa: E402

@@ -82,7 +82,7 @@ def test_unfused_mode_and_tensor_scales():
     q, kc, ks, vc, vs, bt, sl = _dev(c)
     out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fused=False, fmt=1, k_ts=c.k_ts, v_ts=c.v_ts)
     check_close(out.float().cpu().numpy(), c.ref, "unfused")
-    # other tensor scales: the oracle is the judge
+    # other tensor scales: the oracle gives the answer
     for k_ts, v_ts in ((2.0 * c.k_ts, 0.5 * c.v_ts), (0.25 * c.k_ts, 1.5 * c.v_ts)):   # outputs stay of order one: the rule's mean bound is absolute
         want = O.reference_nvfp4(c.q, c.kc, c.ks, c.vc, c.vs, c.bt, c.sl, k_ts, v_ts)
         out = uq_cuda.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fmt=1, k_ts=k_ts, v_ts=v_ts)
