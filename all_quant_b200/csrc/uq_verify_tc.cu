@@ -651,20 +651,21 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 
   if (warp == kWarpProd) {
     // ================================================================= producer
-    const int ppt = kKeys / p.PAGE;   // pages per tile
+    // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
+    const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
     UQ_PROF_DECL
-    const uint32_t page_bytes_codes = (uint32_t)p.PAGE * C::kCodeRow, page_bytes_scales = (uint32_t)p.PAGE * C::kScaleB;
+    const uint32_t page_bytes_codes = (uint32_t)unit * C::kCodeRow, page_bytes_scales = (uint32_t)unit * C::kScaleB;
     while (ok && wk.next(sg)) {
       if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
-      const int pages_valid = (n_loc + p.PAGE - 1) / p.PAGE;
+      const int pages_valid = (n_loc + unit - 1) / unit;   // (units)
       const int32_t* bt = p.block_table + (size_t)sg.b * p.max_pages;
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
         const int stage = cnt % kRawStages;
         const int vp = min(ppt, pages_valid - t * ppt);
         int pid = 0;
-        if (lane < vp) pid = __ldg(bt + t * ppt + lane);
+        if (lane < vp) pid = __ldg(bt + (t * ppt + lane) / spp);
         ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -673,7 +674,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * 2u * (page_bytes_codes + page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
-          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE;   // first cache row of this (page, head)
+          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) % spp) * unit;   // first cache row of this unit of (page, head)
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
           tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
@@ -1389,7 +1390,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// The code arrays as a 2-D byte tensor [cache rows][D/2]; a box is one page of one head (PAGE rows).  The number
+// The code arrays as a 2-D byte tensor [cache rows][D/2]; a box is one page of one head (`page` rows: PAGE, or 128 for larger pages).  The number
 // of physical pages is not part of the launch arguments, so the row extent is the largest the map can hold:
 // only rows named by the page table are ever touched.
 bool make_code_map(CUtensorMap* map, const uint8_t* base, int code_row_bytes, int page) {
@@ -1438,7 +1439,8 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   const long long max_tiles = ((long long)p.max_pages * p.PAGE + kKeys - 1) / kKeys;
   prm.chunk_min = x.ns_eff >= 2 ? (int)((max_tiles + x.ns_eff - 2) / (x.ns_eff - 1)) : 1;
   CUtensorMap mk, mv;
-  if (!(C::kBS ? make_unpack_map(&mk, p.kc, D, p.PAGE) : make_code_map(&mk, p.kc, C::kCodeRow, p.PAGE)) || !make_code_map(&mv, p.vc, C::kCodeRow, p.PAGE))
+  const int box_rows = std::min(p.PAGE, kKeys);   // a copy moves a page of up to 128 tokens, or a 128-token part of a larger one
+  if (!(C::kBS ? make_unpack_map(&mk, p.kc, D, box_rows) : make_code_map(&mk, p.kc, C::kCodeRow, box_rows)) || !make_code_map(&mv, p.vc, C::kCodeRow, box_rows))
     return cudaErrorInvalidValue;
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1474,7 +1476,7 @@ extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
   if (p.fmt != 0 && p.fmt != 1) return false;
   if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
-  if (!(p.PAGE == 16 || p.PAGE == 32 || p.PAGE == 64 || p.PAGE == 128)) return false;
+  if (p.PAGE < 16 || p.PAGE > 1024 || (p.PAGE & (p.PAGE - 1))) return false;   // powers of two: pages that tile, or are tiled by, the 128-key tile
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
   if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
   if (p.fmt == 0 && tc::block_scaled(p.D) && (reinterpret_cast<uintptr_t>(p.kc) & 31)) return false;   // the unpacking tensor map wants 32-byte alignment

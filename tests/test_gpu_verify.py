@@ -132,6 +132,36 @@ def test_more_than_64_query_rows_run_as_draft_chunks_on_the_tensor_core_kernel(K
     check_close(merged.float().cpu().numpy(), ref, f"K={K} partial")
 
 
+@pytest.mark.parametrize("PAGE,D,fmt", [(16, 128, 0), (256, 128, 0), (512, 128, 0), (256, 64, 0), (1024, 256, 0), (256, 128, 1), (48, 128, 0)])
+def test_page_sizes_from_16_to_1024_tokens(PAGE, D, fmt):
+    """Pages smaller than the 128-key tile are copied whole, larger ones in 128-token parts; a page size that is not a power
+    of two runs on the CUDA-core kernel.  Ragged lengths that end inside a page and inside a part of a page."""
+    rng = np.random.default_rng(PAGE + D)
+    B, K, HQ, HKV = 3, 4, 8, 2
+    sl = np.array([2 * PAGE + 77, 130, 3 * PAGE], np.int32)
+    npg = -(-int(sl.max()) // PAGE)
+    pages = B * npg
+    kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    if fmt == 0:
+        ks = rng.integers(125, 130, (pages, HKV, PAGE, D // 32)).astype(np.uint8)
+        vs = rng.integers(125, 130, (pages, HKV, PAGE, D // 32)).astype(np.uint8)
+    else:
+        ks = rng.integers(0x30, 0x40, (pages, HKV, PAGE, D // 16)).astype(np.uint8)
+        vs = rng.integers(0x30, 0x40, (pages, HKV, PAGE, D // 16)).astype(np.uint8)
+    bt = rng.permutation(pages).astype(np.int32).reshape(B, npg)
+    qb = O.bf16_bits(0.3 * rng.standard_normal((B, K, HQ, D)).astype(np.float32))
+    ref = O.reference(qb, kc, ks, vc, vs, bt, sl) if fmt == 0 else O.reference_nvfp4(qb, kc, ks, vc, vs, bt, sl, 0.5, 0.5)
+    q = dev(qb.view(np.int16), torch.bfloat16)
+    kw = dict(fmt=1, k_ts=0.5, v_ts=0.5) if fmt else {}
+    for nsplit in (None, 3):
+        out = uq_cuda.uq_decode_cuda(q, dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl), nsplit=nsplit, **kw)
+        assert uq_cuda.last_status() == (0, 0, 0, 0)
+        assert uq_cuda.last_path() == (2 if PAGE & (PAGE - 1) == 0 else 1)
+        mx = np.abs(ref).max()      # random codes and scales give outputs of order ten: the rule is applied to outputs normalised to O(1)
+        check_close(out.float().cpu().numpy() / mx, ref / mx, f"PAGE={PAGE} D={D} fmt={fmt} nsplit={nsplit}")
+
+
 def test_late_outliers_take_the_second_pass():
     """Keys whose scores (and V scales) dwarf those of a segment's first tile arrive late in every sequence: the quick path
     marks the segment and the careful pass redoes it; outputs follow the oracle on the same bytes."""
