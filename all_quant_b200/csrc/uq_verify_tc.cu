@@ -653,6 +653,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // ================================================================= producer
     // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
     const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
+    const int spp_sh = __ffs(spp) - 1;   // (a power of two: the per-tile arithmetic below is shifts and masks, no division)
     UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)unit * C::kCodeRow, page_bytes_scales = (uint32_t)unit * C::kScaleB;
     while (ok && wk.next(sg)) {
@@ -665,7 +666,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const int stage = cnt % kRawStages;
         const int vp = min(ppt, pages_valid - t * ppt);
         int pid = 0;
-        if (lane < vp) pid = __ldg(bt + (t * ppt + lane) / spp);
+        if (lane < vp) pid = __ldg(bt + ((t * ppt + lane) >> spp_sh));
         ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -674,7 +675,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * 2u * (page_bytes_codes + page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
-          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) % spp) * unit;   // first cache row of this unit of (page, head)
+          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;   // first cache row of this unit of (page, head)
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
           tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
