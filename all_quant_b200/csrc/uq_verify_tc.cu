@@ -95,6 +95,12 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PROF_TB(n)
 #endif
 
+#ifndef UQ_RS128
+#define UQ_RS128 3   // raw tiles in flight at head_dim 128
+#endif
+#ifndef UQ_SB128
+#define UQ_SB128 3   // K / S^T / P^T ring depth at head_dim 128
+#endif
 #ifndef UQ_V64
 #define UQ_V64 4   // V-decode warps at 64 rows
 #endif
@@ -115,8 +121,8 @@ __host__ __device__ constexpr int v_warps(int NT) { return NT < 64 ? 8 : UQ_V64;
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 8 + v_warps(NT)) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
 __host__ __device__ constexpr bool block_scaled(int D) { return D == 128; }          // Q.K straight from the e2m1 codes and scale bytes (see Cfg::kBS)
-__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : (D == 128 ? 3 : 4); }   // raw code/scale tiles in flight (TMA)
-__host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : 3; }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
+__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : (D == 128 ? UQ_RS128 : 4); }   // raw code/scale tiles in flight (TMA)
+__host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : (D == 128 ? UQ_SB128 : 3); }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
 __host__ __device__ constexpr int ring_vb(int D) { return D == 256 ? 1 : 2; }      // decoded V tiles (shared memory)
 constexpr float kRescaleAt = 12.0f;  // a score this far (log2) above the row's reference maximum does not fit the fp16 probability tile
 constexpr int kRedoWords = 32;       // a CTA's first 32 * kRedoWords segments can be marked for the second pass; later ones take the careful path at once
