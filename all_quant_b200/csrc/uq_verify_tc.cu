@@ -16,7 +16,7 @@
 //   K decode  4 warps      thread = key: e2m1 -> fp16 by the hardware conversion, one fp16 multiply by the group scale
 //                          relative to the key's largest, tcgen05.st into the TMEM A operand (ring of 3)
 //   V decode  4 warps      thread = key: the same decode -> 128-byte-swizzled fp16 tile in shared memory (ring of 2)
-//   producer  1 warp       TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code row without
+//   producer  2 warps      (one for the K side, one for the V side of every tile) TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code row without
 //                          bank conflicts) of the K/V code pages + bulk copies of the scale pages, ring of 4 tiles
 //   Q.K issue 1 warp       8 tcgen05.mma per tile (one thread), owns the TMEM allocation
 //   P.V issue 1 warp       8 tcgen05.mma per tile (one thread)
@@ -101,6 +101,12 @@ __device__ unsigned long long g_tc_prof[5][8];
 #ifndef UQ_SB128
 #define UQ_SB128 3   // K / S^T / P^T ring depth at head_dim 128
 #endif
+#ifndef UQ_PF
+#define UQ_PF 0   // tiles ahead of the copies that the producer prefetches into L2 (0 = none)
+#endif
+#ifndef UQ_PROD2
+#define UQ_PROD2 1   // 1: a second copy warp issues the V side of every tile (the first keeps the K side); 0: one warp issues both
+#endif
 #ifndef UQ_V64
 #define UQ_V64 4   // V-decode warps at 64 rows
 #endif
@@ -174,6 +180,14 @@ UQ_DEV void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.
 UQ_DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// the same boxes and ranges fetched into L2 only (no shared memory, no barrier): issued a few tiles ahead of the copies, so
+// that a copy, which can start only when its shared-memory stage is free, finds its bytes in L2 instead of waiting for HBM
+UQ_DEV void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+UQ_DEV void bulk_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // contiguous bulk copy (scale pages)
 UQ_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -592,7 +606,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
     // a raw stage is free again after the four K (or relay) warps and the V warps have read it (block-scaled: and after the Q.K instructions have)
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 4 + (kNV == 8 && kVB == 2 ? 4 : kNV) + (C::kBS ? 1 : 0)); }
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), UQ_PROD2 ? 2 : 1); mbar_init(bar_raw_empty(s), 4 + (kNV == 8 && kVB == 2 ? 4 : kNV) + (C::kBS ? 1 : 0)); }
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
@@ -655,8 +669,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // does this pass run segment `ord`?  (pass 1: the marked ones)
   auto take = [&]() -> bool { ord++; return pass == 0 || (ord < 32 * kRedoWords && ((redo[ord >> 5] >> (ord & 31)) & 1u)); };
 
-  if (warp == kWarpProd) {
+  if (warp == kWarpProd || (UQ_PROD2 && warp == kWarpProd + 2)) {
     // ================================================================= producer
+    const int side = !UQ_PROD2 ? 2 : (warp == kWarpProd ? 0 : 1);   // 0 K codes and scales, 1 V codes and scales, 2 both
     // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
     const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
     const int spp_sh = __ffs(spp) - 1;   // (a power of two: the per-tile arithmetic below is shifts and masks, no division)
@@ -673,21 +688,33 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const int vp = min(ppt, pages_valid - t * ppt);
         int pid = 0;
         if (lane < vp) pid = __ldg(bt + ((t * ppt + lane) >> spp_sh));
+        // the tile UQ_PF ahead (same segment): its page ids are read now, beside the wait below
+        const int tp = t + UQ_PF;
+        const int vpp = (UQ_PF > 0 && tp < sg.t1) ? min(ppt, pages_valid - tp * ppt) : 0;
+        int pidp = 0;
+        if (lane < vpp) pidp = __ldg(bt + ((tp * ppt + lane) >> spp_sh));
         ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t dst = sm_a + C::oRaw + stage * C::kRawStage;
         if (lane == 0) { UQ_TRACE(0, cnt) }
-        if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * 2u * (page_bytes_codes + page_bytes_scales));
+        if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * (side == 2 ? 2u : 1u) * (page_bytes_codes + page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
           const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;   // first cache row of this unit of (page, head)
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
-          tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
-          tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
-          bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
-          bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          if (side != 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
+          if (side != 0) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
+          if (side != 1) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          if (side != 0) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+        }
+        if (lane < vpp) {
+          const int rowp = (pidp * p.HKV + sg.hk) * p.PAGE + ((tp * ppt + lane) & (spp - 1)) * unit;
+          tma_prefetch_2d(&map_kc, 0, rowp);
+          tma_prefetch_2d(&map_vc, 0, rowp);
+          bulk_prefetch(p.ks + (size_t)rowp * C::kScaleB, page_bytes_scales);
+          bulk_prefetch(p.vs + (size_t)rowp * C::kScaleB, page_bytes_scales);
         }
       }
     }
