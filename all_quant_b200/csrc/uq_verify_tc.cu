@@ -105,7 +105,7 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_PF 0   // tiles ahead of the copies that the producer prefetches into L2 (0 = none)
 #endif
 #ifndef UQ_PROD2
-#define UQ_PROD2 1   // 1: a second copy warp issues the V side of every tile (the first keeps the K side); 0: one warp issues both
+#define UQ_PROD2 1   // copy warps beside the first: 0 one warp issues everything; 1 K side / V side; 2 K codes / V codes / both scale slices
 #endif
 #ifndef UQ_V64
 #define UQ_V64 4   // V-decode warps at 64 rows
@@ -606,7 +606,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // ---- set-up: barriers, tile prefix, TMEM
   if (tid == 0) {
     // a raw stage is free again after the four K (or relay) warps and the V warps have read it (block-scaled: and after the Q.K instructions have)
-    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), UQ_PROD2 ? 2 : 1); mbar_init(bar_raw_empty(s), 4 + (kNV == 8 && kVB == 2 ? 4 : kNV) + (C::kBS ? 1 : 0)); }
+    for (int s = 0; s < kRawStages; s++) { mbar_init(bar_raw_full(s), UQ_PROD2 + 1); mbar_init(bar_raw_empty(s), 4 + (kNV == 8 && kVB == 2 ? 4 : kNV) + (C::kBS ? 1 : 0)); }
     // role barriers count one arrival per warp (lane 0, after __syncwarp): 128 separate arrivals per tile and
     // barrier serialise in the shared-memory unit and cost more than the work they order
     for (int i = 0; i < kSB; i++) {
@@ -669,9 +669,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // does this pass run segment `ord`?  (pass 1: the marked ones)
   auto take = [&]() -> bool { ord++; return pass == 0 || (ord < 32 * kRedoWords && ((redo[ord >> 5] >> (ord & 31)) & 1u)); };
 
-  if (warp == kWarpProd || (UQ_PROD2 && warp == kWarpProd + 2)) {
+  if (warp == kWarpProd || (UQ_PROD2 >= 1 && warp == kWarpProd + 2) || (UQ_PROD2 == 2 && warp == kWarpProd + 3)) {
     // ================================================================= producer
-    const int side = !UQ_PROD2 ? 2 : (warp == kWarpProd ? 0 : 1);   // 0 K codes and scales, 1 V codes and scales, 2 both
+    // what this warp copies of every tile: bit 0 K codes, bit 1 V codes, bit 2 K scales, bit 3 V scales
+    const int side = UQ_PROD2 == 0 ? 15 : (UQ_PROD2 == 1 ? (warp == kWarpProd ? 5 : 10) : (warp == kWarpProd ? 1 : (warp == kWarpProd + 2 ? 2 : 12)));
     // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
     const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
     const int spp_sh = __ffs(spp) - 1;   // (a power of two: the per-tile arithmetic below is shifts and masks, no division)
@@ -698,16 +699,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (!ok) break;
         const uint32_t dst = sm_a + C::oRaw + stage * C::kRawStage;
         if (lane == 0) { UQ_TRACE(0, cnt) }
-        if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * (side == 2 ? 2u : 1u) * (page_bytes_codes + page_bytes_scales));
+        if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * ((uint32_t)__popc(side & 3) * page_bytes_codes + (uint32_t)__popc(side & 12) * page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
           const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;   // first cache row of this unit of (page, head)
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
-          if (side != 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
-          if (side != 0) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
-          if (side != 1) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
-          if (side != 0) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
+          if (side & 2) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
+          if (side & 4) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          if (side & 8) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
         }
         if (lane < vpp) {
           const int rowp = (pidp * p.HKV + sg.hk) * p.PAGE + ((tp * ppt + lane) & (spp - 1)) * unit;
