@@ -107,6 +107,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #ifndef UQ_PROD2
 #define UQ_PROD2 1   // copy warps beside the first: 0 one warp issues everything; 1 K side / V side; 2 K codes / V codes / both scale slices
 #endif
+#ifndef UQ_EARLY
+#define UQ_EARLY 1   // 1: the V decode gives its raw stage back once the tile's codes are in registers, not after the decode
+#endif
 #ifndef UQ_V64
 #define UQ_V64 4   // V-decode warps at 64 rows
 #endif
@@ -912,6 +915,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           uint4 c4[GN];
 #pragma unroll
           for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(vcode + (((g0 + g) ^ swz) << 4));
+          // UltraQuant: codes and scale bytes of the tile are in registers after the last group's loads, so the raw stage can
+          // go back to the copy warps now (the arrival orders the loads before it), a decode earlier than at the end
+          if (UQ_EARLY && FMT == 0 && gb + 4 >= kGPT) warp_arrive(bar_raw_empty(stage));
 #pragma unroll
           for (int g = 0; g < GN; g++) {
             const int gg = g0 + g;
@@ -933,7 +939,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         UQ_PROF_T1(2)
         fence_async_smem();
         warp_arrive(bar(bVfull + buf));
-        warp_arrive(bar_raw_empty(stage));
+        if (!(UQ_EARLY && FMT == 0) || ((UQ_ABL & 32) && cnt)) warp_arrive(bar_raw_empty(stage));
         if (vw == 0 && lane == 0) { UQ_TRACE(4, cnt) }
         UQ_PROF_T1(3)
       }
