@@ -908,6 +908,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const uint8_t* vsc = sm + C::oRaw + stage * C::kRawStage + C::kOffVS + kk * C::kScaleB;   // (NVFP4: read per group below)
         const uint8_t* vcode = raw + kk * C::kCodeRow;
         const int swz = (kk / C::kRowsPer128) & (C::kChunks - 1);
+        uint32_t vs2[kGPT];   // NVFP4: the two scale bytes of each of this thread's groups, read before the stage is given back
+        if constexpr (FMT == 1) {
+#pragma unroll
+          for (int g = 0; g < kGPT; g++) vs2[g] = *reinterpret_cast<const uint16_t*>(vsc + 2 * (gfirst + g));
+        }
 #pragma unroll
         for (int gb = 0; gb < ((UQ_ABL & 32) && cnt ? 0 : kGPT); gb += 4) {
           constexpr int GN = kGPT < 4 ? kGPT : 4;
@@ -915,16 +920,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           uint4 c4[GN];
 #pragma unroll
           for (int g = 0; g < GN; g++) c4[g] = *reinterpret_cast<const uint4*>(vcode + (((g0 + g) ^ swz) << 4));
-          // UltraQuant: codes and scale bytes of the tile are in registers after the last group's loads, so the raw stage can
-          // go back to the copy warps now (the arrival orders the loads before it), a decode earlier than at the end
-          if (UQ_EARLY && FMT == 0 && gb + 4 >= kGPT) warp_arrive(bar_raw_empty(stage));
+          // codes and scale bytes of the tile are in registers after the last group's loads, so the raw stage can go back to
+          // the copy warps now (the arrival orders the loads before it), a decode earlier than at the end
+          if (UQ_EARLY && gb + 4 >= kGPT) warp_arrive(bar_raw_empty(stage));
 #pragma unroll
           for (int g = 0; g < GN; g++) {
             const int gg = g0 + g;
             uint32_t m, m2;   // multiplier 0: keys past the end decode to zeros
             if constexpr (FMT == 0) m = m2 = live ? pow2_f16x2((int)((uint32_t)(sc >> (8 * gg)) & 0xFFu) - vref) : 0u;
             else {
-              e4m3_pair_f16x2(*reinterpret_cast<const uint16_t*>(vsc + 2 * gg), m, m2);
+              e4m3_pair_f16x2(vs2[gb + g], m, m2);
               if (!live) m = m2 = 0u;
             }
             uint32_t o[16];
@@ -939,7 +944,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         UQ_PROF_T1(2)
         fence_async_smem();
         warp_arrive(bar(bVfull + buf));
-        if (!(UQ_EARLY && FMT == 0) || ((UQ_ABL & 32) && cnt)) warp_arrive(bar_raw_empty(stage));
+        if (!UQ_EARLY || ((UQ_ABL & 32) && cnt)) warp_arrive(bar_raw_empty(stage));
         if (vw == 0 && lane == 0) { UQ_TRACE(4, cnt) }
         UQ_PROF_T1(3)
       }
