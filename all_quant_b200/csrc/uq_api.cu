@@ -3,10 +3,16 @@
 //
 // Dispatch (the reference's is a template tree over variant / BLOCK_M / warps / stages, reference
 // cuda/uq_decode.cu:402-626; this library has two kernels and ignores those hints):
-//   tcgen05 kernel  when head_dim, page size and row count are ones it serves (uq_verify_tc.cu)
-//   CUDA-core kernel otherwise, and always for few query rows (uq_verify_fma.cu)
+//   tcgen05 kernel  when head_dim, page size, alignment and row count are ones it serves (uq_verify_tc.cu): every
+//                   power-of-two page from 16 to 1024 tokens, up to 64 rows per launch, 65-128 rows as draft chunks
+//   CUDA-core kernel for everything else (uq_verify_fma.cu)
 // followed by the combine kernel.  Every check happens before the first launch, so
 // cudaErrorInvalidValue means nothing was enqueued (callers of the reference skip on it).
+//
+// Alignment contract (checked here; a pointer that breaks it is refused, never dereferenced): q and kc 16 bytes (both
+// kernels read them as 16-byte vectors), mo 8 bytes, ml and out 4 bytes, the page table and seq_lens 4 bytes.  vc, ks and
+// vs may have any alignment on the CUDA-core kernel; the tcgen05 kernel wants kc / vc / ks / vs 16-byte aligned (kc 32
+// for the block-scaled head_dim 128) and a call that is not falls to the CUDA-core kernel.
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
@@ -37,15 +43,26 @@ cudaError_t uq_merge_packed_dispatch(const float*, int, size_t, int, void*, cuda
 
 namespace {
 
+constexpr int kMaxDevices = 64;   // per-device tables (status record, attributes, scratch address); a device index beyond is refused
 std::atomic<unsigned long long> g_launches{0};
 thread_local int t_last_path = 0;
 thread_local cudaEvent_t t_ev_before = nullptr, t_ev_after = nullptr;
 
-int pow2ceil(int v) {
+int pow2ceil(int v) {   // saturates at 2^30 (an int cannot hold the next power)
   int p = 1;
-  while (p < v) p <<= 1;
+  while (p < v && p < (1 << 30)) p <<= 1;
   return p;
 }
+
+// Argument ranges within which the size arithmetic below cannot overflow and the kernels' 32-bit indices hold.
+bool sizes_ok(const UQParams& p) {
+  if (p.B < 0 || p.B > (1 << 20) || p.K < 1 || p.K > 128 || p.HQ < 1 || p.HQ > (1 << 16) || p.HKV < 1 || p.HKV > p.HQ || p.HQ % p.HKV) return false;
+  if (p.HQ / p.HKV > 128) return false;
+  if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
+  return p.nsplit >= 1 && p.nsplit <= 128;
+}
+
+bool aligned(const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
 
 // UQ_B200_CFG="path=fma" or "path=tc" forces a kernel (a forced tc on an unserved shape is invalid value).
 int forced_path() {
@@ -57,36 +74,42 @@ int forced_path() {
 }
 
 // Device address of the current device's status record (the symbol's name is only a host-side handle).
+// (nullptr for a device index outside the per-device tables: the caller answers cudaErrorInvalidDevice)
 unsigned int* status_ptr() {
-  static unsigned int* cached[64] = {nullptr};
+  static std::atomic<unsigned int*> cached[kMaxDevices];
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (!cached[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_uq_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    cached[dev] = reinterpret_cast<unsigned int*>(ptr);
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return nullptr; }
+  unsigned int* ptr = cached[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_uq_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    ptr = reinterpret_cast<unsigned int*>(sym);
+    cached[dev].store(ptr, std::memory_order_release);   // (two threads racing here store the same address)
   }
-  return cached[dev];
+  return ptr;
 }
 
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[kMaxDevices];
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-  return cached[dev] > 0 ? cached[dev] : 148;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 148; }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (!n) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n > 0 ? n : 148;
 }
 
 bool shape_ok(const UQParams& p) {
-  if (p.fmt != 0 && p.fmt != 1) return false;   // 0 UltraQuant, 1 NVFP4 (CUDA-core kernel only)
-  if (p.B < 0 || p.K < 1 || p.HQ < 1 || p.HKV < 1 || p.HQ % p.HKV) return false;
-  if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
+  if (p.fmt != 0 && p.fmt != 1) return false;   // 0 UltraQuant, 1 NVFP4; both kernels serve both
+  if (!sizes_ok(p)) return false;
   if (p.PAGE < 1 || p.max_pages < 0) return false;
-  if (p.nsplit < 1 || p.nsplit > 128) return false;
   if (uq_block_m(p.K, p.HQ, p.HKV) > 128) return false;   // the reference's limit on rows per tile
-  return p.q && p.kc && p.ks && p.vc && p.vs && p.block_table && p.seq_lens && p.mo && p.ml;
+  if (!(p.q && p.kc && p.ks && p.vc && p.vs && p.block_table && p.seq_lens && p.mo && p.ml)) return false;
+  // the alignment contract (see the head of this file): refused here, before anything is enqueued
+  if (!aligned(p.q, 16) || !aligned(p.kc, 16) || !aligned(p.mo, 8) || !aligned(p.ml, 4) || !aligned(p.block_table, 4) || !aligned(p.seq_lens, 4)) return false;
+  return !p.out || aligned(p.out, 4);
 }
 
 cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s);
@@ -103,7 +126,11 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
   x.k_total = p.K;
   x.len_cut = 0;
   x.status = status_ptr();
-  if (!x.status) return cudaErrorInitializationError;
+  if (!x.status) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    return dev < 0 || dev >= kMaxDevices ? cudaErrorInvalidDevice : cudaErrorInitializationError;
+  }
   // More query rows than the tensor-core kernel takes in one launch (K * group > 64, up to the 128 of uq_block_m): the
   // drafts are run as chunks of consecutive drafts, each a verify call of its own on the sequence cut after the chunk
   // (see UQLaunch), sharing the caller's scratch one after the other.  A tree-masked call is chunked without the cut: its
@@ -164,9 +191,14 @@ cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_par
 }  // namespace
 
 // ---- the reference's C++ surface -------------------------------------------------------------------
-int uq_block_m(int K, int HQ, int HKV) { return std::max(16, pow2ceil(K * pow2ceil(HQ / std::max(1, HKV)))); }
-size_t uq_mo_elems(const UQParams& p) { return (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV) * p.D; }
-size_t uq_ml_elems(const UQParams& p) { return (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV); }
+// (out-of-range arguments give sizes of 2^30 rows or zero elements instead of wrapping: callers compare these with what they
+// hold, and the launches refuse such arguments anyway)
+int uq_block_m(int K, int HQ, int HKV) {
+  if (K < 1 || HQ < 1 || HKV < 1 || K > (1 << 15) || HQ / HKV > (1 << 15)) return 1 << 30;
+  return std::max(16, pow2ceil(K * pow2ceil(HQ / HKV)));
+}
+size_t uq_mo_elems(const UQParams& p) { return sizes_ok(p) ? (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV) * p.D : 0; }
+size_t uq_ml_elems(const UQParams& p) { return sizes_ok(p) ? (size_t)p.B * p.HKV * p.nsplit * uq_block_m(p.K, p.HQ, p.HKV) : 0; }
 size_t uq_workspace_bytes(const UQParams& p) { return (uq_mo_elems(p) + uq_ml_elems(p)) * sizeof(float); }
 int uq_has_sm90() { return 0; }
 
@@ -259,24 +291,33 @@ size_t uqb_static_scratch_bytes(void) { return kStaticScratchFloats * sizeof(flo
 
 int uqb_decode_launch_static(const UQParams* p, int nwarps, int stages, void* stream) {
   if (!p) return (int)cudaErrorInvalidValue;
-  if (p->nsplit < 1 || p->nsplit > 128 || p->B < 0 || p->K < 1 || p->HKV < 1 || p->HQ < 1 || p->D < 1) return (int)cudaErrorInvalidValue;
+  if (!sizes_ok(*p)) return (int)cudaErrorInvalidValue;   // (before any size arithmetic)
   // the partials of this call must fit the built-in array: refuse, before anything is enqueued, a call that needs more
   if (uq_mo_elems(*p) + uq_ml_elems(*p) > kStaticScratchFloats) return (int)cudaErrorInvalidValue;
+  {
+    // every other argument check of the ordinary launch, before the device is asked for anything (the scratch pointers
+    // stand in as aligned non-null values; the real ones are set below)
+    UQParams probe = *p;
+    probe.mo = probe.ml = reinterpret_cast<float*>(uintptr_t(256));
+    if (!shape_ok(probe) || !probe.out) return (int)cudaErrorInvalidValue;
+  }
   // once per device, with that device current: ask the runtime where the array lives on this device
-  static float* base[64] = {nullptr};
+  static std::atomic<float*> base[kMaxDevices];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-  if (!base[dev]) {
+  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  float* scratch = base[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess) return (int)e;
-    base[dev] = reinterpret_cast<float*>(ptr);
+    scratch = reinterpret_cast<float*>(ptr);
+    base[dev].store(scratch, std::memory_order_release);
   }
   UQParams q = *p;
-  q.mo = base[dev];
-  q.ml = base[dev] + uq_mo_elems(q);
+  q.mo = scratch;
+  q.ml = scratch + uq_mo_elems(q);
   return (int)uq_decode_launch(q, nwarps, stages, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -8,36 +8,45 @@
 //     S^T[key, row] = Kdeq[key, :] . Q[row, :]        M = 128 keys, N = NT rows, K = D      (A from TMEM)
 //     O^T[d,   row] += Vdeq[key, d] * P[key, row]     M = 128 channels, N = NT rows, K = 128 keys
 //
-// One CTA per SM.  Warp roles (NSG = 4 softmax warpgroups when there are 32+ rows, else 2):
+// head_dim 128 with the UltraQuant cache takes S^T from a block-scaled contraction (kind::mxf8f6f4, one UE8M0 scale per 32
+// channels = the cache's own format): the K codes are never decoded (the copy engine unpacks them, the scale bytes go to
+// TMEM as they are) and Q is two e4m3 tiles (leading bits + remainder).  head_dim 64 / 256 and the NVFP4 cache decode K to
+// fp16 into a TMEM A operand instead.
+//
+// One CTA per SM, persistent over a flat list of 128-key tiles.  Warp roles (NSG = 4 softmax warpgroups at 32+ rows, else 2):
 //   softmax   4*NSG warps  thread = (key, NT/NSG rows): reads its lane of S^T from TMEM, exp2 against a per-row REFERENCE
-//                          maximum that moves only when a score exceeds it by 2^8 (the threads agree through one
-//                          rendezvous per tile), writes P^T fp16 to shared memory (MN-major B operand), keeps row sums in
-//                          registers; at the end of a segment reduces the sums, reads O^T and writes the partial.
-//   K decode  4 warps      thread = key: e2m1 -> fp16 by the hardware conversion, one fp16 multiply by the group scale
-//                          relative to the key's largest, tcgen05.st into the TMEM A operand (ring of 3)
-//   V decode  4 warps      thread = key: the same decode -> 128-byte-swizzled fp16 tile in shared memory (ring of 2)
-//   producer  2 warps      (one for the K side, one for the V side of every tile) TMA tensor copies (64-byte-swizzled boxes, so a thread can read a whole code row without
-//                          bank conflicts) of the K/V code pages + bulk copies of the scale pages, ring of 4 tiles
-//   Q.K issue 1 warp       8 tcgen05.mma per tile (one thread), owns the TMEM allocation
-//   P.V issue 1 warp       8 tcgen05.mma per tile (one thread)
-// The key's reference scales 2^(ref-127) are applied in fp32 by the softmax threads that own the key (K's to the score,
-// V's to the probability, relative to a running reference of the segment so that P fits fp16).
-// FMT = 1 is the NVFP4 cache (reference cuda/uq_decode.h:28-29: one e4m3fn scale byte per 16 channels): the two decode
-// roles multiply the converted codes by the block scale itself (exact in fp16) and the keys' references stay at 2^0.
-// Work is a flat list of 128-key tiles over all (sequence, kv head) items, cut into equal chunks, one per CTA;
-// a chunk that crosses items yields several segments, each written to its own partial slot.
+//                          that is fixed at the segment's first tile (quick pass; a segment where a probability or V value
+//                          then overflows fp16 is found by its epilogue and run again on the careful path, where the threads
+//                          agree tile by tile on moving the references), writes P^T fp16 (MN-major B operand) times the key's
+//                          V reference relative to the segment's, keeps row sums in registers; at the end of a segment
+//                          reduces the sums, reads O^T and writes the normalised partial with m + log2 l.
+//   relay     4 warps      block-scaled: the tile's K scale bytes -> TMEM, the keys' largest V scale bytes -> a side band for
+//                          the softmax threads.  Otherwise these are the K decode warps (thread = key: e2m1 -> fp16 by the
+//                          hardware conversion, one fp16 multiply by the group scale relative to the key's largest,
+//                          tcgen05.st into the TMEM A operand).
+//   V decode  4 warps at 64 rows, 8 below (two groups that take turns at the tiles): thread = key, the same decode ->
+//                          128-byte-swizzled fp16 tile in shared memory (ring of 2); gives its raw stage back as soon as the
+//                          key's codes and scale bytes are in registers.
+//   copy      2 warps      (K side / V side of every tile) TMA tensor copies of the code pages + bulk copies of the scale
+//                          pages into a ring of raw stages (3 at head_dim 128), mbarrier complete_tx.  No multicast.
+//   issue     1 thread     chosen by elect.sync: P.V of tile i, then Q.K of tile i + 2; tcgen05.commit to mbarriers; owns the
+//                          TMEM allocation.
+// Work is a flat list of tiles over all (sequence, kv head) items, cut into chunks of equal WEIGHT (an item counts its tiles
+// plus a few for what a segment start costs), one per CTA; a chunk that crosses items yields several segments, each written
+// to its own partial slot.
 //
-// Every wait is bounded (about one second): on expiry the thread records the barrier in the status record,
-// raises the CTA's abort flag and every role drains to the common exit, which frees TMEM.
+// Every wait is bounded (about one second): on expiry the thread records the barrier in the status record, raises the CTA's
+// abort flag and every role drains to the common exit, which frees TMEM.
 //
-// Where the time goes (clock64 timeline of one CTA, headline shape, K=8): the roles are latency bound, not throughput
-// bound.  A tile takes the softmax role about 3 200 cycles (score load 220, exp2 burst of all softmax warps at once and
-// the P^T write 1 500, rendezvous and hand-over 1 000, gap 500) against about 1 120 for the tensor pipe (a tcgen05.mma with
-// M = 128 costs 65-76 cycles for any N <= 128) and 600-1 000 for each decode role; every change of segment drains and
-// refills the pipeline (about 30 000 cycles: epilogue, query tile conversion, first-tile reference move).
+// Where the time goes (headline shape, K=8, B200): the call is bound neither by HBM (the same call on an L2-resident cache is
+// 3 % faster), nor by the tensor pipe (without its instructions: no change), but by the roles' serial chains: with every
+// role reduced to its waits and arrivals and the tensor instructions left out, the copy ring alone takes 95 us against 126
+// for the whole call: three raw stages at about 2 200 cycles from the first request of a tile to its barrier completing
+// (1 000 of them the eight copy instructions leaving their two warps) set a floor near 1 100 cycles per tile.
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "uq_common.cuh"
 
@@ -101,9 +110,6 @@ __device__ unsigned long long g_tc_prof[5][8];
 #ifndef UQ_SB128
 #define UQ_SB128 3   // K / S^T / P^T ring depth at head_dim 128
 #endif
-#ifndef UQ_PF
-#define UQ_PF 0   // tiles ahead of the copies that the producer prefetches into L2 (0 = none)
-#endif
 #ifndef UQ_PROD2
 #define UQ_PROD2 1   // copy warps beside the first: 0 one warp issues everything; 1 K side / V side; 2 K codes / V codes / both scale slices
 #endif
@@ -117,7 +123,7 @@ __device__ unsigned long long g_tc_prof[5][8];
 #define UQ_NSG4_AT 32
 #endif
 #ifndef UQ_ABL
-#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no work in the softmax's common tile, 32 no V decode, 64 no scale relay, 128 / 256 / 512 softmax / V / relay reduced to their waits and arrivals
+#define UQ_ABL 0   // timing experiments only (results become wrong): 1 no exp2, 2 no P write, 4 no reference loads, 8 no score loads, 16 no work in the softmax's common tile, 32 no V decode, 64 no scale relay, 128 / 256 / 512 softmax / V / relay reduced to their waits and arrivals, 1024 no tensor instructions (commits only), 2048 no copies of the scale slices
 #endif
 constexpr int kKeys = 128;      // keys per tile = accumulator lanes
 // Thread layout: NSG softmax warpgroups (each owns NT / NSG query rows of every key), then K decode (4 warps), V decode (4),
@@ -183,14 +189,6 @@ UQ_DEV void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.
 UQ_DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-// the same boxes and ranges fetched into L2 only (no shared memory, no barrier): issued a few tiles ahead of the copies, so
-// that a copy, which can start only when its shared-memory stage is free, finds its bytes in L2 instead of waiting for HBM
-UQ_DEV void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
-UQ_DEV void bulk_prefetch(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // contiguous bulk copy (scale pages)
 UQ_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -675,7 +673,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   if (warp == kWarpProd || (UQ_PROD2 >= 1 && warp == kWarpProd + 2) || (UQ_PROD2 == 2 && warp == kWarpProd + 3)) {
     // ================================================================= producer
     // what this warp copies of every tile: bit 0 K codes, bit 1 V codes, bit 2 K scales, bit 3 V scales
-    const int side = UQ_PROD2 == 0 ? 15 : (UQ_PROD2 == 1 ? (warp == kWarpProd ? 5 : 10) : (warp == kWarpProd ? 1 : (warp == kWarpProd + 2 ? 2 : 12)));
+    const int side = (UQ_PROD2 == 0 ? 15 : (UQ_PROD2 == 1 ? (warp == kWarpProd ? 5 : 10) : (warp == kWarpProd ? 1 : (warp == kWarpProd + 2 ? 2 : 12)))) & ((UQ_ABL & 2048) ? 3 : 15);
     // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
     const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
     const int spp_sh = __ffs(spp) - 1;   // (a power of two: the per-tile arithmetic below is shifts and masks, no division)
@@ -687,16 +685,17 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       const int n_loc = uq_n_local(p, x, sg.b, &off);
       const int pages_valid = (n_loc + unit - 1) / unit;   // (units)
       const int32_t* bt = p.block_table + (size_t)sg.b * p.max_pages;
+      // Page ids come 32 units at a time, a block ahead (lane j of `cur` = unit blk0 + j, `nxt` the block after it): the
+      // table's latency (an L2 round trip) stays out of the per-tile chain wait -> request.
+      auto load_ids = [&](int ub) -> int { const int uu = ub + lane; return uu < pages_valid ? __ldg(bt + (uu >> spp_sh)) : 0; };
+      int blk0 = sg.t0 * ppt;
+      int cur = load_ids(blk0), nxt = load_ids(blk0 + 32);
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
         const int stage = cnt % kRawStages;
         const int vp = min(ppt, pages_valid - t * ppt);
-        int pid = 0;
-        if (lane < vp) pid = __ldg(bt + ((t * ppt + lane) >> spp_sh));
-        // the tile UQ_PF ahead (same segment): its page ids are read now, beside the wait below
-        const int tp = t + UQ_PF;
-        const int vpp = (UQ_PF > 0 && tp < sg.t1) ? min(ppt, pages_valid - tp * ppt) : 0;
-        int pidp = 0;
-        if (lane < vpp) pidp = __ldg(bt + ((tp * ppt + lane) >> spp_sh));
+        if (t * ppt >= blk0 + 32) { cur = nxt; blk0 += 32; nxt = load_ids(blk0 + 32); }
+        // (units per tile divide 32 and blk0 is a multiple of them: a tile's units lie in one block)
+        const int pid = __shfl_sync(0xffffffffu, cur, (t * ppt - blk0 + lane) & 31);
         ok = wait(bar_raw_empty(stage), ((cnt / kRawStages) & 1) ^ 1, 100 + stage, t UQ_PROF_SITE(0));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -705,20 +704,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         if (lane == 0) mbar_expect_tx(bar_raw_full(stage), (uint32_t)vp * ((uint32_t)__popc(side & 3) * page_bytes_codes + (uint32_t)__popc(side & 12) * page_bytes_scales));
         __syncwarp();
         if (lane < vp) {
-          const int row0 = (pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;   // first cache row of this unit of (page, head)
+          // first cache row of this unit of (page, head); 64-bit: a cache may hold more than 2^31 / PAGE (page, head) slices
+          const long long row0 = ((long long)pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
-          if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, row0, fb);
-          if (side & 2) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, row0, fb);
+          if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, (int)row0, fb);
+          if (side & 2) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, (int)row0, fb);
           if (side & 4) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
           if (side & 8) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
-        }
-        if (lane < vpp) {
-          const int rowp = (pidp * p.HKV + sg.hk) * p.PAGE + ((tp * ppt + lane) & (spp - 1)) * unit;
-          tma_prefetch_2d(&map_kc, 0, rowp);
-          tma_prefetch_2d(&map_vc, 0, rowp);
-          bulk_prefetch(p.ks + (size_t)rowp * C::kScaleB, page_bytes_scales);
-          bulk_prefetch(p.vs + (size_t)rowp * C::kScaleB, page_bytes_scales);
         }
       }
     }
@@ -750,7 +743,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           tc_fence_after();
           UQ_TRACE(5, c)
           const uint32_t d = tmem + C::cS + buf * NT, a = tmem + C::cK + buf * C::kKCols;
-          if constexpr (C::kBS) {
+          if (UQ_ABL & 1024) {
+            tc_commit(bar(bSfull + buf));
+            if (C::kBS) tc_commit(bar_raw_empty(c % kRawStages));
+          } else if constexpr (C::kBS) {
             // A = the unpacked K codes of the tile's raw stage (K-major, 128-byte rows), B = the leading and the remainder tile of Q
             const int stage = c % kRawStages;
             const uint64_t a_desc = smem_desc(sm_a + C::oRaw + stage * C::kRawStage, 16, 1024);
@@ -782,7 +778,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           UQ_TRACE(7, c)
           const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
 #pragma unroll
-          for (int db = 0; db < C::kDB; db++) {
+          for (int db = 0; db < ((UQ_ABL & 1024) ? 0 : C::kDB); db++) {
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; kk++)
               mma_ss(tmem + C::cO + db * NT, va + (uint64_t)((db * 2 * C::kVHalf + kk * 2048) >> 4), pa + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i == 0 && kk == 0) ? 0u : 1u);
@@ -1276,7 +1272,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (!ok) break;
         } else if (!first) {
           // quick path: what this tile wrote may have overflowed; mark the segment for the second pass and carry on
-          if (grew && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
+          if (!UQ_ABL && grew && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
         }
         if (first || (agree && *reinterpret_cast<volatile int*>(&vote[vslot]))) {
           UQ_PROF_COUNT(6)
@@ -1389,7 +1385,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           }
         }
         // quick path: the segment's result is garbage then; the second pass computes it again on the careful path
-        if (!careful && __any_sync(0xffffffffu, bad) && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
+        if (!UQ_ABL && !careful && __any_sync(0xffffffffu, bad) && lane == 0) { atomicOr(&redo[ord >> 5], 1u << (ord & 31)); redo[kRedoWords] = 1u; }
         if (st < rows) { const float lr = (lsum[st] + lsum[NT + st]) + (lsum[2 * NT + st] + lsum[3 * NT + st]); ml[st] = lr > 0.f ? mr[st] + log2f(lr) : -INFINITY; }
       }
       tc_fence_before();
@@ -1465,18 +1461,46 @@ bool make_unpack_map(CUtensorMap* map, const uint8_t* base, int channels, int pa
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The tensor maps of the caches this thread used last (a serving loop calls with the same few caches over and over: encoding
+// a map costs the host a microsecond or two per call).  A map depends on the base address, the row width and the box only.
+struct MapKey {
+  const void* base;
+  int row_bytes, box_rows, unpack;
+  bool operator==(const MapKey& o) const { return base == o.base && row_bytes == o.row_bytes && box_rows == o.box_rows && unpack == o.unpack; }
+};
+bool cached_map(CUtensorMap* out, const MapKey& key) {
+  constexpr int kSlots = 16;
+  thread_local MapKey keys[kSlots] = {};
+  thread_local CUtensorMap maps[kSlots];
+  thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; i++)
+    if (keys[i] == key) { *out = maps[i]; return true; }
+  CUtensorMap m;
+  const uint8_t* base = static_cast<const uint8_t*>(key.base);
+  if (!(key.unpack ? make_unpack_map(&m, base, key.row_bytes * 2, key.box_rows) : make_code_map(&m, base, key.row_bytes, key.box_rows))) return false;
+  const int slot = used < kSlots ? used++ : (next = (next + 1) % kSlots);
+  keys[slot] = key;
+  maps[slot] = m;
+  *out = m;
+  return true;
+}
+
 template <int D, int NT, int FMT>
 cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   using C = Cfg<D, NT, FMT>;
   auto kern = uq_verify_tc_kernel<D, NT, FMT>;
-  static bool ready[64] = {false};
+  static std::atomic<bool> ready[64];
+  static std::atomic<int> sm_counts[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidValue;
-  if (!ready[dev]) {   // per device: the attribute belongs to the device's copy of the kernel
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!ready[dev].load(std::memory_order_acquire)) {   // per device: the attribute belongs to the device's copy of the kernel
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
     if (e != cudaSuccess) { cudaGetLastError(); return e; }
-    ready[dev] = true;
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sm_counts[dev].store(n, std::memory_order_relaxed);
+    ready[dev].store(true, std::memory_order_release);
   }
   Params prm;
   prm.p = p;
@@ -1486,10 +1510,9 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   prm.chunk_min = x.ns_eff >= 2 ? (int)((max_tiles + x.ns_eff - 2) / (x.ns_eff - 1)) : 1;
   CUtensorMap mk, mv;
   const int box_rows = std::min(p.PAGE, kKeys);   // a copy moves a page of up to 128 tokens, or a 128-token part of a larger one
-  if (!(C::kBS ? make_unpack_map(&mk, p.kc, D, box_rows) : make_code_map(&mk, p.kc, C::kCodeRow, box_rows)) || !make_code_map(&mv, p.vc, C::kCodeRow, box_rows))
-    return cudaErrorInvalidValue;
-  int sms = 0;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (!cached_map(&mk, MapKey{p.kc, C::kCodeRow, box_rows, C::kBS ? 1 : 0}) || !cached_map(&mv, MapKey{p.vc, C::kCodeRow, box_rows, 0})) return cudaErrorInvalidValue;
+  const int sms = sm_counts[dev].load(std::memory_order_relaxed);
+  if (sms <= 0) return cudaErrorInitializationError;
   kern<<<sms, cta_threads(NT), C::kSmem, s>>>(prm, mk, mv);
   return cudaGetLastError();
 }
@@ -1534,9 +1557,14 @@ bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
 // The flat list gives a CTA ceil(total / SMs) tiles and total >= Hkv x (tiles of the longest item), so an item spans at
 // most ceil(SMs / Hkv) + 1 CTAs; slots beyond that would only be marked empty by the kernel and skipped by the combine.
 int uq_verify_tc_splits(const UQParams& p, const UQLaunch&) {
+  static std::atomic<int> cached[64];
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); return p.nsplit; }
+  if (dev >= 0 && dev < 64) sms = cached[dev].load(std::memory_order_relaxed);
+  if (sms <= 0) {
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); return p.nsplit; }
+    if (dev >= 0 && dev < 64) cached[dev].store(sms, std::memory_order_relaxed);
+  }
   const int span = (sms + p.HKV - 1) / p.HKV + 1;
   return std::max(1, std::min(p.nsplit, span));
 }

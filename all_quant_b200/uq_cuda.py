@@ -71,6 +71,18 @@ def lib():
     return _lib
 
 
+_SMS = {}
+
+
+def _sm_count(device):
+    """Multiprocessors of `device`, looked up once (the property query is not free and sat in every call)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _SMS.get(idx)
+    if n is None:
+        n = _SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
 def _check(err, what):
     if err != 0:
         name = {1: "cudaErrorInvalidValue (shape not served / bad argument)"}.get(err, f"cudaError {err}")
@@ -186,7 +198,7 @@ def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nspl
     block_table = block_table.to(torch.int32)
     q = q.contiguous()
     if nsplit is None:
-        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], _sm_count(q.device), K, HQ // HKV)
     e = ext()
     mo = ml = None
     if workspace is not None:   # caller-owned fp32 scratch, nothing is allocated inside
@@ -248,7 +260,7 @@ def uq_tree_decode(q, kc, ks, vc, vs, block_table, seq_lens, tree_mask=None, *, 
     tm = tree_mask.to(device=q.device, dtype=torch.int32)
     tm = (tm.expand(B, K) if tm.dim() == 1 else tm).contiguous()
     if nsplit is None:
-        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], _sm_count(q.device), K, HQ // HKV)
     p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale)
     L = lib()
     n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
@@ -278,7 +290,7 @@ def uq_decode_static(q, kc, ks, vc, vs, block_table, seq_lens, out, *, nsplit=No
     B, K, HQ, D = q.shape
     HKV = kc.shape[1]
     if nsplit is None:
-        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], _sm_count(q.device), K, HQ // HKV)
     p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale if sm_scale is not None else D ** -0.5)
     p.out = out.data_ptr()
     L = lib()
@@ -392,7 +404,7 @@ def uq_decode_partial(q, kc, ks, vc, vs, block_table, seq_lens, pos_offset=None,
     block_table = block_table.to(torch.int32).contiguous()
     q = q.contiguous()
     if nsplit is None:
-        nsplit = auto_nsplit(B, HKV, block_table.shape[1], torch.cuda.get_device_properties(q.device).multi_processor_count, K, HQ // HKV)
+        nsplit = auto_nsplit(B, HKV, block_table.shape[1], _sm_count(q.device), K, HQ // HKV)
     p = _params(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, sm_scale)
     L = lib()
     n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))

@@ -64,3 +64,45 @@ def test_cpu_tensors_are_refused_not_served_by_a_fallback():
     s = torch.zeros(1, 1, 64, 4, dtype=torch.uint8)
     with pytest.raises(RuntimeError):
         uq_cuda.uq_decode_cuda(q, c, s, c, s, torch.zeros(1, 1, dtype=torch.int32), torch.ones(1, dtype=torch.int32))
+
+
+def _fake_params(**over):
+    """A UQParams whose pointers are made-up, well-aligned addresses: only for calls that must be refused by the host-side
+    checks before anything touches the device."""
+    p = uq_cuda.UQParams()
+    base = 0x7F0000000000
+    for i, n in enumerate(("q", "kc", "ks", "vc", "vs", "block_table", "seq_lens", "mo", "ml", "out")):
+        setattr(p, n, base + i * 0x100000)
+    p.B, p.K, p.HQ, p.HKV, p.D, p.PAGE, p.max_pages, p.nsplit = 2, 4, 8, 2, 128, 64, 16, 4
+    p.sm_scale = 128 ** -0.5
+    for k, v in over.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("field,delta", [("kc", 1), ("kc", 8), ("q", 2), ("q", 8), ("mo", 4), ("ml", 2), ("out", 2), ("seq_lens", 1),
+                                         ("block_table", 2)])
+def test_misaligned_pointers_are_refused_before_any_launch(field, delta):
+    """The alignment contract of the launch (q and kc 16 bytes, mo 8, ml / out / tables 4): a pointer that breaks it is
+    answered with cudaErrorInvalidValue and nothing is enqueued - no kernel ever sees it."""
+    L = uq_cuda.lib()
+    p = _fake_params()
+    setattr(p, field, getattr(p, field) + delta)
+    n0 = L.uqb_launch_count()
+    assert L.uqb_decode_launch(ctypes.byref(p), 0, 0, None) == uq_cuda.cudaErrorInvalidValue
+    assert L.uqb_decode_partial_launch(ctypes.byref(p), None, ctypes.c_void_p(0x7F1000000000), ctypes.c_void_p(0x7F1000100000), None) == uq_cuda.cudaErrorInvalidValue
+    assert L.uqb_launch_count() == n0
+
+
+@pytest.mark.parametrize("over", [dict(K=0), dict(K=1 << 20), dict(HQ=7), dict(HKV=0), dict(D=96), dict(nsplit=0), dict(nsplit=129),
+                                  dict(B=-1), dict(K=64, HQ=64, HKV=8), dict(PAGE=0), dict(fmt=2), dict(HQ=1 << 30, HKV=1)])
+def test_out_of_range_arguments_are_refused_and_sizes_do_not_wrap(over):
+    L = uq_cuda.lib()
+    p = _fake_params(**over)
+    n0 = L.uqb_launch_count()
+    assert L.uqb_decode_launch(ctypes.byref(p), 0, 0, None) == uq_cuda.cudaErrorInvalidValue
+    assert L.uqb_decode_launch_static(ctypes.byref(p), 0, 0, None) == uq_cuda.cudaErrorInvalidValue
+    assert L.uqb_launch_count() == n0
+    # the size helpers return (no endless loop, no wrapped product): zero elements for arguments outside the served ranges
+    assert L.uqb_workspace_bytes(ctypes.byref(p)) < (1 << 62)
+    assert L.uqb_block_m(1 << 30, 1 << 30, 1) == 1 << 30
