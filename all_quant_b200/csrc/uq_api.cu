@@ -37,7 +37,8 @@ cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_
 cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
 int uq_verify_tc_splits(const UQParams&, const UQLaunch&);
-cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, cudaStream_t);
+cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, const UQPeerPush*, cudaStream_t);
+cudaError_t uq_merge_wait_dispatch(const void*, int, size_t, unsigned int, size_t, int, void*, unsigned long long, unsigned int*, cudaStream_t);
 cudaError_t uq_merge_dispatch(const float*, const float*, int, size_t, int, void*, cudaStream_t);
 cudaError_t uq_merge_packed_dispatch(const float*, int, size_t, int, void*, cudaStream_t);
 
@@ -112,12 +113,13 @@ bool shape_ok(const UQParams& p) {
   return !p.out || aligned(p.out, 4);
 }
 
-cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s);
+cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s, const UQPeerPush* push);
 
-cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s, const int32_t* tree_mask = nullptr) {
+cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, float* lse_part, cudaStream_t s, const int32_t* tree_mask = nullptr,
+                const UQPeerPush* push = nullptr) {
   if (!shape_ok(p)) return cudaErrorInvalidValue;
   if (tree_mask && p.K > 16) return cudaErrorInvalidValue;   // the reference's limit (uqmt/tree.py:135)
-  if (!o_part && !p.out) return cudaErrorInvalidValue;
+  if (!o_part && !p.out && !push) return cudaErrorInvalidValue;
   if (p.B == 0) return cudaSuccess;
   UQLaunch x{};
   x.pos_offset = pos_offset;
@@ -148,17 +150,22 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
         pc.K = std::min(per, p.K - k0);
         xc.k_first = k0;
         xc.len_cut = tree_mask ? 0 : p.K - k0 - pc.K;
-        cudaError_t e = run_one(pc, xc, o_part, lse_part, s);
+        UQPeerPush pp{};
+        if (push) {   // every chunk stores its rows into the peers' buffers; the last one raises the flags
+          pp = *push;
+          pp.raise = k0 + per >= p.K;
+        }
+        cudaError_t e = run_one(pc, xc, o_part, lse_part, s, push ? &pp : nullptr);
         if (e != cudaSuccess) return e;
       }
       return cudaSuccess;
     }
   }
-  return run_one(p, x, o_part, lse_part, s);
+  return run_one(p, x, o_part, lse_part, s, push);
 }
 
 // One launch of a verify kernel and its combine; x carries the caller's pointers and the draft chunk.
-cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s) {
+cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_part, cudaStream_t s, const UQPeerPush* push) {
   x.G = p.HQ / p.HKV;
   x.rows = p.K * x.G;
   x.BM = uq_block_m(p.K, p.HQ, p.HKV);
@@ -185,7 +192,7 @@ cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_par
   if (timed) cudaEventRecord(t_ev_after, s);
   if (e != cudaSuccess) return e;
   g_launches += 2;
-  return uq_combine_dispatch(p, x, o_part, lse_part, s);
+  return uq_combine_dispatch(p, x, o_part, lse_part, push, s);
 }
 
 }  // namespace
@@ -273,6 +280,66 @@ int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* st
 
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16, void* stream) {
   cudaError_t e = uq_merge_dispatch(o_parts, lse2_parts, R, rows, D, out_bf16, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && rows > 0) g_launches += 1;
+  return (int)e;
+}
+
+// ---- context split over peer memory ---------------------------------------------------------------------------------
+size_t uqb_peer_bytes(int world, size_t rows, int D) {
+  if (world < 1 || world > kMaxPeers || D < 1) return 0;
+  return uq_peer_total_bytes(world, uq_peer_slot_floats(rows, D));
+}
+
+int uqb_peer_alloc(size_t bytes, void** ptr, unsigned char handle64[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  if (!ptr || !handle64 || bytes == 0) return (int)cudaErrorInvalidValue;
+  void* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(d, 0, bytes);   // flags and the block counter start at zero; sequence numbers start at one
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+  if (e != cudaSuccess) { cudaFree(d); return (int)e; }
+  std::memcpy(handle64, &h, 64);
+  *ptr = d;
+  return 0;
+}
+
+int uqb_peer_open(const unsigned char handle64[64], void** ptr) {
+  if (!ptr || !handle64) return (int)cudaErrorInvalidValue;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, 64);
+  return (int)cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+int uqb_peer_close(void* ptr) { return ptr ? (int)cudaIpcCloseMemHandle(ptr) : (int)cudaErrorInvalidValue; }
+int uqb_peer_free(void* ptr) { return ptr ? (int)cudaFree(ptr) : (int)cudaErrorInvalidValue; }
+
+int uqb_decode_partial_push_launch(const UQParams* p, const int32_t* pos_offset, void* const* bases, int world, int rank, unsigned int seq, void* stream) {
+  if (!p || !bases || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || seq == 0u || !sizes_ok(*p)) return (int)cudaErrorInvalidValue;
+  const size_t rows = (size_t)p->B * p->K * p->HQ, slot_floats = uq_peer_slot_floats(rows, p->D);
+  const int parity = (int)(seq & 1u);
+  UQPeerPush push{};
+  for (int r = 0; r < world; r++) {
+    if (!bases[r] || !aligned(bases[r], 16)) return (int)cudaErrorInvalidValue;
+    char* base = reinterpret_cast<char*>(bases[r]);
+    push.slot[r] = reinterpret_cast<float*>(base) + ((size_t)parity * world + rank) * slot_floats;
+    push.flag[r] = reinterpret_cast<unsigned int*>(base + uq_peer_data_bytes(world, slot_floats)) + parity * kMaxPeers + rank;
+  }
+  push.counter = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(bases[rank]) + uq_peer_data_bytes(world, slot_floats)) + 2 * kMaxPeers;
+  push.rows_total = rows;
+  push.world = world;
+  push.seq = seq;
+  push.raise = 1;
+  return (int)run(*p, pos_offset, nullptr, nullptr, reinterpret_cast<cudaStream_t>(stream), nullptr, &push);
+}
+
+int uqb_merge_wait_launch(const void* own_base, int world, unsigned int seq, size_t rows, int D, void* out_bf16, unsigned long long wait_ns, void* stream) {
+  if (seq == 0u || world < 1 || world > kMaxPeers || D < 1) return (int)cudaErrorInvalidValue;
+  unsigned int* status = status_ptr();
+  if (!status) return (int)cudaErrorInitializationError;
+  cudaError_t e = uq_merge_wait_dispatch(own_base, world, uq_peer_slot_floats(rows, D), seq, rows, D, out_bf16, wait_ns ? wait_ns : 1000000000ull, status,
+                                         reinterpret_cast<cudaStream_t>(stream));
   if (e == cudaSuccess && rows > 0) g_launches += 1;
   return (int)e;
 }

@@ -1,21 +1,23 @@
 // Log-sum-exp combine of split-KV partials (the reference's uq_reduce_kernel, reference
 // cuda/uq_decode.cu:353-388, restated): per query row,
 //   mx = max_s lse_s;  w_s = 2^(lse_s - mx);  out = sum_s w_s * o_s / sum_s w_s;  all -inf -> zeros.
-// One warp per output row; lanes stride the head dimension.  Three outputs are served by the same
-// arithmetic: bf16 [B,K,Hq,D] (the op's result), fp32 partial + lse (one shard of a context split), and
-// the merge of R shards' partials into bf16.
+// One warp per output row; lanes stride the head dimension.  The same arithmetic serves: bf16 [B,K,Hq,D] (the op's
+// result), fp32 partial + lse (one shard of a context split), that partial stored straight into every rank's exchange
+// buffer over NVLink with a flag behind it (plain peer stores, no collective call), and the merge of R shards' partials
+// into bf16, with or without a bounded wait for the R flags in front of it.
 #include "uq_common.cuh"
 
 namespace {
 
 // Partials of (b, hk) live in scratch slots s = 0..ns_eff-1, rows r = j*G + g with stride BM.
-template <bool kPartialOut>
+// kOut: 0 bf16 result, 1 fp32 partial + lse2 to the caller's arrays, 2 the same partial to every rank's exchange buffer
+template <int kOut>
 __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const UQLaunch x, float* __restrict__ o_part,
-                                                         float* __restrict__ lse_part) {
+                                                         float* __restrict__ lse_part, const UQPeerPush push) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);   // over [B, K, HQ]
   const int lane = threadIdx.x & 31;
   const int total = p.B * p.K * p.HQ;
-  if (row >= total) return;
+  if (row < total) {
   const int h = row % p.HQ, j = (row / p.HQ) % p.K, b = row / (p.HQ * p.K);
   const int hk = h / x.G, r = j * x.G + (h % x.G);
   const int D = p.D;
@@ -78,13 +80,24 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
     }
   }
   const float inv = (den > 0.f ? 1.f / den : 0.f) * x.out_scale;
-  if (kPartialOut) {
+  if (kOut == 1) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int d = lane + 32 * i;
       if (d < D) o_part[orow * D + d] = acc[i] * inv;
     }
     if (lane == 0) lse_part[orow] = den > 0.f ? mx + log2f(den) : -INFINITY;
+  } else if (kOut == 2) {
+    const float lse2 = den > 0.f ? mx + log2f(den) : -INFINITY;
+    for (int r = 0; r < push.world; r++) {   // plain stores into each rank's buffer (the local one included)
+      float* dst = push.slot[r];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < D) dst[orow * D + d] = acc[i] * inv;
+      }
+      if (lane == 0) dst[push.rows_total * D + orow] = lse2;
+    }
   } else {
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + orow * D;
 #pragma unroll
@@ -93,12 +106,54 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
       if (d < D) out[d] = __float2bfloat16_rn(acc[i] * inv);
     }
   }
+  }
+  if (kOut == 2 && push.raise) {
+    // the block that finishes last raises this rank's flag on every rank: each block's stores are fenced at system scope
+    // before its ticket, and the last ticket holder fences again before the flags, so whoever sees a flag sees the partial
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int ticket = atomicAdd(push.counter, 1u);
+      if (ticket == gridDim.x - 1) {
+        __threadfence_system();
+        for (int r = 0; r < push.world; r++) *reinterpret_cast<volatile unsigned int*>(push.flag[r]) = push.seq;
+        *push.counter = 0u;
+      }
+    }
+  }
+}
+
+UQ_DEV unsigned int load_acquire_sys(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+UQ_DEV unsigned long long timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 // Merge of R shards: o [R, rows, D], lse2 [R, rows] -> bf16 [rows, D].  The shards may be apart by any stride (in floats):
 // rows * D and rows for two plain arrays, rows * (D + 1) for both when every shard is one packed buffer (o, then lse2).
-__global__ void __launch_bounds__(128) uq_merge_kernel(const float* __restrict__ o, const float* __restrict__ lse, int R, size_t rows, int D,
-                                                       size_t o_stride, size_t l_stride, __nv_bfloat16* __restrict__ out) {
+// flags != nullptr: thread r of every block first waits until flags[r] == seq (rank r's partial has arrived in this rank's
+// exchange buffer), for wait_ns nanoseconds at most; when a wait runs out the status record gets code 3 with the rank and
+// the sequence number, nothing is written and the kernel returns.
+__global__ void __launch_bounds__(128) uq_merge_kernel(const float* o, const float* lse, int R, size_t rows, int D,
+                                                       size_t o_stride, size_t l_stride, __nv_bfloat16* __restrict__ out,
+                                                       const unsigned int* flags, unsigned int seq, unsigned long long wait_ns, unsigned int* status) {
+  if (flags) {
+    int arrived = 1;
+    if ((int)threadIdx.x < R) {
+      const unsigned long long t0 = timer_ns();
+      while (load_acquire_sys(flags + threadIdx.x) != seq) {
+        if (timer_ns() - t0 > wait_ns) { arrived = 0; break; }
+        __nanosleep(40);
+      }
+      if (!arrived) uq_report(status, 3u, threadIdx.x, seq);
+    }
+    if (!__syncthreads_and(arrived)) return;
+  }
   const size_t row = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -132,20 +187,23 @@ __global__ void __launch_bounds__(128) uq_merge_kernel(const float* __restrict__
 
 }  // namespace
 
-cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_part, float* lse_part, cudaStream_t s) {
+cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_part, float* lse_part, const UQPeerPush* push, cudaStream_t s) {
   const int rows = p.B * p.K * p.HQ;
   if (rows == 0) return cudaSuccess;
-  if (o_part)
-    uq_combine_kernel<true><<<(rows + 3) / 4, 128, 0, s>>>(p, x, o_part, lse_part);
+  const UQPeerPush none{};
+  if (push)
+    uq_combine_kernel<2><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr, *push);
+  else if (o_part)
+    uq_combine_kernel<1><<<(rows + 3) / 4, 128, 0, s>>>(p, x, o_part, lse_part, none);
   else
-    uq_combine_kernel<false><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr);
+    uq_combine_kernel<0><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr, none);
   return cudaGetLastError();
 }
 
 cudaError_t uq_merge_dispatch(const float* o, const float* lse, int R, size_t rows, int D, void* out, cudaStream_t s) {
   if (!o || !lse || !out || R < 1 || D < 32 || D > 256 || D % 32) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
-  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, lse, R, rows, D, rows * D, rows, reinterpret_cast<__nv_bfloat16*>(out));
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(o, lse, R, rows, D, rows * D, rows, reinterpret_cast<__nv_bfloat16*>(out), nullptr, 0u, 0ull, nullptr);
   return cudaGetLastError();
 }
 
@@ -154,6 +212,19 @@ cudaError_t uq_merge_packed_dispatch(const float* packed, int R, size_t rows, in
   if (!packed || !out || R < 1 || D < 32 || D > 256 || D % 32) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
   const size_t stride = rows * D + rows;
-  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(packed, packed + rows * D, R, rows, D, stride, stride, reinterpret_cast<__nv_bfloat16*>(out));
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(packed, packed + rows * D, R, rows, D, stride, stride, reinterpret_cast<__nv_bfloat16*>(out), nullptr, 0u, 0ull, nullptr);
+  return cudaGetLastError();
+}
+
+// The merge of a context split over peer memory: the R slots of this rank's exchange buffer (parity seq & 1), each rank's
+// partial awaited through its flag.  `own` is the buffer's base, slot_floats its slot size.
+cudaError_t uq_merge_wait_dispatch(const void* own, int R, size_t slot_floats, unsigned int seq, size_t rows, int D, void* out,
+                                   unsigned long long wait_ns, unsigned int* status, cudaStream_t s) {
+  if (!own || !out || !status || R < 1 || R > kMaxPeers || D < 32 || D > 256 || D % 32 || rows * (size_t)(D + 1) > slot_floats) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const int parity = (int)(seq & 1u);
+  const float* data = reinterpret_cast<const float*>(own) + (size_t)parity * R * slot_floats;
+  const unsigned int* flags = reinterpret_cast<const unsigned int*>(reinterpret_cast<const char*>(own) + uq_peer_data_bytes(R, slot_floats)) + parity * kMaxPeers;
+  uq_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(data, data + rows * D, R, rows, D, slot_floats, slot_floats, reinterpret_cast<__nv_bfloat16*>(out), flags, seq, wait_ns, status);
   return cudaGetLastError();
 }

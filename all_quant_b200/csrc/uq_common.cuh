@@ -29,6 +29,24 @@ struct UQLaunch {
   unsigned int* status;       // this device's status record (4 words), see uq_report
 };
 
+// ---- where the combine of a context shard sends its packed partial (context split over peer memory) ----------------
+// Every rank owns one exchange buffer, mapped on every other rank: [2 parities][world slots][slot_floats] floats, then
+// [2][kMaxPeers] flag words, then one counter word.  A call with sequence number seq uses parity seq & 1: rank r stores its
+// partial (o [rows, D], then lse2 [rows]) into slot r of every rank's buffer and then sets flag[parity][r] = seq there.
+constexpr int kMaxPeers = 8;
+struct UQPeerPush {
+  float* slot[kMaxPeers];          // this rank's slot in every rank's buffer, parity applied (slot[rank] is the local one)
+  unsigned int* flag[kMaxPeers];   // this rank's flag word in every rank's buffer, parity applied
+  unsigned int* counter;           // local word counting the combine's finished blocks (zero between calls)
+  size_t rows_total;               // rows of the whole call: the lse2 values follow rows_total * D floats of o
+  int world;
+  unsigned int seq;
+  int raise;                       // 1: this launch is the call's last and raises the flags once its blocks are done
+};
+__host__ __device__ inline size_t uq_peer_slot_floats(size_t rows, int D) { return (rows * (size_t)(D + 1) + 3) / 4 * 4; }
+__host__ __device__ inline size_t uq_peer_data_bytes(int world, size_t slot_floats) { return ((size_t)2 * world * slot_floats * sizeof(float) + 255) / 256 * 256; }
+__host__ __device__ inline size_t uq_peer_total_bytes(int world, size_t slot_floats) { return uq_peer_data_bytes(world, slot_floats) + 2 * kMaxPeers * sizeof(unsigned int) + 64; }
+
 // Scratch slot (b, hk, s): rows are r = j * G + g (draft j, head g of the group), row stride BM.
 UQ_DEV size_t uq_slot(const UQParams& p, int b, int hk, int s) { return ((size_t)b * p.HKV + hk) * p.nsplit + s; }
 

@@ -35,7 +35,8 @@ class UQParams(ctypes.Structure):
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
            "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_append_nvfp4_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
-           "uqb_decode_launch_static", "uqb_static_scratch_bytes")
+           "uqb_decode_launch_static", "uqb_static_scratch_bytes",
+           "uqb_peer_bytes", "uqb_peer_alloc", "uqb_peer_open", "uqb_peer_close", "uqb_peer_free", "uqb_decode_partial_push_launch", "uqb_merge_wait_launch")
 
 
 def lib():
@@ -67,6 +68,14 @@ def lib():
         L.uqb_debug_events.restype = None
         L.uqb_decode_launch_static.argtypes = [pp, i, i, vp]
         L.uqb_static_scratch_bytes.restype = sz
+        L.uqb_peer_bytes.argtypes = [i, sz, i]
+        L.uqb_peer_bytes.restype = sz
+        L.uqb_peer_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
+        L.uqb_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.uqb_peer_close.argtypes = [vp]
+        L.uqb_peer_free.argtypes = [vp]
+        L.uqb_decode_partial_push_launch.argtypes = [pp, vp, ctypes.POINTER(vp), i, i, ctypes.c_uint, vp]
+        L.uqb_merge_wait_launch.argtypes = [vp, i, ctypes.c_uint, sz, i, vp, ctypes.c_ulonglong, vp]
         _lib = L
     return _lib
 
@@ -527,3 +536,113 @@ def uq_decode_context_split(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_
     o_all = both[:, :n_o].contiguous().view((world,) + tuple(o.shape))
     l_all = both[:, n_o:].contiguous().view((world,) + tuple(lse.shape))
     return merge_fn(o_all, l_all)
+
+
+class ContextSplit:
+    """Mode (b) without a collective call on the data path: every rank owns an exchange buffer that all ranks of the box map
+    (CUDA IPC; one process per GPU), a call is two launches per rank - the shard's attention, whose combine kernel stores the
+    packed partial into every rank's buffer over NVLink and raises a flag behind it, and the merge, which waits (bounded) for
+    all ranks' flags and then merges what has arrived locally.  Not in the reference, which has no multi-GPU code.
+
+    Set-up (allocates and maps memory, exchanges the handles over `group` once): ContextSplit(rows, D, group=...), rows =
+    B*K*Hq of the largest call.  Then run(...) per call, the same number of times on every rank.  `wait_ns` bounds the
+    merge's wait for the other ranks (0 = one second); a wait that runs out leaves code 3 in last_status() and the output
+    of that call undefined - the group should then be abandoned (a rank has left or hangs)."""
+
+    def __init__(self, rows, D, *, group=None, device=None, wait_ns=0, _bases=None, _rank=None):
+        L = lib()
+        self.rows, self.D, self.wait_ns, self.seq = int(rows), int(D), int(wait_ns), 0
+        self._opened, self._own, self._ws = [], None, {}
+        if _bases is not None:   # several ranks' objects inside one process (tests on one GPU): the buffers are shared as they are
+            self.world, self.rank, self.bases = len(_bases), int(_rank), list(_bases)
+            return
+        import torch.distributed as dist
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        nbytes = int(L.uqb_peer_bytes(self.world, self.rows, self.D))
+        if nbytes == 0:
+            raise RuntimeError("ContextSplit: up to 8 ranks")
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(dev):
+            _check(L.uqb_peer_alloc(nbytes, ctypes.byref(own), handle), "uq_peer_alloc")
+            self._own = own.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self.bases = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.bases.append(self._own)
+                    continue
+                ptr = ctypes.c_void_p()
+                _check(L.uqb_peer_open(h, ctypes.byref(ptr)), "uq_peer_open")
+                self._opened.append(ptr.value)
+                self.bases.append(ptr.value)
+        dist.barrier(group=group)   # nobody stores into a buffer before every rank has mapped all of them
+
+    @staticmethod
+    def in_one_process(world, rows, D, wait_ns=0):
+        """`world` rank objects that share one process and one GPU (single-GPU tests of the two kernels: their launches run
+        one after the other on a stream, none waits for a later one)."""
+        L = lib()
+        nbytes = int(L.uqb_peer_bytes(world, rows, D))
+        bases = []
+        for _ in range(world):
+            ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            _check(L.uqb_peer_alloc(nbytes, ctypes.byref(ptr), handle), "uq_peer_alloc")
+            bases.append(ptr.value)
+        objs = [ContextSplit(rows, D, wait_ns=wait_ns, _bases=bases, _rank=r) for r in range(world)]
+        objs[0]._owned_all = bases
+        return objs
+
+    def push(self, q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, *, seq, nsplit=None, sm_scale=None):
+        """First launch of call `seq`: this rank's shard, its partial stored into every rank's buffer, then the flags."""
+        _need_cuda(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset)
+        B, K, HQ, D = q.shape
+        if B * K * HQ > self.rows or D != self.D:
+            raise RuntimeError("ContextSplit: the call has more rows than the exchange buffers were made for")
+        if not (q.is_contiguous() and block_table_local.dtype == torch.int32 and block_table_local.is_contiguous()
+                and seq_lens.dtype == torch.int32 and pos_offset.dtype == torch.int32):
+            raise RuntimeError("ContextSplit: q contiguous, tables and offsets int32 (nothing is converted on this path)")
+        HKV = kc.shape[1]
+        if nsplit is None:
+            nsplit = auto_nsplit(B, HKV, block_table_local.shape[1], _sm_count(q.device), K, HQ // HKV)
+        p = _params(q, kc, ks, vc, vs, block_table_local, seq_lens, nsplit, sm_scale if sm_scale is not None else D ** -0.5)
+        L = lib()
+        key = (B, K, HQ, HKV, D, int(nsplit), q.device.index)
+        ws = self._ws.get(key)
+        if ws is None:   # the scratch of this shape: allocated at its first call, kept
+            n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
+            ws = self._ws[key] = (torch.empty(n_mo + n_ml, dtype=torch.float32, device=q.device), n_mo)
+        p.mo, p.ml = ws[0].data_ptr(), ws[0].data_ptr() + 4 * ws[1]
+        bases = (ctypes.c_void_p * self.world)(*self.bases)
+        with torch.cuda.device(q.device):
+            err = L.uqb_decode_partial_push_launch(ctypes.byref(p), pos_offset.data_ptr(), bases, self.world, self.rank, int(seq), _stream(q))
+        _check(err, "uq_decode_partial_push_launch")
+
+    def merge(self, q, out=None, *, seq):
+        """Second launch of call `seq`: wait for every rank's flag, merge the slots of the local buffer into `out` (bf16, q's shape)."""
+        B, K, HQ, D = q.shape
+        out = torch.empty_like(q) if out is None else out
+        with torch.cuda.device(q.device):
+            err = lib().uqb_merge_wait_launch(self.bases[self.rank], self.world, int(seq), B * K * HQ, D, out.data_ptr(), self.wait_ns, _stream(q))
+        _check(err, "uq_merge_wait_launch")
+        return out
+
+    def run(self, q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, *, out=None, nsplit=None, sm_scale=None):
+        """One call on this rank: push, then merge.  Every rank returns the full bf16 output."""
+        self.seq += 1
+        self.push(q, kc, ks, vc, vs, block_table_local, seq_lens, pos_offset, seq=self.seq, nsplit=nsplit, sm_scale=sm_scale)
+        return self.merge(q, out, seq=self.seq)
+
+    def close(self):
+        """Unmap the other ranks' buffers and free this rank's (after every rank has finished its last call)."""
+        L = lib()
+        for ptr in self._opened:
+            L.uqb_peer_close(ptr)
+        self._opened = []
+        for ptr in getattr(self, "_owned_all", []):
+            L.uqb_peer_free(ptr)
+        self._owned_all = []
+        if self._own:
+            L.uqb_peer_free(self._own)
+            self._own = None

@@ -83,7 +83,7 @@ def local_kv_bytes(cfg, plan):
 
 
 def peaks():
-    """Measured roofline denominators of this pool (driver-written file), else the stated fallback."""
+    """The measured copy bandwidth of MEASURED_PEAKS.json when the file is there, else the stated fallback figure."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
@@ -149,7 +149,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ data
-def build_case(cfg, plan, K, seed, device, copies=2):
+def build_case(cfg, plan, K, seed, device, copies=2, q_seed=None):
     """Seeded synthetic cache(s) and queries on `device` for this rank's shard; the cache is encoded by the
     library's append kernel.  Returns q, the page table, global seq_lens, pos_offset, `copies` caches with the
     same bytes at different addresses, and (for the append leg) the K newest tokens of every sequence with their slots."""
@@ -191,7 +191,9 @@ def build_case(cfg, plan, K, seed, device, copies=2):
             new_k.append(k[lo:].bfloat16())
             new_v.append(v[lo:].bfloat16())
             new_slots.append(slots[lo:])
-    q = torch.randn(B, K, hq, D, generator=g, device=device).bfloat16()
+    # (a context split hands every rank the same queries: they come from a generator of their own there)
+    gq = g if q_seed is None else torch.Generator(device=device).manual_seed(q_seed)
+    q = torch.randn(B, K, hq, D, generator=gq, device=device).bfloat16()
     sl = torch.tensor(plan["lens"], dtype=torch.int32, device=device)
     po = torch.full((B,), off, dtype=torch.int32, device=device)
     caches = [(kc, ks, vc, vs)]
@@ -206,6 +208,7 @@ def build_case(cfg, plan, K, seed, device, copies=2):
 def cpu_sample(case_np, steps, warmup, nvfp4=None):
     """Times the CPU oracle on sequence 0 (all KV heads, full context) of one layer; nvfp4 = (k_ts, v_ts) for an NVFP4 cache."""
     from oracle import uq_oracle as O
+    O.set_threads(0)
     q, kc, ks, vc, vs, bt, sl = case_np
     ts = []
     out = None
@@ -229,6 +232,7 @@ def run_reference_arm(args, cfg):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     from oracle import uq_oracle as O
+    O.set_threads(0)   # all host cores: a launcher's OMP_NUM_THREADS=1 for its workers is not this arm's choice
     rng = np.random.default_rng(1001)
     B, HQ, HKV, D, PAGE = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE"))
     lens = seq_lengths(cfg)

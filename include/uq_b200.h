@@ -3,6 +3,12 @@
  * (0 = success, 1 = cudaErrorInvalidValue = "this shape is not served", nothing was enqueued).
  * All launches are asynchronous on `stream` (a cudaStream_t passed as void*), allocate nothing and
  * never read device memory on the host.  Pointers are caller-owned device memory.
+ * Alignment: q and kc 16 bytes, mo 8 bytes, ml / out / block_table / seq_lens 4 bytes; a pointer that breaks this is
+ * refused with cudaErrorInvalidValue before anything is enqueued.  (vc, ks, vs: any alignment; 16-byte aligned ones - 32
+ * for kc at head_dim 128 - let the call run on the tcgen05 kernel instead of the CUDA-core one.)
+ * First call: the first uqb_decode_* / uqb_tree_* / uqb_merge_wait_* call on each device loads the library's device
+ * module (which carries the 24 MiB array of uqb_decode_launch_static whether or not that entry is ever used), looks up
+ * per-device addresses and sets kernel attributes; make it outside any stream capture.  Device indices 0..63.
  *
  * Each function names the reference interface it stands in for (reference file:line), or says that
  * the reference has no counterpart. */
@@ -90,6 +96,35 @@ int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_
  * all-gather of the ranks' buffers gives): packed fp32 [R][rows*D + rows].  No counterpart in the reference. */
 int uqb_merge_packed_launch(const float* packed, int R, size_t rows, int D, void* out_bf16, void* stream);
 
+/* ---- context split over peer memory: the partials cross NVLink by plain stores, no collective call (no counterpart
+ *      in the reference, which has no multi-GPU code) ------------------------------------------------------------------
+ * Every rank owns one exchange buffer of uqb_peer_bytes(world, rows, D) bytes (rows = B*K*Hq of the largest call it will
+ * serve), allocated by uqb_peer_alloc, which also returns a 64-byte handle; the other ranks (one process per GPU of one
+ * box) open the handle with uqb_peer_open and get a pointer to that buffer that their kernels can store through.  These
+ * four calls allocate / map memory: they belong to set-up, never to the serving loop.
+ * A call then is two launches per rank, both asynchronous and allocation-free:
+ *   uqb_decode_partial_push_launch  attention over this rank's context shard (as uqb_decode_partial_launch); the combine
+ *                                   kernel stores the packed partial (o fp32 [rows,D], then lse2 [rows]) into this rank's
+ *                                   slot of EVERY rank's buffer (bases[r], r = 0..world-1, bases[rank] the local one) and,
+ *                                   when its last block is done, sets this rank's flag there to `seq`;
+ *   uqb_merge_wait_launch           waits until all `world` flags of the local buffer equal `seq`, then merges the slots
+ *                                   to bf16 [rows,D] (the arithmetic of uqb_merge_packed_launch).
+ * seq is the caller's call counter: it starts at 1, grows by one per call and is the same on every rank; slots and flags
+ * are double buffered by its parity, so a rank may run one call ahead of the slowest.  The wait is bounded: after wait_ns
+ * nanoseconds (0 = one second) without a rank's flag the kernel writes nothing, records code 3 with that rank and seq in
+ * the status record (uqb_last_status) and returns - the output of that call is then undefined and the caller decides
+ * (a rank that has left: stop using the group).  p->out, p->mo / p->ml as for uqb_decode_partial_launch (scratch needed,
+ * out unused).  world <= 8.  All pointers in `bases` must be device-accessible from this rank. */
+size_t uqb_peer_bytes(int world, size_t rows, int D);
+int uqb_peer_alloc(size_t bytes, void** ptr, unsigned char handle64[64]);
+int uqb_peer_open(const unsigned char handle64[64], void** ptr);
+int uqb_peer_close(void* ptr);
+int uqb_peer_free(void* ptr);
+int uqb_decode_partial_push_launch(const UQParams* p, const int32_t* pos_offset, void* const* bases, int world, int rank,
+                                   unsigned int seq, void* stream);
+int uqb_merge_wait_launch(const void* own_base, int world, unsigned int seq, size_t rows, int D, void* out_bf16,
+                          unsigned long long wait_ns, void* stream);
+
 /* ---- the launch for callers that may not allocate (no counterpart in the reference) ---------- */
 
 /* uqb_decode_launch without caller-owned scratch: p->mo and p->ml are ignored and the split-KV partials go to a
@@ -114,7 +149,11 @@ size_t uqb_static_scratch_bytes(void);
 
 /* Every device-side wait in this library is bounded; a wait that runs out records what it was
  * waiting for and the kernel returns.  Reads (and clears) the current device's record:
- * out4[0] = code (0 = none), out4[1] = block, out4[2] = barrier id, out4[3] = tile.  Synchronises the device. */
+ * out4[0] = code (0 = none, 1 = a barrier wait of the attention kernel, 3 = a rank's flag in uqb_merge_wait_launch),
+ * out4[1] = block, out4[2] = barrier id (code 3: the rank), out4[3] = tile (code 3: seq).  Synchronises the device.
+ * When the code is not zero, the outputs of the calls since the last read are undefined (the kernel that gave up left
+ * its results unwritten or partial): a caller that cannot afford that reads the record before it uses them, e.g. once
+ * per step behind the step's own synchronisation; the launches themselves still return 0. */
 int uqb_last_status(uint32_t out4[4]);
 /* Which kernel the last uqb_decode_* call on this thread chose: 1 = CUDA-core path, 2 = tcgen05 path. */
 int uqb_last_path(void);

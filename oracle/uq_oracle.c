@@ -30,6 +30,20 @@ int uqo_max_threads(void) {
 #endif
 }
 
+/* Number of threads the parallel loops below use from now on (n < 1: every processor of the machine).  A launcher may
+ * have set OMP_NUM_THREADS=1 for its workers (torch.distributed.run does): the benchmark's CPU arm calls this so that its
+ * figure is for all host cores whoever started it.  Returns the count in effect. */
+int uqo_set_threads(int n) {
+#ifdef _OPENMP
+  if (n < 1) n = omp_get_num_procs();
+  omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /*
  * Encoder for one group of 32 values (uqmt/attn.py:52-66, frozen twin tools/gen_vectors.py:18-30).
  *   amax  = max |x| clamped below at 1e-30

@@ -58,6 +58,14 @@ def max_threads():
     return int(lib().uqo_max_threads())
 
 
+def set_threads(n=0):
+    """Threads of the oracle's parallel loops from now on (0 = all processors, whatever OMP_NUM_THREADS said); returns the count."""
+    L = lib()
+    L.uqo_set_threads.argtypes = [ctypes.c_int]
+    L.uqo_set_threads.restype = ctypes.c_int
+    return int(L.uqo_set_threads(int(n)))
+
+
 def bf16_bits(x):
     """fp32 numpy array -> bf16 bit patterns (round to nearest even), as uint16."""
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)

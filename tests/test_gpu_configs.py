@@ -178,3 +178,59 @@ def test_query_block_with_one_entry_far_above_the_rest(D):
     out = uq_cuda.uq_decode_cuda(dev(qb.view(np.int16), torch.bfloat16), dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl), sm_scale=D ** -0.5 / 16)
     assert uq_cuda.last_status() == (0, 0, 0, 0)
     check_close(out.float().cpu().numpy(), ref, f"query outliers D={D}")
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_context_split_over_exchange_buffers_in_one_process(R):
+    """The two launches of the peer-memory context split - the shard's attention whose combine stores the packed partial
+    into every rank's exchange buffer and raises its flag, and the merge that waits for all flags - with the R ranks'
+    buffers living in one process on one GPU (the launches run in stream order, so no kernel waits for a later one).  Every
+    rank's merged output equals the oracle's answer for the whole sequence, on two calls in a row (the second on the other
+    parity of the double-buffered slots)."""
+    rng = np.random.default_rng(40 + R)
+    HQ, HKV, D, PAGE, K = 32, 4, 256, 64, 8
+    sl = np.array([3000], np.int32)
+    kc, ks, vc, vs, bt = make_cache(rng, sl, HKV, D, PAGE)
+    caches = tuple(dev(a) for a in (kc, ks, vc, vs))
+    ranks = uq_cuda.ContextSplit.in_one_process(R, K * HQ, D)
+    try:
+        for call in range(2):
+            qb = O.bf16_bits(rng.standard_normal((1, K, HQ, D)).astype(np.float32))
+            ref = O.reference(qb, kc, ks, vc, vs, bt, sl)
+            q = dev(qb.view(np.int16), torch.bfloat16)
+            for r, cs in enumerate(ranks):
+                bt_r, off_r = uq_cuda.context_shard(dev(bt), r, R, PAGE)
+                cs.push(q, *caches, bt_r, dev(sl), off_r, seq=call + 1)
+            for cs in ranks:
+                out = cs.merge(q, seq=call + 1)
+                assert uq_cuda.last_status() == (0, 0, 0, 0)
+                check_close(out.float().cpu().numpy(), ref, f"{R} ranks, call {call}, rank {cs.rank}")
+    finally:
+        torch.cuda.synchronize()
+        ranks[0].close()
+
+
+def test_a_rank_that_never_arrives_ends_the_merge_wait_with_a_status():
+    """The merge's wait for the other ranks is bounded: with a limit of two milliseconds and a second rank that never stores
+    anything (its flag is never set), the kernel returns, the status record names the wait (code 3), the missing rank and
+    the sequence number, and the next ordinary call on the device is unaffected."""
+    rng = np.random.default_rng(77)
+    HQ, HKV, D, PAGE, K = 8, 2, 128, 64, 2
+    sl = np.array([300], np.int32)
+    kc, ks, vc, vs, bt = make_cache(rng, sl, HKV, D, PAGE)
+    caches = tuple(dev(a) for a in (kc, ks, vc, vs))
+    qb = O.bf16_bits(rng.standard_normal((1, K, HQ, D)).astype(np.float32))
+    q = dev(qb.view(np.int16), torch.bfloat16)
+    ranks = uq_cuda.ContextSplit.in_one_process(2, K * HQ, D, wait_ns=2_000_000)
+    try:
+        bt_0, off_0 = uq_cuda.context_shard(dev(bt), 0, 2, PAGE)
+        ranks[0].push(q, *caches, bt_0, dev(sl), off_0, seq=1)     # rank 1 never pushes
+        ranks[0].merge(q, seq=1)
+        code, _, who, seq = uq_cuda.last_status()
+        assert (code, who, seq) == (3, 1, 1)
+        out = uq_cuda.uq_decode_cuda(q, *caches, dev(bt), dev(sl))
+        assert uq_cuda.last_status() == (0, 0, 0, 0)
+        check_close(out.float().cpu().numpy(), O.reference(qb, kc, ks, vc, vs, bt, sl), "call after the timed-out wait")
+    finally:
+        torch.cuda.synchronize()
+        ranks[0].close()
