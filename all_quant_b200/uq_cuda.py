@@ -92,6 +92,32 @@ def _sm_count(device):
     return n
 
 
+def _pow2ceil(v):
+    return 1 if v <= 1 else 1 << (int(v) - 1).bit_length()
+
+
+def _block_m(K, HQ, HKV):
+    """uq_block_m in Python (reference cuda/uq_decode.cu:398): the hot path of a call does its size arithmetic here instead of
+    through three more library calls; tests/test_abi.py holds the two against each other."""
+    return max(16, _pow2ceil(K * _pow2ceil(HQ // HKV)))
+
+
+class _on_device:
+    """`with torch.cuda.device(d)` only when d is not already the current device (the context manager costs a call several
+    microseconds; a serving loop is on its device already)."""
+
+    def __init__(self, device):
+        self.ctx = None if device.index is None or device.index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None:
+            self.ctx.__exit__(*a)
+
+
 def _check(err, what):
     if err != 0:
         name = {1: "cudaErrorInvalidValue (shape not served / bad argument)"}.get(err, f"cudaError {err}")
@@ -151,7 +177,8 @@ class _Ext:
                 raise RuntimeError(f"scale tensors hold {ks.shape[-1]} / {vs.shape[-1]} bytes per row, fmt={int(fmt)} needs {per_row}")
         p = _params(q, kc, ks, vc, vs, bt, sl, nsplit, sm_scale, variant, mb, fmt, k_ts, v_ts)
         L = lib()
-        n_mo, n_ml = int(L.uqb_mo_elems(ctypes.byref(p))), int(L.uqb_ml_elems(ctypes.byref(p)))
+        n_ml = p.B * p.HKV * p.nsplit * _block_m(p.K, p.HQ, p.HKV)
+        n_mo = n_ml * p.D
         if mo is None:
             mo = torch.empty(n_mo, dtype=torch.float32, device=q.device)
         if ml is None:
@@ -161,9 +188,10 @@ class _Ext:
         if mo.numel() < n_mo or ml.numel() < n_ml:
             raise RuntimeError("scratch too small")
         p.mo, p.ml, p.out = mo.data_ptr(), ml.data_ptr(), out.data_ptr()
-        with torch.cuda.device(q.device):
+        with _on_device(q.device):
             err = L.uqb_decode_launch(ctypes.byref(p), int(nwarps), int(stages), _stream(q))
-        _check(err, "uq_decode_launch")
+        if err:
+            _check(err, "uq_decode_launch")
         return out
 
 
@@ -204,17 +232,18 @@ def uq_decode_cuda(q, kc, ks, vc, vs, block_table, seq_lens, *, fused=True, nspl
     sm_scale = sm_scale if sm_scale is not None else D ** -0.5
     if seq_lens.dtype != torch.int32:
         seq_lens = seq_lens.to(torch.int32)
-    block_table = block_table.to(torch.int32)
-    q = q.contiguous()
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if not q.is_contiguous():
+        q = q.contiguous()
     if nsplit is None:
         nsplit = auto_nsplit(B, HKV, block_table.shape[1], _sm_count(q.device), K, HQ // HKV)
     e = ext()
     mo = ml = None
     if workspace is not None:   # caller-owned fp32 scratch, nothing is allocated inside
-        nm = e.workspace_floats(B, K, HQ, HKV, D, nsplit)
-        BM = e.block_m(K, HQ, HKV)
-        mo = workspace[: nm - B * HKV * nsplit * BM].view(-1)
-        ml = workspace[nm - B * HKV * nsplit * BM: nm]
+        n_ml = B * HKV * int(nsplit) * _block_m(K, HQ, HKV)
+        mo = workspace[: n_ml * D]
+        ml = workspace[n_ml * D: n_ml * (D + 1)]
     if fused or K == 1:
         return e.decode(q, kc, ks, vc, vs, block_table, seq_lens, nsplit, nwarps, stages, variant, mb, sm_scale, mo, ml, out, fmt, k_ts, v_ts)
     qs = q.reshape(B * K, 1, HQ, D)

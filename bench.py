@@ -91,6 +91,11 @@ def peaks():
         return 6650.0, "fallback"
 
 
+# DRAM traffic of one launch of the attention kernel from the ncu capture summarised in the named file (dram__bytes_read.sum +
+# dram__bytes_write.sum of a half-size headline call, whose algorithmic bytes are given beside it); None = no capture on record
+TRAFFIC_PROFILE = {"source": "profiles/uq_verify_tc_kernel_ctx16384_K8_ncu_full.md", "dram_bytes": 147.1e6 + 17.4e6, "algorithmic_bytes": 142606336}
+
+
 def kv_bytes(cfg, seq_lens):
     return int(sum(int(n) for n in seq_lens) * cfg["HKV"] * 2 * (cfg["D"] // 2 + scale_bytes(cfg)))
 
@@ -292,6 +297,95 @@ def run_reference_arm(args, cfg):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
+Q_SEED = 4242   # the queries of a context split are the same on every rank
+
+
+class Run:
+    """This rank's share of one configuration: the seeded case, caller-owned scratch and output, and the step function."""
+
+    def __init__(self, cfg, K, rank, world, dev, exchange="peer", copies=None, group=None):
+        import torch
+        from all_quant_b200 import uq_cuda
+        self.cfg, self.K, self.rank, self.world, self.dev = cfg, K, rank, world, dev
+        self.plan = shard_plan(cfg, rank, world)
+        self.mode, hkv, hq = self.plan["mode"], self.plan["hkv"], self.plan["hq"]
+        self.layers, self.fmt = cfg["layers"], cfg.get("fmt", 0)
+        # one cache per layer; a single-layer configuration alternates two copies so that no call finds its cache in L2
+        self.case = build_case(cfg, self.plan, K, 1001 + rank, dev, copies=copies or (self.layers if self.layers > 1 else 2),
+                               q_seed=Q_SEED if cfg["shard"] == "context" else None)
+        c = self.case
+        self.q, self.bt, self.sl, self.po, self.caches = c["q"], c["bt"], c["sl"], c["po"], c["caches"]
+        B, D = cfg["B"], cfg["D"]
+        self.nsplit = uq_cuda.auto_nsplit(B, hkv, self.bt.shape[1], uq_cuda._sm_count(dev), K, hq // hkv)
+        self.ws = torch.empty(uq_cuda.workspace_floats(B, K, hq, hkv, D, self.nsplit), dtype=torch.float32, device=dev)
+        self.out = torch.empty_like(self.q)
+        self.by_local = local_kv_bytes(cfg, self.plan)                                         # one layer, this rank
+        self.by_step = kv_bytes(cfg, self.plan["lens"]) * self.layers * (world if self.mode == "replicas" else 1)   # one step, all ranks
+        self.cache_bytes = sum(t.numel() for t in self.caches[0])
+        self.exchange = exchange if self.mode == "context" else None
+        self.cs = uq_cuda.ContextSplit(B * K * hq, D, group=group) if self.exchange == "peer" else None
+        self.uq = uq_cuda
+
+    def step(self, i, q=None, bt=None, sl=None, out=None, fused=True):
+        uq, c, cfg = self.uq, self.case, self.cfg
+        q = self.q if q is None else q
+        bt = self.bt if bt is None else bt
+        sl = self.sl if sl is None else sl
+        out = self.out if out is None else out
+        o = None
+        for layer in range(self.layers):
+            kc, ks, vc, vs = self.caches[(i * self.layers + layer) % len(self.caches)]
+            if cfg["append"] and c["new_k"] is not None:
+                uq.append_kv(kc, ks, vc, vs, c["new_k"], c["new_v"], c["new_slots"])
+            if self.exchange == "peer":
+                o = self.cs.run(q, kc, ks, vc, vs, bt, sl, self.po, out=out, nsplit=self.nsplit)
+            elif self.exchange == "nccl":
+                o = uq.uq_decode_context_split(q, kc, ks, vc, vs, bt, sl, self.po, nsplit=self.nsplit)
+            elif fused:
+                o = uq.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, nsplit=self.nsplit, workspace=self.ws, out=out, fmt=self.fmt,
+                                      k_ts=c["k_ts"], v_ts=c["v_ts"])
+            else:   # the reference's no-sharing mode: K single-query problems, the cache read K times (it allocates its own scratch)
+                o = uq.uq_decode_cuda(q, kc, ks, vc, vs, bt, sl, fused=False, fmt=self.fmt, k_ts=c["k_ts"], v_ts=c["v_ts"])
+        return o
+
+    def close(self):
+        if self.cs is not None:
+            self.cs.close()
+
+
+def parity_of(run, got):
+    """Sequence 0 of this rank's output against the CPU oracle on the cache bytes the kernel read (rank 0 calls this).
+    Head-partitioned and replicated runs: this rank's own heads.  Context split: the other ranks' shards are rebuilt here from
+    their seeds and sequence 0's pages put in logical order, so the merged output is checked against the whole context."""
+    import torch
+    from oracle import uq_oracle as O
+    O.set_threads(0)
+    cfg, K = run.cfg, run.K
+    nv = (run.case["k_ts"], run.case["v_ts"]) if run.fmt == 1 else None
+    if run.mode == "context" and run.world > 1:
+        PAGE = cfg["PAGE"]
+        parts = []
+        for r in range(run.world):
+            pl = shard_plan(cfg, r, run.world)
+            cr = run.case if r == run.rank else build_case(cfg, pl, K, 1001 + r, run.dev, copies=1, q_seed=Q_SEED)
+            npg = int(-(-int(pl["local"][0]) // PAGE))
+            idx = cr["bt"][0, :npg].long()
+            parts.append(tuple(t[idx].cpu().numpy() for t in cr["caches"][0]))
+            del cr
+        kc, ks, vc, vs = (np.concatenate([p[i] for p in parts]) for i in range(4))
+        bt = np.arange(kc.shape[0], dtype=np.int32)[None]
+        q = run.q.view(torch.int16).cpu().numpy().view(np.uint16)[:1]
+        ref = O.reference(q, kc, ks, vc, vs, bt, run.plan["lens"][:1].astype(np.int32))
+        what = f"sequence 0 (whole context, {run.world} shards reassembled on rank 0) vs CPU oracle"
+    else:
+        q, kc, ks, vc, vs, bt, sl = case_to_numpy(run.case)
+        ref = O.reference_nvfp4(q[:1], kc, ks, vc, vs, bt[:1], sl[:1], *nv) if nv else O.reference(q[:1], kc, ks, vc, vs, bt[:1], sl[:1])
+        what = "sequence 0 vs CPU oracle" + (f" (rank 0's {run.plan['hkv']} kv heads)" if run.world > 1 else "")
+    d = np.abs(got[:1] - ref)
+    return {"max_abs_err": float(d.max()), "mean_abs_err": float(d.mean()), "max_abs_ref": float(np.abs(ref).max()),
+            "ok": bool(d.max() <= 1e-2 * np.abs(ref).max() and d.mean() <= 1e-3), "checked": what}
+
+
 def run_ours(args, cfg):
     import torch
     import torch.distributed as dist
@@ -311,34 +405,8 @@ def run_ours(args, cfg):
         json_fd = os.dup(1)
         os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
-    K = args.kq
-    B, HQ, HKV, D, PAGE, layers = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE", "layers"))
-    plan = shard_plan(cfg, rank, world)
-    mode, hkv, hq = plan["mode"], plan["hkv"], plan["hq"]
-    # one cache per layer; a single-layer configuration alternates two copies so that no call finds its cache in L2
-    case = build_case(cfg, plan, K, 1001 + rank, dev, copies=layers if layers > 1 else 2)
-    q, bt, sl, po, caches = case["q"], case["bt"], case["sl"], case["po"], case["caches"]
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    nsplit = uq_cuda.auto_nsplit(B, hkv, bt.shape[1], sms, K, hq // hkv)
-    ws = torch.empty(uq_cuda.workspace_floats(B, K, hq, hkv, D, nsplit), dtype=torch.float32, device=dev)
-    out = torch.empty_like(q)
-    by_local = local_kv_bytes(cfg, plan)                       # one layer, this rank
-    by_step = kv_bytes(cfg, plan["lens"]) * layers * (world if mode == "replicas" else 1)   # one step, all ranks
-    cache_bytes = sum(t.numel() for t in caches[0])
     lib = uq_cuda.lib()
-    fmt = cfg.get("fmt", 0)
-
-    def step(i, qq=q, btt=bt, sll=sl, oo=out):
-        o = None
-        for layer in range(layers):
-            kc, ks, vc, vs = caches[(i * layers + layer) % len(caches)]
-            if cfg["append"] and case["new_k"] is not None:
-                uq_cuda.append_kv(kc, ks, vc, vs, case["new_k"], case["new_v"], case["new_slots"])
-            if mode == "context":
-                o = uq_cuda.uq_decode_context_split(qq, kc, ks, vc, vs, btt, sll, po, nsplit=nsplit)
-            else:
-                o = uq_cuda.uq_decode_cuda(qq, kc, ks, vc, vs, btt, sll, nsplit=nsplit, workspace=ws, out=oo, fmt=fmt, k_ts=case["k_ts"], v_ts=case["v_ts"])
-        return o
+    peak, peak_kind = peaks()
 
     def barrier():
         if world > 1:
@@ -351,6 +419,38 @@ def run_ours(args, cfg):
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    def time_steps(fn, steps, warm=3):
+        """ms per step of fn(i): `warm` untimed, then exactly `steps` between two events, barrier + synchronize on both sides, max over ranks."""
+        for i in range(warm):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    def time_kernel(fn, n):
+        """ms of the attention kernel alone: events recorded by the library around that kernel (of a step's last layer)."""
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for i, (a, b) in enumerate(pairs):
+            a.record()
+            b.record()      # a torch event gets its handle at its first record
+            lib.uqb_debug_events(a.cuda_event, b.cuda_event)
+            fn(i)
+        lib.uqb_debug_events(None, None)
+        barrier()
+        return max_over_ranks(float(np.mean([a.elapsed_time(b) for a, b in pairs])))
+
+    K = args.kq
+    B, HQ, HKV, D, PAGE, layers = (cfg[k] for k in ("B", "HQ", "HKV", "D", "PAGE", "layers"))
+    run = Run(cfg, K, rank, world, dev, exchange=args.exchange)
+    mode, hkv, hq = run.mode, run.plan["hkv"], run.plan["hq"]
+    q, bt, sl, caches, case, fmt, nsplit = run.q, run.bt, run.sl, run.caches, run.case, run.fmt, run.nsplit
+    step = run.step
 
     for i in range(max(3, args.warmup)):
         step(i)
@@ -367,17 +467,8 @@ def run_ours(args, cfg):
         barrier()
         ms_total = e0.elapsed_time(e1)
         launches = uq_cuda.launch_count() - n0
-        # ---- dominant kernel alone: events recorded by the library around the verify kernel (of the step's last layer)
-        nk = min(args.steps, 50)
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
-        for i, (a, b) in enumerate(pairs):
-            a.record()
-            b.record()      # a torch event gets its handle at its first record
-            lib.uqb_debug_events(a.cuda_event, b.cuda_event)
-            step(i)
-        lib.uqb_debug_events(None, None)
-        barrier()
-        kern_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
+        # ---- dominant kernel alone
+        kern_ms = time_kernel(step, min(args.steps, 50))
         # ---- the same steps replayed from a CUDA graph (the call allocates nothing and reads nothing back, so a caller can
         # capture it once warmed): len(caches) steps per graph, so the alternation of the cache copies is kept
         graph_ms = None
@@ -424,7 +515,7 @@ def run_ours(args, cfg):
             if hnew is not None:
                 case["new_k"].copy_(hnew[0], non_blocking=True)
                 case["new_v"].copy_(hnew[1], non_blocking=True)
-            hout.copy_(step(i, dq, dbt, dsl, out), non_blocking=True)
+            hout.copy_(step(i, dq, dbt, dsl, run.out), non_blocking=True)
 
         for i in range(3):
             e2e_step(i)
@@ -482,24 +573,21 @@ def run_ours(args, cfg):
     ms_step = max_over_ranks(ms_total / args.steps)
     e2e_step_ms = max_over_ranks(e2e_ms / args.steps)
     e2e_serial_step_ms = max_over_ranks(e2e_serial_ms / args.steps)
-    kern_ms = max_over_ranks(kern_ms)
     status = uq_cuda.last_status()
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    peak, peak_kind = peaks()
+    by_local, by_step, cache_bytes = run.by_local, run.by_step, run.cache_bytes
     value = by_step / (ms_step * 1e-3) / 1e12
     achieved = by_local / (kern_ms * 1e-3) / 1e9
     sharding = {"single": "single GPU", "replicas": "every rank runs the whole call on kv heads of its own, no collective",
                 "heads": f"kv heads divided across ranks ({hkv} per rank), no collective",
-                "context": "context pages divided across ranks; partials all-gathered over NCCL and merged by the log-sum-exp kernel inside the step"}[mode]
-    # DRAM bytes per launch of the attention kernel from the one ncu capture of it (dram__bytes_read.sum 147.1 MB +
-    # dram__bytes_write.sum 17.4 MB at B=8, context 16384, K=8, UltraQuant cache: 1.154 x that call's algorithmic
-    # bytes), scaled by the bytes of this call; only for the captured kernel and shape family, else null
-    traffic = None
-    if args.config == 1 and fmt == 0 and K == 8 and world == 1:
-        traffic = int(round(by_local * (147.1e6 + 17.4e6) / 142606336.0))
+                "context": "context pages divided across ranks; " + ("every rank's combine kernel stores its packed partial into all ranks' exchange buffers over NVLink "
+                           "(plain peer stores, a flag behind them) and the merge kernel waits for the flags: no collective call" if run.exchange == "peer" else
+                           "partials all-gathered over NCCL and merged by the log-sum-exp kernel") + ", inside the step"}[mode]
+    # DRAM bytes per launch of the attention kernel: from the ncu capture named in `traffic_source`, taken on a half-size case
+    # (the capture-size rule) and scaled by the bytes of this call; given only for the captured kernel and shape family
+    traffic, traffic_source = None, None
+    if args.config == 1 and fmt == 0 and K == 8 and world == 1 and TRAFFIC_PROFILE:
+        traffic = int(round(by_local * TRAFFIC_PROFILE["dram_bytes"] / TRAFFIC_PROFILE["algorithmic_bytes"]))
+        traffic_source = dict(TRAFFIC_PROFILE, kind="scaled_from_profile")
     l2 = (f"{len(caches)} cache copies alternate; each {cache_bytes / 1e6:.0f} MB copy exceeds the 126 MB L2" if cache_bytes > 126e6 else
           f"{len(caches)} caches of {cache_bytes / 1e6:.0f} MB are read in turn ({len(caches) * cache_bytes / 1e6:.0f} MB between two reads of the same bytes; L2 is 126 MB)")
     line = {"metric": "kv_read_throughput", "value": value, "unit": "TB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -508,26 +596,103 @@ def run_ours(args, cfg):
             "config": {"workload": cfg["name"] + f" K={K}", "kq": K, "nsplit": nsplit, "layers": layers, "l2": l2, "sharding": sharding,
                        "kernel_path": {1: "cuda-core", 2: "tcgen05"}.get(uq_cuda.last_path(), "?")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                         "peak_kind": peak_kind, "kernel_us": kern_ms * 1e3, "algorithmic_bytes": by_local},
+                         "traffic_source": traffic_source, "peak_kind": peak_kind, "kernel_us": kern_ms * 1e3, "algorithmic_bytes": by_local},
             "e2e": {"value": by_step / (e2e_step_ms * 1e-3) / 1e12, "unit": "TB/s", "us_per_layer_call": e2e_step_ms * 1e3 / layers,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(hout.numel() * 2),
                     "how": "two buffer sets; the input copy of the next step and the output copy of the previous one run on streams of their own beside the kernels",
                     "serial_us_per_layer_call": e2e_serial_step_ms * 1e3 / layers},
             "graph_replay_ms_per_step": graph_ms, "gpu_launches": int(launches), "tokens_verified_per_s": B * K * (world if mode == "replicas" else 1) / (ms_step * 1e-3),
             "clocks": clk.summary(), "device_status": list(status)}
-    # ---- CPU baseline beside it (N = 1 only), and a parity check of sequence 0 for free
+    # ---- parity of sequence 0 against the CPU oracle (rank 0, every world size), and the CPU baseline beside it at N = 1
+    got = step(0).float().cpu().numpy()
+    if rank == 0:
+        line["parity"] = parity_of(run, got)
     if world == 1 and not args.no_cpu:
-        t_seq, ref0, cores = cpu_sample(case_to_numpy(case), steps=2, warmup=1, nvfp4=(case["k_ts"], case["v_ts"]) if fmt == 1 else None)
-        scale = float(plan["lens"].sum()) / float(plan["lens"][0]) * layers
+        t_seq, _, cores = cpu_sample(case_to_numpy(case), steps=2, warmup=1, nvfp4=(case["k_ts"], case["v_ts"]) if fmt == 1 else None)
+        scale = float(run.plan["lens"].sum()) / float(run.plan["lens"][0]) * layers
         t_step = t_seq * scale
         line["cpu_baseline"] = {"value": by_step / t_step / 1e12, "unit": "TB/s", "cores": cores, "kind": "port", "us_per_layer_call": t_step * 1e6 / layers,
-                                "sample": f"sequence 0 ({int(plan['lens'][0])} tokens) of {B}, all kv heads, one layer of {layers}, K={K}, 2 timed runs; "
+                                "sample": f"sequence 0 ({int(run.plan['lens'][0])} tokens) of {B}, all kv heads, one layer of {layers}, K={K}, 2 timed runs; "
                                           f"scaled x{scale:.2f} (tokens x layers) to a step"}
-        got = step(0).float().cpu().numpy()[:1]
-        d = np.abs(got - ref0)
-        line["parity"] = {"max_abs_err": float(d.max()), "mean_abs_err": float(d.mean()), "max_abs_ref": float(np.abs(ref0).max()),
-                          "ok": bool(d.max() <= 1e-2 * np.abs(ref0).max() and d.mean() <= 1e-3), "checked": "sequence 0 vs CPU oracle"}
-    os.write(json_fd, (json.dumps(line) + "\n").encode())
+
+    # ---- the whole metric of the headline configuration in the same line (N = 1): every K, the no-sharing mode, and the
+    # reference's own CUDA kernels timed on this GPU
+    if world == 1 and args.config == 1 and fmt == 0 and not args.ctx and not args.lean:
+        per_k, no_sharing, gpu_ref = {}, {}, {}
+        n_k = 20
+        for k in (1, 2, 4, 8):
+            rk = run if k == K else Run(cfg, k, rank, world, dev)
+            t = time_steps(rk.step, n_k)
+            tk = time_kernel(rk.step, n_k)
+            per_k[str(k)] = {"us_per_layer_call": t * 1e3, "kernel_us": tk * 1e3, "frac": rk.by_local / (tk * 1e-3) / 1e9 / peak}
+            # the no-sharing mode (reference cuda/uq_cuda.py:58-61): K single-query problems over B*K pseudo-sequences
+            no_sharing[str(k)] = {"us_per_layer_call": (t if k == 1 else time_steps(lambda i: rk.step(i, fused=False), n_k)) * 1e3}
+            no_sharing[str(k)]["fused_gain"] = no_sharing[str(k)]["us_per_layer_call"] / (t * 1e3)
+            try:
+                sys.path.insert(0, os.path.join(ROOT, "baseline"))
+                import ref_gpu
+                gpu_ref[str(k)] = ref_gpu.sweep(rk.case, k, HQ, HKV, D, PAGE, mode="short", iters=30, check_against=rk.step(0))
+            except Exception as e:
+                gpu_ref[str(k)] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+            if "us" in gpu_ref[str(k)]:
+                gpu_ref[str(k)]["speedup_of_this_library"] = gpu_ref[str(k)]["us"] / (t * 1e3)
+            if rk is not run:
+                del rk
+                torch.cuda.empty_cache()
+        line["per_k"] = per_k
+        line["k8_over_k1"] = per_k["8"]["us_per_layer_call"] / per_k["1"]["us_per_layer_call"]
+        line["no_sharing"] = no_sharing
+        line["gpu_reference"] = {"what": "the reference's own CUDA kernels (its variants 1 and 2, mma.sync) built for sm_100a from its checkout and tuned "
+                                         "with its own protocol on this GPU, same inputs; its tcgen05 variant is not run (its waits end in a trap)",
+                                 "per_k": gpu_ref}
+
+    # ---- the two sharded configurations in the scaling run's line (N > 1, default configuration): heads divided (config 3)
+    # and the context split (config 4), each with its parity and the same configuration timed on rank 0's GPU alone
+    if world > 1 and args.config == 1 and fmt == 0 and not args.lean:
+        run.close()
+        del run, case, caches
+        torch.cuda.empty_cache()
+        sharded = {}
+        for cid in (3, 4):
+            c2 = dict(CONFIGS[cid])
+            r2 = Run(c2, K, rank, world, dev)
+            t = time_steps(r2.step, 30)
+            tk = time_kernel(r2.step, 20)
+            ent = {"workload": c2["name"] + f" K={K}", "us_per_call": t * 1e3, "kernel_us": tk * 1e3, "tokens_verified_per_s": c2["B"] * K / (t * 1e-3),
+                   "per_gpu_frac": r2.by_local / (tk * 1e-3) / 1e9 / peak, "per_gpu_algorithmic_bytes": r2.by_local,
+                   "sharding": "context pages divided; partials exchanged by peer stores, merged after a flag wait" if r2.mode == "context" else f"{r2.plan['hkv']} kv heads per rank, no collective"}
+            got2 = r2.step(0).float().cpu().numpy()
+            if rank == 0:
+                ent["parity"] = parity_of(r2, got2)
+            if r2.mode == "context":   # the NCCL all-gather variant of the same step, for comparison
+                r2.close()
+                r3 = Run(c2, K, rank, world, dev, exchange="nccl")
+                ent["us_per_call_nccl_allgather"] = time_steps(r3.step, 30) * 1e3
+                del r3
+            r2.close()
+            del r2
+            torch.cuda.empty_cache()
+            barrier()
+            if rank == 0:   # the whole configuration on one GPU, in the same run
+                r1 = Run(c2, K, 0, 1, dev)
+                for i in range(3):
+                    r1.step(i)
+                torch.cuda.synchronize()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for i in range(20):
+                    r1.step(i)
+                a1.record()
+                torch.cuda.synchronize()
+                ent["single_gpu_us_per_call"] = a0.elapsed_time(a1) / 20 * 1e3
+                ent["speedup_over_single_gpu"] = ent["single_gpu_us_per_call"] / ent["us_per_call"]
+                del r1
+                torch.cuda.empty_cache()
+            barrier()
+            sharded[f"cfg{cid}"] = ent
+        line["sharded"] = sharded
+    if rank == 0:
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 
@@ -543,6 +708,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (profiler captures use a shorter one; the JSON says so)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--fmt", type=int, default=0, choices=[0, 1], help="cache format: 0 UltraQuant (the headline), 1 NVFP4 (configurations 1 and 3)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="context split (configuration 4, N > 1): partials by peer stores and flags, or by an NCCL all-gather")
+    ap.add_argument("--lean", action="store_true", help="only the headline measurement: no per-K table, no reference-GPU sweep, no sharded configurations")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.steps <= 0:

@@ -44,6 +44,7 @@ def test_params_struct_is_136_bytes():
 def test_block_m_and_scratch_sizes(K, HQ, HKV, bm):
     e = uq_cuda.ext()
     assert e.block_m(K, HQ, HKV) == bm     # max(16, pow2(K * pow2(G))), reference cuda/uq_decode.cu:398
+    assert uq_cuda._block_m(K, HQ, HKV) == bm   # the Python twin the call path uses
     B, D, ns = 8, 128, 9
     assert e.workspace_floats(B, K, HQ, HKV, D, ns) == B * HKV * ns * bm * (D + 1)
     assert e.has_sm90() == 0
