@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libuq_b200.so")
-SOURCES = ["uq_api.cu", "uq_append.cu", "uq_verify_fma.cu", "uq_verify_tc.cu", "uq_combine.cu"]
+SOURCES = ["uq_api.cu", "uq_append.cu", "uq_verify_fma.cu", "uq_verify_tc.cu", "uq_combine.cu", "uq_layout.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
          "-I", os.path.join(ROOT, "include"), "-I", CSRC] + os.environ.get("UQ_NVCC_EXTRA", "").split()

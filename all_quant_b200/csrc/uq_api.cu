@@ -40,6 +40,7 @@ int uq_verify_tc_splits(const UQParams&, const UQLaunch&);
 cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, const UQPeerPush*, cudaStream_t);
 cudaError_t uq_merge_wait_dispatch(const void*, int, size_t, unsigned int, size_t, int, void*, unsigned long long, unsigned int*, cudaStream_t);
 cudaError_t uq_merge_dispatch(const float*, const float*, int, size_t, int, void*, cudaStream_t);
+cudaError_t uq_layout_dispatch(int, uint8_t*, uint8_t*, uint8_t*, uint8_t*, uint8_t*, long long, int, int, int, int, int, cudaStream_t);
 cudaError_t uq_merge_packed_dispatch(const float*, int, size_t, int, void*, cudaStream_t);
 
 namespace {
@@ -281,6 +282,21 @@ int uqb_tree_decode_launch(const UQParams* p, const int32_t* tree_mask, void* st
 int uqb_merge_launch(const float* o_parts, const float* lse2_parts, int R, size_t rows, int D, void* out_bf16, void* stream) {
   cudaError_t e = uq_merge_dispatch(o_parts, lse2_parts, R, rows, D, out_bf16, reinterpret_cast<cudaStream_t>(stream));
   if (e == cudaSuccess && rows > 0) g_launches += 1;
+  return (int)e;
+}
+
+int uqb_cache_to_upstream_launch(const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs, uint8_t* slots_out, long long pages, int HKV,
+                                 int PAGE, int D, int slot_bytes, int flags, void* stream) {
+  cudaError_t e = uq_layout_dispatch(0, const_cast<uint8_t*>(kc), const_cast<uint8_t*>(ks), const_cast<uint8_t*>(vc), const_cast<uint8_t*>(vs), slots_out, pages, HKV,
+                                     PAGE, D, slot_bytes, flags, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && pages > 0) g_launches += 1;
+  return (int)e;
+}
+
+int uqb_cache_from_upstream_launch(const uint8_t* slots_in, uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, long long pages, int HKV, int PAGE, int D,
+                                   int slot_bytes, void* stream) {
+  cudaError_t e = uq_layout_dispatch(1, kc, ks, vc, vs, const_cast<uint8_t*>(slots_in), pages, HKV, PAGE, D, slot_bytes, 0, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess && pages > 0) g_launches += 1;
   return (int)e;
 }
 

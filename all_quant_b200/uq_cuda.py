@@ -36,7 +36,8 @@ EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes",
            "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_append_nvfp4_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes",
-           "uqb_peer_bytes", "uqb_peer_alloc", "uqb_peer_open", "uqb_peer_close", "uqb_peer_free", "uqb_decode_partial_push_launch", "uqb_merge_wait_launch")
+           "uqb_peer_bytes", "uqb_peer_alloc", "uqb_peer_open", "uqb_peer_close", "uqb_peer_free", "uqb_decode_partial_push_launch", "uqb_merge_wait_launch",
+           "uqb_cache_to_upstream_launch", "uqb_cache_from_upstream_launch")
 
 
 def lib():
@@ -76,6 +77,8 @@ def lib():
         L.uqb_peer_free.argtypes = [vp]
         L.uqb_decode_partial_push_launch.argtypes = [pp, vp, ctypes.POINTER(vp), i, i, ctypes.c_uint, vp]
         L.uqb_merge_wait_launch.argtypes = [vp, i, ctypes.c_uint, sz, i, vp, ctypes.c_ulonglong, vp]
+        L.uqb_cache_to_upstream_launch.argtypes = [vp, vp, vp, vp, vp, ctypes.c_longlong, i, i, i, i, i, vp]
+        L.uqb_cache_from_upstream_launch.argtypes = [vp, vp, vp, vp, vp, ctypes.c_longlong, i, i, i, i, vp]
         _lib = L
     return _lib
 
@@ -411,6 +414,44 @@ def append_kv_nvfp4(kc, ks, vc, vs, key, value, slot_mapping, k_ts, v_ts):
         err = lib().uqb_append_nvfp4_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
                                             slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], float(k_ts), float(v_ts), _stream(key))
     _check(err, "uq_append_nvfp4_launch")
+
+
+def to_upstream_layout(kc, ks, vc, vs, slot_bytes=None, *, canon_negzero=False, zero_sentinel=False, out=None):
+    """This library's cache arrays -> the upstream engines' slot array uint8 [pages, PAGE, Hkv, slot_bytes] (slot = K codes, K
+    scale bytes, V codes, V scale bytes, zero padding; reference cuda/UPSTREAM_COMPAT.md:81-88).  canon_negzero writes a
+    minus-zero code as zero, zero_sentinel gives an all-zero group the scale byte 0: with both, a 'paper'-rule cache carries the
+    upstream encoder's bytes (reference cuda/UPSTREAM_COMPAT.md:93-95)."""
+    _need_cuda(kc, ks, vc, vs)
+    pages, HKV, PAGE, half = kc.shape
+    D = 2 * half
+    slot_bytes = D + 2 * (D // 32) if slot_bytes is None else int(slot_bytes)
+    for t in (kc, ks, vc, vs):
+        if not t.is_contiguous() or t.dtype != torch.uint8:
+            raise RuntimeError("cache tensors must be contiguous uint8")
+    if out is None:
+        out = torch.empty(pages, PAGE, HKV, slot_bytes, dtype=torch.uint8, device=kc.device)
+    with _on_device(kc.device):
+        err = lib().uqb_cache_to_upstream_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), out.data_ptr(), pages, HKV, PAGE, D, slot_bytes,
+                                                 (1 if canon_negzero else 0) | (2 if zero_sentinel else 0), _stream(kc))
+    _check(err, "uq_cache_to_upstream_launch")
+    return out
+
+
+def from_upstream_layout(cache, D):
+    """The upstream engines' slot array uint8 [pages, PAGE, Hkv, slot >= D + D/16] -> (kc, ks, vc, vs) of this library
+    (reference cuda/UPSTREAM_COMPAT.md:81-85); the page table and seq_lens carry over unchanged."""
+    _need_cuda(cache)
+    if cache.dtype != torch.uint8 or not cache.is_contiguous() or cache.dim() != 4:
+        raise RuntimeError("cache must be contiguous uint8 [pages, PAGE, Hkv, slot]")
+    pages, PAGE, HKV, slot = cache.shape
+    G = D // 32
+    kc = torch.empty(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device=cache.device)
+    ks = torch.empty(pages, HKV, PAGE, G, dtype=torch.uint8, device=cache.device)
+    vc, vs = torch.empty_like(kc), torch.empty_like(ks)
+    with _on_device(cache.device):
+        err = lib().uqb_cache_from_upstream_launch(cache.data_ptr(), kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), pages, HKV, PAGE, D, slot, _stream(cache))
+    _check(err, "uq_cache_from_upstream_launch")
+    return kc, ks, vc, vs
 
 
 def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):

@@ -49,6 +49,41 @@ def build(force=False):
     return LIB
 
 
+HARNESS = os.path.join(OUT_DIR, "test_vectors_b200")
+EXT = os.path.join(OUT_DIR, "uq_cuda_ext.so")
+
+
+def build_boundary(force=False):
+    """The reference's own callers built against THIS library, unchanged and straight from the checkout: its vector harness
+    (cuda/test_vectors.cu:21-72) as a binary and its torch binding (cuda/uq_ext.cpp:6-37) as the module `uq_cuda_ext`, both
+    compiled with -I include (this repository's uq_decode.h) and linked with libuq_b200.so.  Outputs go to baseline/_ref/.
+    Returns the paths that exist afterwards."""
+    ref = os.environ.get("UQ_REFERENCE", "/root/reference")
+    inc, libdir = os.path.join(ROOT, "include"), os.path.join(ROOT, "all_quant_b200")
+    src_h, src_e = os.path.join(ref, "cuda", "test_vectors.cu"), os.path.join(ref, "cuda", "uq_ext.cpp")
+    os.makedirs(OUT_DIR, exist_ok=True)
+    rpath = "-Wl,-rpath,$ORIGIN/../../all_quant_b200"
+    if os.path.exists(src_h) and (force or not os.path.exists(HARNESS)):
+        cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-I", inc, src_h, "-L", libdir, "-luq_b200",
+               "-Xlinker", "-rpath=$ORIGIN/../../all_quant_b200", "-o", HARNESS]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("building the reference's vector harness against libuq_b200.so failed:\n" + r.stderr[-2000:])
+    if os.path.exists(src_e) and (force or not os.path.exists(EXT)):
+        import sysconfig
+        import torch
+        from torch.utils import cpp_extension as ce
+        incs = [inc, sysconfig.get_paths()["include"], "/usr/local/cuda/include"] + ce.include_paths()
+        tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=uq_cuda_ext", "-DTORCH_API_INCLUDE_EXTENSION_H",
+               f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"] + [f"-I{i}" for i in incs] + [src_e, "-L", libdir, "-luq_b200", rpath,
+               "-L", tlib, "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda", "-L", "/usr/local/cuda/lib64", "-lcudart", "-o", EXT]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("building the reference's torch binding against libuq_b200.so failed:\n" + r.stderr[-2000:])
+    return [f for f in (HARNESS, EXT) if os.path.exists(f)]
+
+
 def candidates(K, G, mode):
     """The reference's tuning grid (cuda/bench_cuda.py:62-69), or a short list around the configurations that won it."""
     bm = max(16, 1 << (K * G - 1).bit_length())
@@ -137,6 +172,7 @@ def main():
     a = ap.parse_args()
     if a.build:
         print(build(force=True))
+        print(build_boundary(force=True))
     if a.sweep:
         import torch
         import bench

@@ -72,6 +72,21 @@ int uqb_append_nvfp4_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, 
  * out may be x: the reference's fwht (uqmt/quant.py:84-98, rotate_kq :105-107) for the queries. */
 int uqb_fwht_launch(const void* x, void* out, long long rows, int D, int dtype, void* stream);
 
+/* ---- the upstream engines' slot layout ------------------------------------------------------------ */
+
+/* Byte permute between this library's four cache arrays and the upstream engines' single array of per-token slots
+ * [pages, PAGE, HKV, slot_bytes], slot = K codes (D/2) | K scale bytes (D/32) | V codes | V scale bytes | padding: the
+ * converter of the reference's compatibility notes (reference cuda/UPSTREAM_COMPAT.md:81-88, torch permute / cat there).
+ * slot_bytes >= D + D/16.  flags of the outbound direction: 1 = a minus-zero code nibble (0x8) is written as 0x0
+ * (canon_negzero, reference cuda/compat/paper_rule_cpu_check.py:14-18), 2 = a 32-channel group whose codes are all zero
+ * gets the scale byte 0, upstream's mark for an all-zero group (reference cuda/UPSTREAM_COMPAT.md:93-95); with both, a
+ * cache written by uqb_append_ex_launch with the 'paper' rule holds the upstream encoder's bytes.  The inbound direction
+ * is the permute alone (both layouts decode as code * 2^(byte - 127)).  kc / vc 16-byte aligned. */
+int uqb_cache_to_upstream_launch(const uint8_t* kc, const uint8_t* ks, const uint8_t* vc, const uint8_t* vs, uint8_t* slots_out,
+                                 long long pages, int HKV, int PAGE, int D, int slot_bytes, int flags, void* stream);
+int uqb_cache_from_upstream_launch(const uint8_t* slots_in, uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs,
+                                   long long pages, int HKV, int PAGE, int D, int slot_bytes, void* stream);
+
 /* ---- context-split partials and their merge (no counterpart in the reference) ---------------- */
 
 /* Attention of all queries over ONE SHARD of each sequence's context.  The cache and block_table in

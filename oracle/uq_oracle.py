@@ -234,3 +234,39 @@ def merge(o, lse):
     out = np.empty(o.shape[1:], np.float32)
     lib().uqo_merge(_p(o), _p(lse), R, rows, D, _p(out))
     return out
+
+
+# ---- the upstream engines' slot layout (reference cuda/UPSTREAM_COMPAT.md:81-95, cuda/compat/paper_rule_cpu_check.py:14-18)
+def canon_negzero(packed):
+    """A code nibble 0x8 (minus zero) becomes 0x0 (the upstream encoder never writes minus zero)."""
+    packed = np.asarray(packed, np.uint8)
+    lo, hi = packed & 0xF, packed >> 4
+    lo = np.where(lo == 8, 0, lo)
+    hi = np.where(hi == 8, 0, hi)
+    return (lo | (hi << 4)).astype(np.uint8)
+
+
+def zero_sentinel(packed, scales):
+    """Scale byte 0 for every 32-channel group (16 code bytes) whose codes are all zero in magnitude: the upstream encoder's
+    mark of an all-zero group."""
+    packed, scales = np.asarray(packed, np.uint8), np.asarray(scales, np.uint8).copy()
+    groups = packed.reshape(packed.shape[:-1] + (scales.shape[-1], 16))
+    scales[((groups & 0x77) == 0).all(-1)] = 0
+    return scales
+
+
+def to_upstream(kc, ks, vc, vs, slot_bytes=None, canon=False, sentinel=False):
+    """[pages,Hkv,PAGE,*] x 4 -> uint8 [pages,PAGE,Hkv,slot]: K codes, K scale bytes, V codes, V scale bytes, zero padding."""
+    if sentinel:
+        ks, vs = zero_sentinel(kc, ks), zero_sentinel(vc, vs)
+    if canon:
+        kc, vc = canon_negzero(kc), canon_negzero(vc)
+    aos = np.concatenate([kc, ks, vc, vs], -1).transpose(0, 2, 1, 3)
+    pad = 0 if slot_bytes is None else slot_bytes - aos.shape[-1]
+    return np.ascontiguousarray(np.pad(aos, [(0, 0)] * 3 + [(0, pad)]))
+
+
+def from_upstream(cache, D):
+    G = D // 32
+    c = np.asarray(cache, np.uint8).transpose(0, 2, 1, 3)
+    return tuple(np.ascontiguousarray(a) for a in (c[..., :D // 2], c[..., D // 2:D // 2 + G], c[..., D // 2 + G:D + G], c[..., D + G:D + 2 * G]))

@@ -32,7 +32,7 @@ def load_cases(pattern="*"):
     out = []
     for f in sorted(glob.glob(os.path.join(GOLDEN, pattern + ".npz"))):
         base = os.path.basename(f)[:-4]
-        if base in ("gen_codec", "gen_append", "tree_cases", "gen_rotate", "gen_nvfp4_quant"):
+        if base in ("gen_codec", "gen_append", "tree_cases", "gen_rotate", "gen_nvfp4_quant", "gen_upstream"):
             continue
         if base.startswith("nvfp4_") and not pattern.startswith("nvfp4_"):
             continue

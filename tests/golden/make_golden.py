@@ -10,6 +10,10 @@ Two kinds of fixture:
        uqmt.vllm_adapter.append_kv, uqmt.tree.tree_reference), for the cases the frozen vectors do not cover.
   nvfp4_cuda_<set>.npz   the reference's frozen NVFP4 vectors (cuda/vectors_nvfp4), repacked the same way; the scale
       arrays are e4m3fn bytes [pages,Hkv,PAGE,D/16] and `ts` holds the per-tensor scales (k_ts, v_ts).
+gen_upstream.npz holds the upstream engines' slot layout (the converter of cuda/UPSTREAM_COMPAT.md:81-88 applied with torch) and the
+bytes of the upstream encoder vendored by the reference (cuda/compat/upstream/reference.py, run the way
+cuda/compat/paper_rule_cpu_check.py runs it) beside the reference's own 'paper'-rule bytes; `--upstream-only` writes it alone.
+`--sycl-only` repacks the sycl vectors alone.
 `--tree-only` regenerates tree_cases.npz alone, `--nvfp4-only` the nvfp4_cuda_* files alone, `--rotate-only` gen_rotate.npz
 (uqmt.quant.fwht and the 'paper' scale rule of uqmt.quant.quantize) and gen_nvfp4_quant.npz (uqmt.quant.quantize_nvfp4) alone.
 """
@@ -60,7 +64,8 @@ def repack_cuda_vectors(sub="vectors", prefix="ref_cuda_", group=32):
         save(f"{prefix}{name}.npz", **arrs)
 
 
-SYCL_KEEP = ("b2k16_d128_p32", "b3k2_d64_p16", "b4k3_d128_p64_g1", "edge_short_k4", "b1k8_d128_p64")
+SYCL_KEEP = ("b2k16_d128_p32", "b3k2_d64_p16", "b4k3_d128_p64_g1", "edge_short_k4", "b1k8_d128_p64",
+             "b2k1_d128_p64", "b2k4_d128_p64", "rot_h128_b2k4", "paper_rule_b2k4")   # all nine cases of sycl/vectors/manifest.txt
 
 
 def repack_sycl_vectors():
@@ -265,7 +270,64 @@ def gen_tree():
     save("tree_cases.npz", **arrs)
 
 
+def gen_upstream():
+    import importlib.util
+    import re
+    import types
+    from uqmt import quant as UQ
+    here = os.path.join(REF, "cuda", "compat")
+
+    def load(name, path):
+        sp = importlib.util.spec_from_file_location(name, path)
+        m = importlib.util.module_from_spec(sp)
+        sys.modules[name] = m
+        sp.loader.exec_module(m)
+        return m
+    for pkg in ("vllm", "vllm.v1", "vllm.v1.attention", "vllm.v1.attention.ops", "vllm.v1.attention.ops.ultraquant"):
+        sys.modules.setdefault(pkg, types.ModuleType(pkg))
+    load("vllm.v1.attention.ops.ultraquant.format", os.path.join(here, "upstream", "format.py"))
+    UR = load("vllm.v1.attention.ops.ultraquant.reference", os.path.join(here, "upstream", "reference.py"))
+    # canon_negzero as the reference's check script defines it (the script itself writes into the checkout when run)
+    text = open(os.path.join(here, "paper_rule_cpu_check.py")).read()
+    ns = {"torch": torch}
+    exec(re.search(r"def canon_negzero\(pk\):.*?\n    return [^\n]*\n", text, re.S).group(0), ns)
+    canon = ns["canon_negzero"]
+    torch.manual_seed(5)
+    arrs = {}
+    for D in (64, 128, 256):
+        G = D // 32
+        pages, HKV, PAGE = 3, 2, 16
+        n = pages * HKV * PAGE
+        x = torch.randn(2, n, D) * torch.exp(0.7 * torch.randn(2, n, G, 1)).expand(2, n, G, 32).reshape(2, n, D)
+        x = x * (torch.rand(2, n, G, 1) > 0.2).float().expand(2, n, G, 32).reshape(2, n, D)     # a fifth of the groups all zero
+        pk, sc = UQ.quantize(x, "paper", 0.156)
+        if D in (128, 256):   # the vendored encoder asserts these head sizes
+            enc = UR.ultraquant_encode(x.reshape(-1, D), rotate=False)
+            up_codes, up_scales = enc.codes_packed.reshape(pk.shape), enc.scale_bytes.reshape(sc.shape)
+            assert torch.equal(canon(pk), up_codes)
+        else:
+            up_codes, up_scales = canon(pk), None
+        kc, vc = (t.reshape(pages, HKV, PAGE, D // 2).contiguous() for t in pk)
+        ks, vs = (t.reshape(pages, HKV, PAGE, G).contiguous() for t in sc)
+        aos = torch.cat([kc, ks, vc, vs], -1).permute(0, 2, 1, 3).contiguous()          # ours_to_upstream
+        pad = torch.nn.functional.pad(aos, (0, 8))                                      # a slot size 8 bytes above the payload
+        c = aos.permute(0, 2, 1, 3)                                                     # upstream_to_ours
+        back = (c[..., :D // 2], c[..., D // 2:D // 2 + G], c[..., D // 2 + G:D + G], c[..., D + G:D + 2 * G])
+        assert all(torch.equal(a.contiguous(), b) for a, b in zip(back, (kc, ks, vc, vs)))
+        arrs.update({f"d{D}_kc": kc.numpy(), f"d{D}_ks": ks.numpy(), f"d{D}_vc": vc.numpy(), f"d{D}_vs": vs.numpy(), f"d{D}_aos": aos.numpy(),
+                     f"d{D}_aos_pad8": pad.numpy(), f"d{D}_canon_kc": canon(kc).numpy(), f"d{D}_canon_vc": canon(vc).numpy()})
+        if up_scales is not None:
+            arrs.update({f"d{D}_up_ks": up_scales[0].reshape(ks.shape).numpy(), f"d{D}_up_vs": up_scales[1].reshape(vs.shape).numpy()})
+    save("gen_upstream.npz", **arrs)
+
+
 if __name__ == "__main__":
+    if "--upstream-only" in sys.argv:
+        gen_upstream()
+        sys.exit(0)
+    if "--sycl-only" in sys.argv:
+        repack_sycl_vectors()
+        sys.exit(0)
     if "--nvfp4-only" in sys.argv:
         repack_cuda_vectors("vectors_nvfp4", "nvfp4_cuda_", 16)
         sys.exit(0)
