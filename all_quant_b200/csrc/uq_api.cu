@@ -66,6 +66,15 @@ bool sizes_ok(const UQParams& p) {
 
 bool aligned(const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
 
+// UQ_B200_CFG="expire=30" makes the tcgen05 kernel's softmax role withhold one arrival (the query tile of a segment is never
+// announced), so that the issuing thread's bounded wait on barrier 30 runs out after its second and the kernel's give-up path
+// (status record, drain of the copies in flight, common exit) runs on a healthy GPU.  Tests only.
+int forced_expire() {
+  const char* e = std::getenv("UQ_B200_CFG");
+  const char* at = e ? std::strstr(e, "expire=") : nullptr;
+  return at ? std::atoi(at + 7) : 0;
+}
+
 // UQ_B200_CFG="path=fma" or "path=tc" forces a kernel (a forced tc on an unserved shape is invalid value).
 int forced_path() {
   const char* e = std::getenv("UQ_B200_CFG");
@@ -128,6 +137,7 @@ cudaError_t run(const UQParams& p, const int32_t* pos_offset, float* o_part, flo
   x.k_first = 0;
   x.k_total = p.K;
   x.len_cut = 0;
+  x.expire_id = forced_expire();
   x.status = status_ptr();
   if (!x.status) {
     int dev = -1;

@@ -27,6 +27,8 @@ struct UQLaunch {
   // (A tree-masked call is chunked with len_cut = 0: bit t of tree_mask[b, k_first + j] decides about each of the k_total drafts.)
   int k_first, k_total, len_cut;
   unsigned int* status;       // this device's status record (4 words), see uq_report
+  int expire_id;              // 0, or (for the test of the give-up path) 30: the softmax role never announces the query tile of a
+                              // segment, so the wait on barrier 30 runs out after its full limit on an otherwise healthy kernel
 };
 
 // ---- where the combine of a context shard sends its packed partial (context split over peer memory) ----------------

@@ -498,7 +498,13 @@ struct Seg {
 // a segment costs (query conversion, first-tile reference, epilogue), so that a CTA whose chunk crosses into a second item
 // gets correspondingly fewer tiles and all CTAs finish together.  Measured from per-CTA exit times: about twelve tiles'
 // time at 64 rows, eight below.
-__host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? 12 : 8; }
+#ifndef UQ_SEGW64
+#define UQ_SEGW64 12
+#endif
+#ifndef UQ_SEGW
+#define UQ_SEGW 8
+#endif
+__host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? UQ_SEGW64 : UQ_SEGW; }
 
 struct Walker {
   const int* prefix;   // prefix[b] = weighted units of sequences < b (one kv head): tiles + kSegW per non-empty sequence
@@ -590,7 +596,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #ifdef UQ_TC_PROF
     const long long c_start = clock64();
 #endif
-    bool r = mbar_test(b, parity) || mbar_try(b, parity);
+    bool r = mbar_test(b, parity);
+    if (!r) r = mbar_try(b, parity);
     if (!r) r = bounded_wait(b, parity, abort_flag, x.status, id, tile);
 #ifdef UQ_TC_PROF
     if (site) *site += clock64() - c_start;
@@ -713,6 +720,18 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (side & 4) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
           if (side & 8) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
         }
+      }
+    }
+    if (!ok) {
+      // Giving up (a wait ran out somewhere in the CTA): copies this warp requested may still be in flight towards this CTA's
+      // shared memory, which must not be left while they are.  Wait for the full barrier of every stage it armed, for about
+      // 50 microseconds at most per stage (a copy takes one or two; a barrier whose other half was never armed cannot
+      // complete, so the limit also covers the time its bytes need).
+      for (int back = 0; back < kRawStages && back < cnt; back++) {
+        const int c = cnt - 1 - back;
+        const uint32_t fb = bar_raw_full(c % kRawStages), ph = (uint32_t)(c / kRawStages) & 1u;
+        const unsigned long long t0 = now_ns();
+        while (!mbar_test(fb, ph) && now_ns() - t0 < 50000ull) __nanosleep(200);
       }
     }
     UQ_PROF_FLUSH(0, lane == 0)
@@ -1103,7 +1122,9 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       if (st < NT) { mref[mcur * NT + st] = st < rows ? kNegBig : 1.0e30f; }
       if (st == 0) wr[4 + mcur] = 0u;
       fence_async_smem();
-      warp_arrive(bar(bQfull));
+      // (test of the give-up path: with expire_id 30 the query tile is never announced, so the issuing thread's wait for it,
+      // barrier id 30, really runs out after its second; the comparison sits here, once per segment, not in the per-tile waits)
+      if (x.expire_id != 30) warp_arrive(bar(bQfull));
       UQ_TRACE_SEG(3)
       // the first segment of an item marks the slots the item does not use as empty
       if (sg.t0 == 0)

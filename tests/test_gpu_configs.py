@@ -234,3 +234,46 @@ def test_a_rank_that_never_arrives_ends_the_merge_wait_with_a_status():
     finally:
         torch.cuda.synchronize()
         ranks[0].close()
+
+
+@pytest.mark.parametrize("HQ,HKV,K", [(2, 2, 1), (2, 2, 2), (4, 2, 1), (4, 2, 4), (8, 8, 3)])
+def test_few_query_rows_run_on_the_tensor_core_kernel_and_both_kernels_agree(HQ, HKV, K, monkeypatch):
+    """One to eight query rows per (sequence, kv head): measured on a B200 at the headline context the tcgen05 kernel is 3.7 to
+    5 times faster than the CUDA-core kernel even for a single row, so the dispatch sends every served shape there
+    (last_path() == 2); the CUDA-core kernel, forced, gives the same answer."""
+    rng = np.random.default_rng(HQ * 10 + K)
+    D, PAGE = 128, 64
+    sl = np.array([1100, 3, 640], np.int32)
+    kc, ks, vc, vs, bt = make_cache(rng, sl, HKV, D, PAGE)
+    qb = O.bf16_bits(rng.standard_normal((len(sl), K, HQ, D)).astype(np.float32))
+    ref = O.reference(qb, kc, ks, vc, vs, bt, sl)
+    args = (dev(qb.view(np.int16), torch.bfloat16), dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl))
+    out = uq_cuda.uq_decode_cuda(*args)
+    assert uq_cuda.last_path() == 2
+    check_close(out.float().cpu().numpy(), ref, "tcgen05, few rows")
+    monkeypatch.setenv("UQ_B200_CFG", "path=fma")
+    out = uq_cuda.uq_decode_cuda(*args)
+    assert uq_cuda.last_path() == 1 and uq_cuda.last_status() == (0, 0, 0, 0)
+    check_close(out.float().cpu().numpy(), ref, "CUDA cores, few rows")
+
+
+@pytest.mark.parametrize("K,HQ,HKV,D,fmt", [(8, 8, 2, 128, 0), (4, 32, 4, 256, 0), (16, 8, 1, 64, 0), (5, 14, 2, 128, 0)])
+def test_cuda_core_kernel_with_many_rows_and_unaligned_value_arrays(K, HQ, HKV, D, fmt, monkeypatch):
+    """The CUDA-core kernel at 16 to 128 rows (passes of 32 rows, every tile staged once per pass), with the V codes and both
+    scale arrays at odd byte offsets (only q and the K codes have an alignment contract), on a page size that is not a power
+    of two."""
+    rng = np.random.default_rng(K * 7 + D)
+    PAGE = 48
+    sl = np.array([500, 47, 1000], np.int32)
+    kc, ks, vc, vs, bt = make_cache(rng, sl, HKV, D, PAGE)
+    qb = O.bf16_bits(rng.standard_normal((len(sl), K, HQ, D)).astype(np.float32))
+    ref = O.reference(qb, kc, ks, vc, vs, bt, sl)
+
+    def odd(a):   # the same bytes starting one byte into a larger allocation
+        buf = torch.empty(a.size + 1, dtype=torch.uint8, device="cuda")
+        view = buf[1:].view(a.shape)
+        view.copy_(dev(a))
+        return view
+    out = uq_cuda.uq_decode_cuda(dev(qb.view(np.int16), torch.bfloat16), dev(kc), odd(ks), odd(vc), odd(vs), dev(bt), dev(sl))
+    assert uq_cuda.last_path() == 1 and uq_cuda.last_status() == (0, 0, 0, 0)
+    check_close(out.float().cpu().numpy(), ref, "CUDA cores, odd offsets")

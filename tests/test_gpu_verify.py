@@ -246,3 +246,24 @@ def test_context_split_partials_merge_to_the_unsplit_answer(R):
         uq_cuda.uq_decode_partial(q, dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(bt), dev(c.sl), dev(off), into=packed[r])
     out2 = uq_cuda.uq_merge_packed(packed, B * K * HQ, D, torch.empty_like(q))
     assert torch.equal(out2, out)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_unaffected(monkeypatch):
+    """The give-up path of the tcgen05 kernel on a healthy GPU: with UQ_B200_CFG=expire=30 the softmax role never announces a
+    segment's query tile (an arrival that nothing makes), so the issuing thread's wait for it - barrier id 30, bounded at one
+    second like every wait of the kernel - runs out.  The kernel must return (every role drains to the common exit, the copy
+    warps wait for their copies in flight, TMEM goes back), the status record must name a wait that ran out (code 1; the
+    issuing thread's, or the softmax role's own wait for scores that were never computed, ids 62-64, whichever CTA reports
+    first), and the next ordinary calls on the device must be right."""
+    c = [x for x in CASES if x.name == "gen_cfg0_K4"][0]
+    q = dev(c.q.view(np.int16), torch.bfloat16)
+    args = (dev(c.kc), dev(c.ks), dev(c.vc), dev(c.vs), dev(c.bt), dev(c.sl))
+    monkeypatch.setenv("UQ_B200_CFG", "path=tc,expire=30")
+    uq_cuda.uq_decode_cuda(q, *args)          # its output is undefined: only the status counts
+    st = uq_cuda.last_status()
+    assert st[0] == 1 and st[2] in (30, 62, 63, 64), st
+    monkeypatch.delenv("UQ_B200_CFG")
+    for _ in range(2):
+        out = uq_cuda.uq_decode_cuda(q, *args)
+        assert uq_cuda.last_status() == (0, 0, 0, 0) and uq_cuda.last_path() == 2
+        check_close(out.float().cpu().numpy(), c.ref, "call after a wait that ran out")
