@@ -136,8 +136,25 @@ __host__ __device__ constexpr int v_warps(int NT) { return NT < 64 ? 8 : UQ_V64;
 __host__ __device__ constexpr int cta_threads(int NT) { return (4 * softmax_groups(NT) + 8 + v_warps(NT)) * 32; }
 // ring depths; head_dim 256 doubles every tile, so its rings are shallower (512 TMEM columns, 227 KB of shared memory)
 __host__ __device__ constexpr bool block_scaled(int D) { return D == 128; }          // Q.K straight from the e2m1 codes and scale bytes (see Cfg::kBS)
-__host__ __device__ constexpr int raw_stages(int D) { return D == 256 ? 2 : (D == 128 ? UQ_RS128 : 4); }   // raw code/scale tiles in flight (TMA)
-__host__ __device__ constexpr int ring_sb(int D) { return D == 256 ? 2 : (D == 128 ? UQ_SB128 : 3); }      // K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory)
+#ifndef UQ_RS128_16
+#define UQ_RS128_16 4   // raw tiles in flight at head_dim 128 with up to 16 rows
+#endif
+#ifndef UQ_RS128_32
+#define UQ_RS128_32 3   // ... with up to 32 rows (the P^T tiles of fewer rows share buffers: room for more raw stages)
+#endif
+#ifndef UQ_PSHARE
+#define UQ_PSHARE 1     // 1: P^T tiles of 16 / 32 rows sit side by side in one 64-row buffer (four / two ring slots per buffer)
+#endif
+// raw code/scale tiles in flight (TMA)
+__host__ __device__ constexpr int raw_stages(int D, int NT) { return D == 256 ? 2 : (D == 128 ? (NT <= 16 ? UQ_RS128_16 : (NT <= 32 ? UQ_RS128_32 : UQ_RS128)) : 4); }
+#ifndef UQ_SB128_16
+#define UQ_SB128_16 3   // the same ring at head_dim 128 with up to 16 rows
+#endif
+#ifndef UQ_SB128_32
+#define UQ_SB128_32 3   // ... with up to 32 rows
+#endif
+// K operand (TMEM), S^T accumulators (TMEM), P^T tiles (shared memory); at most 4 deep (barrier indices)
+__host__ __device__ constexpr int ring_sb(int D, int NT) { return D == 256 ? 2 : (D == 128 ? (NT <= 16 ? UQ_SB128_16 : (NT <= 32 ? UQ_SB128_32 : UQ_SB128)) : 3); }
 __host__ __device__ constexpr int ring_vb(int D) { return D == 256 ? 1 : 2; }      // decoded V tiles (shared memory)
 constexpr float kRescaleAt = 12.0f;  // a score this far (log2) above the row's reference maximum does not fit the fp16 probability tile
 constexpr int kRedoWords = 32;       // a CTA's first 32 * kRedoWords segments can be marked for the second pass; later ones take the careful path at once
@@ -406,7 +423,8 @@ template <int D, int NT, int FMT = 0>
 struct Cfg {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64 / 128 / 256");
   static_assert(NT == 16 || NT == 32 || NT == 64, "rows padded to 16 / 32 / 64");
-  static constexpr int kRawStages = raw_stages(D), kSB = ring_sb(D), kVB = ring_vb(D);
+  static constexpr int kRawStages = raw_stages(D, NT), kSB = ring_sb(D, NT), kVB = ring_vb(D);
+  static_assert(kSB <= 4, "four barrier indices per ring");
   static constexpr int kCodeRow = D / 2;                 // bytes of codes per key
   static constexpr int kGroups = D / 32;                 // 32-channel groups per key: one UE8M0 scale byte each (FMT 0)
   static constexpr int kScaleB = FMT ? D / 16 : D / 32;  // scale bytes per key (NVFP4: one e4m3fn byte per 16 channels)
@@ -430,13 +448,17 @@ struct Cfg {
   static constexpr int kVTile = kHalves * kVHalf;
   static constexpr int kQHalf = NT * 128;                // fp16 [row][64 channels]
   static constexpr int kQTile = kHalves * kQHalf;
-  static constexpr int kPTile = kKeys * 128;             // fp16 [key][row], rows padded to 64
+  static constexpr int kPTile = kKeys * 128;             // fp16 [key][64 rows]: one 128-byte row per key, 128-byte swizzle
+  // A P^T tile of NT rows fills NT * 2 bytes of every key's row: with fewer than 64 rows, kPPer ring slots sit side by side
+  // in one buffer (slot s = buffer s / kPPer, 16-byte chunks (s % kPPer) * NT / 8 ...), which frees shared memory for raw stages
+  static constexpr int kPPer = UQ_PSHARE ? 64 / NT : 1;
+  static constexpr int kPBufs = (kSB + kPPer - 1) / kPPer;
   static constexpr int kDB = D > 128 ? D / 128 : 1;      // 128-channel blocks of O^T (one accumulator each); head_dim 64 uses the lower half of one
   // shared memory map (offsets from the 1024-aligned base)
   static constexpr int oV = 0;
   static constexpr int oQ = oV + kVB * kVTile;
   static constexpr int oP = oQ + kQTile;
-  static constexpr int oRaw = oP + kSB * kPTile;
+  static constexpr int oRaw = oP + kPBufs * kPTile;
   static constexpr int oBar = oRaw + kRawStages * kRawStage;
   static constexpr int kNumBars = 2 * kRawStages + 24;
   static constexpr int oMisc = oBar + kNumBars * 8;
@@ -468,7 +490,7 @@ struct Cfg {
 };
 
 // barrier indices (after the raw ring's full[0..RS) and empty[0..RS))
-enum { bKfull = 0, bSfull = 3, bPfull = 9, bPdone = 12, bVfull = 15, bVdone = 17, bQfull = 19, bOdone = 20, bEpi = 21, bVote = 22 };
+enum { bKfull = 0, bSfull = 4, bPfull = 8, bPdone = 12, bVfull = 16, bVdone = 18, bQfull = 20, bOdone = 21, bEpi = 22, bVote = 23 };
 
 struct Params {
   UQParams p;
@@ -795,7 +817,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
           UQ_TRACE(7, c)
-          const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)(buf * (C::kPTile >> 4));
+          // (a P^T slot inside a shared buffer starts (slot % kPPer) * NT rows = that many * 2 bytes into every key's row)
+          const uint64_t va = v_desc + (uint64_t)(vb * (C::kVTile >> 4)), pa = p_desc + (uint64_t)((buf / C::kPPer) * (C::kPTile >> 4) + (buf % C::kPPer) * (NT * 2 >> 4));
 #pragma unroll
           for (int db = 0; db < ((UQ_ABL & 1024) ? 0 : C::kDB); db++) {
 #pragma unroll
@@ -1176,10 +1199,11 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
               fma_f32x2(y2, y3, pv[4 * j + 2], pv[4 * j + 3], nck, m.z, m.w);
               pv[4 * j] = fast_exp2(-y0); pv[4 * j + 1] = fast_exp2(-y1); pv[4 * j + 2] = fast_exp2(-y2); pv[4 * j + 3] = fast_exp2(-y3);
             }
-            uint8_t* pt = pk + buf * C::kPTile;
+            uint8_t* pt = pk + (buf / C::kPPer) * C::kPTile;
+            const int pc0 = (buf % C::kPPer) * (NT / 8) + r0 / 8;   // first 16-byte chunk of this thread's rows in the key's row
 #pragma unroll
             for (int c = 0; c < HW / 8; c++)
-              *reinterpret_cast<uint4*>(pt + (((r0 / 8 + c) ^ (kk & 7)) << 4)) =
+              *reinterpret_cast<uint4*>(pt + (((pc0 + c) ^ (kk & 7)) << 4)) =
                   make_uint4(mul_f16x2(pack_f16x2(pv[8 * c], pv[8 * c + 1]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 2], pv[8 * c + 3]), vf),
                              mul_f16x2(pack_f16x2(pv[8 * c + 4], pv[8 * c + 5]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 6], pv[8 * c + 7]), vf));
             if (st == 0) { UQ_TRACE(11, cnt) }
@@ -1218,7 +1242,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (!live) vmask = 0u;
           else if (td >= 0) vmask = draft_rows(x.tree_mask, Kq, sg.b, td, r0, HW, rows, G, j_first);
         }
-        uint8_t* pt = sm + C::oP + buf * C::kPTile + kk * 128;
+        uint8_t* pt = sm + C::oP + (buf / C::kPPer) * C::kPTile + kk * 128;
+        const int pc0 = (buf % C::kPPer) * (NT / 8) + r0 / 8;
         float pv[HW];
         // scores -> probabilities against the references `mrow`, in place, with the masks; returns the largest exponent seen
         // (the form for masked tiles, first tiles and the careful path; the common tile has a leaner one below)
@@ -1239,7 +1264,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           const uint32_t vf = live ? pow2_f16x2(min(vref - rbyte, 16)) : 0u;
 #pragma unroll
           for (int c = 0; c < HW / 8; c++)
-            *reinterpret_cast<uint4*>(pt + (((r0 / 8 + c) ^ (kk & 7)) << 4)) =
+            *reinterpret_cast<uint4*>(pt + (((pc0 + c) ^ (kk & 7)) << 4)) =
                 make_uint4(mul_f16x2(pack_f16x2(pv[8 * c], pv[8 * c + 1]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 2], pv[8 * c + 3]), vf),
                            mul_f16x2(pack_f16x2(pv[8 * c + 4], pv[8 * c + 5]), vf), mul_f16x2(pack_f16x2(pv[8 * c + 6], pv[8 * c + 7]), vf));
         };
