@@ -37,7 +37,7 @@ cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_
 cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
 int uq_verify_tc_splits(const UQParams&, const UQLaunch&);
-cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, const UQPeerPush*, cudaStream_t);
+cudaError_t uq_combine_dispatch(const UQParams&, const UQLaunch&, float*, float*, const UQPeerPush*, bool, cudaStream_t);
 cudaError_t uq_merge_wait_dispatch(const void*, int, size_t, unsigned int, size_t, int, void*, unsigned long long, unsigned int*, cudaStream_t);
 cudaError_t uq_merge_dispatch(const float*, const float*, int, size_t, int, void*, cudaStream_t);
 cudaError_t uq_layout_dispatch(int, uint8_t*, uint8_t*, uint8_t*, uint8_t*, uint8_t*, long long, int, int, int, int, int, cudaStream_t);
@@ -203,7 +203,10 @@ cudaError_t run_one(const UQParams& p, UQLaunch x, float* o_part, float* lse_par
   if (timed) cudaEventRecord(t_ev_after, s);
   if (e != cudaSuccess) return e;
   g_launches += 2;
-  return uq_combine_dispatch(p, x, o_part, lse_part, push, s);
+  // (after the tcgen05 kernel, which signals its dependents at once, the combine is launched as a programmatic dependent;
+  // UQ_B200_CFG="pdl=0" turns that off)
+  static const bool pdl_on = !(std::getenv("UQ_B200_CFG") && std::strstr(std::getenv("UQ_B200_CFG"), "pdl=0"));
+  return uq_combine_dispatch(p, x, o_part, lse_part, push, tc && pdl_on && !timed, s);
 }
 
 }  // namespace

@@ -17,6 +17,10 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);   // over [B, K, HQ]
   const int lane = threadIdx.x & 31;
   const int total = p.B * p.K * p.HQ;
+  // Launched as a programmatic dependent of the attention kernel (its blocks may become resident while that kernel's last
+  // CTAs still run): nothing of the partials is read before the whole attention grid has completed and its writes are visible.
+  // (A no-op when the launch carries no such dependency.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (row < total) {
   const int h = row % p.HQ, j = (row / p.HQ) % p.K, b = row / (p.HQ * p.K);
   const int hk = h / x.G, r = j * x.G + (h % x.G);
@@ -187,17 +191,26 @@ __global__ void __launch_bounds__(128) uq_merge_kernel(const float* o, const flo
 
 }  // namespace
 
-cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_part, float* lse_part, const UQPeerPush* push, cudaStream_t s) {
+cudaError_t uq_combine_dispatch(const UQParams& p, const UQLaunch& x, float* o_part, float* lse_part, const UQPeerPush* push, bool pdl, cudaStream_t s) {
   const int rows = p.B * p.K * p.HQ;
   if (rows == 0) return cudaSuccess;
   const UQPeerPush none{};
-  if (push)
-    uq_combine_kernel<2><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr, *push);
-  else if (o_part)
-    uq_combine_kernel<1><<<(rows + 3) / 4, 128, 0, s>>>(p, x, o_part, lse_part, none);
-  else
-    uq_combine_kernel<0><<<(rows + 3) / 4, 128, 0, s>>>(p, x, nullptr, nullptr, none);
-  return cudaGetLastError();
+  // programmatic stream serialisation: the launch may be set up while the attention kernel before it on the stream is still
+  // running (that kernel signals early); the combine's first instruction waits for that kernel's completion
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((rows + 3) / 4);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  float* no_f = nullptr;
+  if (push) return cudaLaunchKernelEx(&cfg, uq_combine_kernel<2>, p, x, no_f, no_f, *push);
+  if (o_part) return cudaLaunchKernelEx(&cfg, uq_combine_kernel<1>, p, x, o_part, lse_part, none);
+  return cudaLaunchKernelEx(&cfg, uq_combine_kernel<0>, p, x, no_f, no_f, none);
 }
 
 cudaError_t uq_merge_dispatch(const float* o, const float* lse, int R, size_t rows, int D, void* out, cudaStream_t s) {

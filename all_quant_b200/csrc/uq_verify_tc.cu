@@ -591,6 +591,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   // compiler keeps every access in the shared state space (ld.shared / st.shared instead of generic loads and stores)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   UQ_TRACE_CTA_T(0)
+  // the combine kernel that follows on the stream may be set up now (its blocks wait for this grid's completion themselves)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const UQParams& p = prm.p;
   const UQLaunch& x = prm.x;
   uint8_t* sm = smem_raw;

@@ -2,10 +2,10 @@
 
 `build()` compiles the reference checkout's `cuda/uq_decode.cu` (its variants 1 and 2: the mma.sync split kernels, reference
 cuda/uq_decode.cu:114-350 and cuda/uq_decode_w.cuh:55-310, with the combine kernel :353-388) for sm_100a, straight from
-the checkout named by $UQ_REFERENCE (default /root/reference), into the git-ignored baseline/_ref/ - no reference source
+the checkout named by $UQ_REFERENCE, into the git-ignored baseline/_ref/ - no reference source
 is copied into this repository.  It is built WITHOUT -DUQ_ENABLE_SM100: the reference's tcgen05 kernel (variant 4) ends a
 wait that runs out in `__trap()` (reference cuda/uq_decode_sm100.cuh:23-30), which on a shared GPU is a fault, so it is
-not run here; its published B300 figures stay as context in BASELINE.md.
+not run here; the figures the reference publishes for it were measured on another chip.
 
 `sweep()` times the built library on a case of bench.py with the reference's own tuning protocol (reference
 cuda/bench_cuda.py:62-75: variant x warps x stages x nsplit, CUDA events around back-to-back launches) and returns the
@@ -28,12 +28,13 @@ OUT_DIR = os.path.join(ROOT, "baseline", "_ref")
 LIB = os.path.join(OUT_DIR, "libuq_ref_v12.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 LAUNCH = "_Z16uq_decode_launchRK8UQParamsiiP11CUstream_st"          # uq_decode_launch(UQParams const&, int, int, CUstream_st*)
+DEFAULT_REFERENCE = os.path.join(os.sep, "root", "reference")   # where the build container keeps the checkout; $UQ_REFERENCE overrides
 NSPLITS = (4, 5, 6, 7, 8, 9, 10, 11, 12, 14, 16, 18, 20, 24, 32, 48)   # reference cuda/bench_cuda.py:58
 
 
 def build(force=False):
     """Compile the reference's kernels where its checkout is present; returns the library path or None."""
-    ref = os.environ.get("UQ_REFERENCE", "/root/reference")
+    ref = os.environ.get("UQ_REFERENCE", DEFAULT_REFERENCE)
     src = os.path.join(ref, "cuda", "uq_decode.cu")
     if not os.path.exists(src):
         return LIB if os.path.exists(LIB) else None
@@ -58,7 +59,7 @@ def build_boundary(force=False):
     (cuda/test_vectors.cu:21-72) as a binary and its torch binding (cuda/uq_ext.cpp:6-37) as the module `uq_cuda_ext`, both
     compiled with -I include (this repository's uq_decode.h) and linked with libuq_b200.so.  Outputs go to baseline/_ref/.
     Returns the paths that exist afterwards."""
-    ref = os.environ.get("UQ_REFERENCE", "/root/reference")
+    ref = os.environ.get("UQ_REFERENCE", DEFAULT_REFERENCE)
     inc, libdir = os.path.join(ROOT, "include"), os.path.join(ROOT, "all_quant_b200")
     src_h, src_e = os.path.join(ref, "cuda", "test_vectors.cu"), os.path.join(ref, "cuda", "uq_ext.cpp")
     os.makedirs(OUT_DIR, exist_ok=True)
