@@ -83,7 +83,10 @@ __global__ void __launch_bounds__(128) uq_combine_kernel(const UQParams p, const
       }
     }
   }
-  const float inv = (den > 0.f ? 1.f / den : 0.f) * x.out_scale;
+  // A wait of the attention kernel that ran out (status code set, not yet read by the host) leaves partials unwritten: the rows
+  // are then NaN rather than numbers that look like an answer, so that a caller sees the failure without a synchronising read
+  // of the status record.
+  const float inv = x.status[0] != 0u ? __int_as_float(0x7fc00000) : (den > 0.f ? 1.f / den : 0.f) * x.out_scale;
   if (kOut == 1) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {

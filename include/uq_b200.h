@@ -166,9 +166,10 @@ size_t uqb_static_scratch_bytes(void);
  * waiting for and the kernel returns.  Reads (and clears) the current device's record:
  * out4[0] = code (0 = none, 1 = a barrier wait of the attention kernel, 3 = a rank's flag in uqb_merge_wait_launch),
  * out4[1] = block, out4[2] = barrier id (code 3: the rank), out4[3] = tile (code 3: seq).  Synchronises the device.
- * When the code is not zero, the outputs of the calls since the last read are undefined (the kernel that gave up left
- * its results unwritten or partial): a caller that cannot afford that reads the record before it uses them, e.g. once
- * per step behind the step's own synchronisation; the launches themselves still return 0. */
+ * When the code is not zero, the outputs of the calls since the last read are not answers (the kernel that gave up left
+ * its results unwritten or partial): from the moment the code is set until this function has read and cleared it, every
+ * decode call on the device writes NaN rows (bf16 outputs and fp32 partials alike), so the failure shows in the data
+ * without a synchronising read; the launches themselves still return 0. */
 int uqb_last_status(uint32_t out4[4]);
 /* Which kernel the last uqb_decode_* call on this thread chose: 1 = CUDA-core path, 2 = tcgen05 path. */
 int uqb_last_path(void);
