@@ -29,7 +29,6 @@ import argparse
 import json
 import os
 import sys
-import threading
 import time
 
 import numpy as np
@@ -102,55 +101,62 @@ def kv_bytes(cfg, seq_lens):
 
 # ------------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """SM clock and throttle reasons while the timed regions run, sampled by an `nvidia-smi` child process every 20 ms (a
+    sampling thread inside this process would take the interpreter lock from the loop that launches the steps: with 20 timed
+    steps that showed as 7 us per step).  Falls back to "unsampled" when nvidia-smi cannot be started."""
+
+    FIELDS = ("clocks.sm", "clocks.max.sm", "clocks_event_reasons.hw_slowdown", "clocks_event_reasons.hw_thermal_slowdown",
+              "clocks_event_reasons.sw_thermal_slowdown", "clocks_event_reasons.sw_power_cap")
+    NAMES = ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap")
 
     def __init__(self, index):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thr = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        self.index, self.proc, self.lines = str(index), None, []
+        try:   # the device's UUID names it whatever CUDA_VISIBLE_DEVICES does to the numbering
+            import torch
+            self.index = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
         except Exception:
-            self.nv = None
-
-    def _loop(self):
-        nv = self.nv
-        names = {getattr(nv, n): n[len("nvmlClocksEventReason"):] for n in dir(nv) if n.startswith("nvmlClocksEventReason") and isinstance(getattr(nv, n), int)}
-        if not names:
-            names = {getattr(nv, n): n[len("nvmlClocksThrottleReason"):] for n in dir(nv) if n.startswith("nvmlClocksThrottleReason") and isinstance(getattr(nv, n), int)}
-        while not self._stop.is_set():
-            try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
-                try:
-                    bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
-                except Exception:
-                    bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
-                for bit, name in names.items():
-                    if bit and bits & bit and name not in ("None", "All", "GpuIdle"):
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            time.sleep(0.002)
+            pass
 
     def __enter__(self):
-        if self.nv is not None:
-            self._thr = threading.Thread(target=self._loop, daemon=True)
-            self._thr.start()
+        import subprocess
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", "--query-gpu=" + ",".join(self.FIELDS), "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            first = self.proc.stdout.readline()     # the child is up and sampling before anything is timed
+            if first:
+                self.lines.append(first)
+        except Exception:
+            self.proc = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        if self._thr is not None:
-            self._thr.join()
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+                self.lines += out.splitlines()
+            except Exception:
+                self.proc.kill()
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
-        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        mhz, max_mhz, reasons = [], None, set()
+        for ln in self.lines:
+            t = [x.strip() for x in ln.split(",")]
+            if len(t) != len(self.FIELDS):
+                continue
+            try:
+                mhz.append(float(t[0]))
+                max_mhz = int(float(t[1]))
+            except ValueError:
+                continue
+            for name, v in zip(self.NAMES, t[2:]):
+                if v == "Active":
+                    reasons.add(name)
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": max_mhz, "reasons": ["unsampled"]}
+        # the median of the samples taken under load (the block also holds host-side pauses, where the clock may idle down)
+        busy = [m for m in mhz if m >= 0.6 * max(mhz)] or mhz
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max_mhz, "reasons": sorted(reasons), "samples": len(mhz), "how": "nvidia-smi -lms 20"}
 
 
 # ------------------------------------------------------------------------------------------------ data
