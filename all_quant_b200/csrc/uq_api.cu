@@ -4,7 +4,7 @@
 // Dispatch (the reference's is a template tree over variant / BLOCK_M / warps / stages, reference
 // cuda/uq_decode.cu:402-626; this library has two kernels and ignores those hints):
 //   tcgen05 kernel  when head_dim, page size, alignment and row count are ones it serves (uq_verify_tc.cu): every
-//                   power-of-two page from 16 to 1024 tokens, up to 64 rows per launch, 65-128 rows as draft chunks
+//                   page size that is a multiple of 16 from 16 to 1024 tokens, up to 64 rows per launch, 65-128 rows as draft chunks
 //   CUDA-core kernel for everything else (uq_verify_fma.cu)
 // followed by the combine kernel.  Every check happens before the first launch, so
 // cudaErrorInvalidValue means nothing was enqueued (callers of the reference skip on it).

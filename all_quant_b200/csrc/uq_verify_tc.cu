@@ -496,6 +496,7 @@ struct Params {
   UQParams p;
   UQLaunch x;
   int chunk_min;      // lower bound on the chunk (tiles per CTA) that keeps segments per item within ns_eff
+  int unit;           // tokens one copy moves: gcd(PAGE, 128) - a whole page of up to 128 tokens, a 128-token part of a larger power-of-two page, or the largest common part of a page size like 48 or 96 and the 128-key tile
 };
 
 // Position in a ring of N slots: the slot and the phase bit of the current lap, counted up tile by tile (a division and
@@ -706,8 +707,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // what this warp copies of every tile: bit 0 K codes, bit 1 V codes, bit 2 K scales, bit 3 V scales
     const int side = (UQ_PROD2 == 0 ? 15 : (UQ_PROD2 == 1 ? (warp == kWarpProd ? 5 : 10) : (warp == kWarpProd ? 1 : (warp == kWarpProd + 2 ? 2 : 12)))) & ((UQ_ABL & 2048) ? 3 : 15);
     // a copy moves one unit: a whole page of up to 128 tokens, or a 128-token part of a larger page
-    const int unit = min(p.PAGE, kKeys), ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile, units per page
-    const int spp_sh = __ffs(spp) - 1;   // (a power of two: the per-tile arithmetic below is shifts and masks, no division)
+    const int unit = prm.unit, ppt = kKeys / unit, spp = p.PAGE / unit;   // tokens per unit, units per tile (1 .. 8), units per page
+    // (units per page are a power of two for power-of-two pages: shifts and masks then, no division in the per-tile chain)
+    const bool spp_p2 = (spp & (spp - 1)) == 0;
+    const int spp_sh = __ffs(spp) - 1;
     UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)unit * C::kCodeRow, page_bytes_scales = (uint32_t)unit * C::kScaleB;
     while (ok && wk.next(sg)) {
@@ -718,7 +721,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       const int32_t* bt = p.block_table + (size_t)sg.b * p.max_pages;
       // Page ids come 32 units at a time, a block ahead (lane j of `cur` = unit blk0 + j, `nxt` the block after it): the
       // table's latency (an L2 round trip) stays out of the per-tile chain wait -> request.
-      auto load_ids = [&](int ub) -> int { const int uu = ub + lane; return uu < pages_valid ? __ldg(bt + (uu >> spp_sh)) : 0; };
+      auto load_ids = [&](int ub) -> int { const int uu = ub + lane; return uu < pages_valid ? __ldg(bt + (spp_p2 ? uu >> spp_sh : uu / spp)) : 0; };
       int blk0 = sg.t0 * ppt;
       int cur = load_ids(blk0), nxt = load_ids(blk0 + 32);
       for (int t = sg.t0; t < sg.t1; t++, cnt++) {
@@ -736,7 +739,8 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         __syncwarp();
         if (lane < vp) {
           // first cache row of this unit of (page, head); 64-bit: a cache may hold more than 2^31 / PAGE (page, head) slices
-          const long long row0 = ((long long)pid * p.HKV + sg.hk) * p.PAGE + ((t * ppt + lane) & (spp - 1)) * unit;
+          const int in_page = spp_p2 ? (t * ppt + lane) & (spp - 1) : (t * ppt + lane) % spp;   // this unit's place in its page
+          const long long row0 = ((long long)pid * p.HKV + sg.hk) * p.PAGE + in_page * unit;
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
           if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, (int)row0, fb);
@@ -1557,7 +1561,9 @@ cudaError_t launch(const UQParams& p, const UQLaunch& x, cudaStream_t s) {
   const long long max_tiles = ((long long)p.max_pages * p.PAGE + kKeys - 1) / kKeys;
   prm.chunk_min = x.ns_eff >= 2 ? (int)((max_tiles + x.ns_eff - 2) / (x.ns_eff - 1)) : 1;
   CUtensorMap mk, mv;
-  const int box_rows = std::min(p.PAGE, kKeys);   // a copy moves a page of up to 128 tokens, or a 128-token part of a larger one
+  int box_rows = kKeys;   // a copy moves gcd(PAGE, 128) tokens: a page of up to 128 tokens, a 128-token part of a larger one, or their common part
+  while (p.PAGE % box_rows) box_rows >>= 1;
+  prm.unit = box_rows;
   if (!cached_map(&mk, MapKey{p.kc, C::kCodeRow, box_rows, C::kBS ? 1 : 0}) || !cached_map(&mv, MapKey{p.vc, C::kCodeRow, box_rows, 0})) return cudaErrorInvalidValue;
   const int sms = sm_counts[dev].load(std::memory_order_relaxed);
   if (sms <= 0) return cudaErrorInitializationError;
@@ -1593,7 +1599,7 @@ extern "C" int uqb_debug_tc_prof(unsigned long long* out40) {
 bool uq_verify_tc_serves(const UQParams& p, const UQLaunch& x) {
   if (p.fmt != 0 && p.fmt != 1) return false;
   if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
-  if (p.PAGE < 16 || p.PAGE > 1024 || (p.PAGE & (p.PAGE - 1))) return false;   // powers of two: pages that tile, or are tiled by, the 128-key tile
+  if (p.PAGE < 16 || p.PAGE > 1024 || p.PAGE % 16) return false;   // multiples of 16 tokens: copies of gcd(PAGE, 128) >= 16 tokens tile both the page and the 128-key tile
   if (x.rows > 64 || p.B > tc::Cfg<128, 64>::kMaxB) return false;
   if ((reinterpret_cast<uintptr_t>(p.kc) | reinterpret_cast<uintptr_t>(p.vc) | reinterpret_cast<uintptr_t>(p.ks) | reinterpret_cast<uintptr_t>(p.vs)) & 15) return false;
   if (p.fmt == 0 && tc::block_scaled(p.D) && (reinterpret_cast<uintptr_t>(p.kc) & 31)) return false;   // the unpacking tensor map wants 32-byte alignment

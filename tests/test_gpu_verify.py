@@ -132,10 +132,13 @@ def test_more_than_64_query_rows_run_as_draft_chunks_on_the_tensor_core_kernel(K
     check_close(merged.float().cpu().numpy(), ref, f"K={K} partial")
 
 
-@pytest.mark.parametrize("PAGE,D,fmt", [(16, 128, 0), (256, 128, 0), (512, 128, 0), (256, 64, 0), (1024, 256, 0), (256, 128, 1), (48, 128, 0)])
+@pytest.mark.parametrize("PAGE,D,fmt", [(16, 128, 0), (256, 128, 0), (512, 128, 0), (256, 64, 0), (1024, 256, 0), (256, 128, 1), (48, 128, 0),
+                                         (96, 128, 0), (80, 64, 0), (192, 256, 0), (48, 128, 1), (144, 128, 0), (24, 128, 0), (40, 64, 0)])
 def test_page_sizes_from_16_to_1024_tokens(PAGE, D, fmt):
-    """Pages smaller than the 128-key tile are copied whole, larger ones in 128-token parts; a page size that is not a power
-    of two runs on the CUDA-core kernel.  Ragged lengths that end inside a page and inside a part of a page."""
+    """Pages smaller than the 128-key tile are copied whole, larger ones in 128-token parts, and a page size that neither
+    divides 128 nor is a multiple of it (48, 80, 96, 144, 192 ...) in parts of gcd(PAGE, 128) tokens, three to eight copies per
+    stream and tile; only a page size that is not a multiple of 16 runs on the CUDA-core kernel.  Ragged lengths that end
+    inside a page and inside a part of a page."""
     rng = np.random.default_rng(PAGE + D)
     B, K, HQ, HKV = 3, 4, 8, 2
     sl = np.array([2 * PAGE + 77, 130, 3 * PAGE], np.int32)
@@ -157,7 +160,7 @@ def test_page_sizes_from_16_to_1024_tokens(PAGE, D, fmt):
     for nsplit in (None, 3):
         out = uq_cuda.uq_decode_cuda(q, dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl), nsplit=nsplit, **kw)
         assert uq_cuda.last_status() == (0, 0, 0, 0)
-        assert uq_cuda.last_path() == (2 if PAGE & (PAGE - 1) == 0 else 1)
+        assert uq_cuda.last_path() == (2 if PAGE % 16 == 0 else 1)
         mx = np.abs(ref).max()      # random codes and scales give outputs of order ten: the rule is applied to outputs normalised to O(1)
         check_close(out.float().cpu().numpy() / mx, ref / mx, f"PAGE={PAGE} D={D} fmt={fmt} nsplit={nsplit}")
 
