@@ -113,6 +113,9 @@ __device__ unsigned long long g_tc_prof[5][8];
 #ifndef UQ_PROD2
 #define UQ_PROD2 1   // copy warps beside the first: 0 one warp issues everything; 1 K side / V side; 2 K codes / V codes / both scale slices
 #endif
+#ifndef UQ_QKMERGE
+#define UQ_QKMERGE 32   // block-scaled Q.K with up to this many rows: the leading and the remainder tile of Q are ONE B operand of 2 NT rows (half the Q.K instructions; the softmax adds the two halves of S^T); 0 = never
+#endif
 #ifndef UQ_EARLY
 #define UQ_EARLY 1   // 1: the V decode gives its raw stage back once the tile's codes are in registers, not after the decode
 #endif
@@ -485,7 +488,9 @@ struct Cfg {
   static constexpr int cK = 0;                           // kSB x kKCols
   static constexpr int cSFB = kSB * kKCols;              // block-scaled: scale bytes of the two Q tiles, 4 columns each
   static constexpr int cS = kBS ? 32 : kSB * kKCols;     // kSB x NT: fp32 S^T
-  static constexpr int cO = cS + kSB * NT;               // kDB x NT: fp32 O^T
+  static constexpr bool kQM = kBS && NT <= UQ_QKMERGE;   // leading and remainder Q tiles contracted by one instruction: S^T = two halves of NT columns
+  static constexpr int kSCols = kQM ? 2 * NT : NT;       // TMEM columns of one S^T slot
+  static constexpr int cO = cS + kSB * kSCols;           // kDB x NT: fp32 O^T
   static_assert(cO + kDB * NT <= 512, "TMEM budget");
 };
 
@@ -789,7 +794,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           if (!wait(bar(bKfull + buf), (c / kSB) & 1, 24 + buf, c UQ_PROF_SITE(2))) return false;
           tc_fence_after();
           UQ_TRACE(5, c)
-          const uint32_t d = tmem + C::cS + buf * NT, a = tmem + C::cK + buf * C::kKCols;
+          const uint32_t d = tmem + C::cS + buf * C::kSCols, a = tmem + C::cK + buf * C::kKCols;
           if (UQ_ABL & 1024) {
             tc_commit(bar(bSfull + buf));
             if (C::kBS) tc_commit(bar_raw_empty(c % kRawStages));
@@ -799,8 +804,14 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             const uint64_t a_desc = smem_desc(sm_a + C::oRaw + stage * C::kRawStage, 16, 1024);
 #pragma unroll
             for (int kb = 0; kb < D / 32; kb++) {
-              mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)(kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB, kb ? 1u : 0u);
-              mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)((C::kQHalf >> 4) + kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB + 4, 1u);
+              if constexpr (C::kQM) {
+                // one instruction over both Q tiles (rows 0 .. NT-1 the leading tile, NT .. 2 NT-1 the remainder: they are
+                // contiguous in shared memory and their scale bytes are rows 0 .. 2 NT-1 of one scale operand)
+                mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)(kb * 2), instr_desc_bs(128, 2 * NT, 5, 0, kb, kb), a, tmem + C::cSFB, kb ? 1u : 0u);
+              } else {
+                mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)(kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB, kb ? 1u : 0u);
+                mma_bs(d, a_desc + (uint64_t)(kb * 2), q_desc + (uint64_t)((C::kQHalf >> 4) + kb * 2), instr_desc_bs(128, NT, 5, 0, kb, kb), a, tmem + C::cSFB + 4, 1u);
+              }
             }
             tc_commit(bar(bSfull + buf));
             tc_commit(bar_raw_empty(stage));   // the K codes of the stage have been read
@@ -1024,6 +1035,20 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       }
       tc_wait_ld();
     };
+    // S^T of this thread's rows: with the merged Q.K the sum of the slot's two halves
+    auto load_s = [&](uint32_t addr, float* dst) {
+      if constexpr (C::kQM) {
+        float lo[HW];
+        if constexpr (HW == 8) { tmem_ld8(addr, reinterpret_cast<uint32_t*>(dst)); tmem_ld8(addr + NT, reinterpret_cast<uint32_t*>(lo)); }
+        else {
+#pragma unroll
+          for (int c = 0; c < HW / 16; c++) { tmem_ld16(addr + c * 16, reinterpret_cast<uint32_t*>(dst) + c * 16); tmem_ld16(addr + NT + c * 16, reinterpret_cast<uint32_t*>(lo) + c * 16); }
+        }
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < HW; i += 2) add_f32x2(dst[i], dst[i + 1], lo[i], lo[i + 1]);
+      } else load_scores(addr, dst);
+    };
     auto store_cols = [&](uint32_t addr, const float* src) {
       if constexpr (HW == 8) tmem_st8(addr, reinterpret_cast<const uint32_t*>(src));
       else {
@@ -1104,11 +1129,16 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const int row = 32 * j + lane;
-            h4[j] = row < NT ? sw[row] : 0x7F7F7F7Fu;
-            l4[j] = row < NT ? sw[NT + row] : 0x7F7F7F7Fu;
+            if constexpr (C::kQM) {   // one scale operand of 2 NT rows: the leading tile's rows, then the remainder's
+              h4[j] = row < 2 * NT ? sw[row] : 0x7F7F7F7Fu;
+              l4[j] = 0x7F7F7F7Fu;
+            } else {
+              h4[j] = row < NT ? sw[row] : 0x7F7F7F7Fu;
+              l4[j] = row < NT ? sw[NT + row] : 0x7F7F7F7Fu;
+            }
           }
           tmem_st4(lane_addr + C::cSFB, h4);
-          tmem_st4(lane_addr + C::cSFB + 4, l4);
+          if (!C::kQM) tmem_st4(lane_addr + C::cSFB + 4, l4);
           tc_wait_st();
         }
         tc_fence_before();
@@ -1192,7 +1222,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
             tc_fence_after();
             if (st == 0) { UQ_TRACE(9, cnt) }
             float pv[HW];
-            load_scores(lane_addr + C::cS + buf * NT + r0, pv);
+            load_s(lane_addr + C::cS + buf * C::kSCols + r0, pv);
             const uint32_t rf = oref[(cnt & 7) * kKeys];
             const float nck = C::kBS ? -csc0 : -(csc0 * uq_scale_f32(rf & 0xFFu));
             const uint32_t vf = pow2_f16x2(min((int)(rf >> 8) - rbyte, 16));
@@ -1231,7 +1261,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         tc_fence_after();
         if (st == 0) { UQ_TRACE(9, cnt) }
         UQ_PROF_TA
-        const uint32_t s_addr = lane_addr + C::cS + buf * NT + r0;
+        const uint32_t s_addr = lane_addr + C::cS + buf * C::kSCols + r0;
         // this key: reference scale bytes, position, visibility
         const uint32_t rf = reinterpret_cast<const uint16_t*>(sm + C::oRef)[(cnt & 7) * kKeys + kk];
         const int vref = (int)(rf >> 8);
@@ -1277,7 +1307,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         // scores of a masked tile: what a row does not see becomes -inf here, once (scale factors are positive, so it stays
         // -inf; a dead key's score may be anything, NaN included)
         auto load_masked = [&]() {
-          load_scores(s_addr, pv);
+          load_s(s_addr, pv);
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < HW; i++) pv[i] = ((vmask >> i) & 1u) ? pv[i] : -INFINITY;
