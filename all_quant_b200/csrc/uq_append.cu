@@ -63,7 +63,7 @@ UQ_DEV void load4<__half>(const __half* p, bool vec, float* out) {
   } else { for (int i = 0; i < 4; i++) out[i] = __half2float(p[i]); }
 }
 
-constexpr int kRotateK = 1, kPaperRule = 2;
+constexpr int kRotateK = 1, kPaperRule = 2, kRouteBulk = 4, kRouteRows = 8;
 
 // Orthonormal Walsh-Hadamard transform of one row of D = 64 / 128 / 256 values held by a warp: lane l owns channels
 // 128 s + 4 l .. + 3 of slab s (lanes 16.. hold zeros at D = 64).  Stage h pairs (i, i + h) -> (a + b, a - b), h ascending.
@@ -185,6 +185,163 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The bulk form of the same encoder, for calls that write many tokens at once (a prompt's keys and values: hundreds of
+// megabytes in, a quarter of that out).  The kernel above spends a warp's whole life on one 8-byte load per lane, which
+// is right for a decode step (launch latency) and a tenth of the memory bandwidth for a prompt.  Here:
+//   * a lane owns 8 consecutive channels (16 bytes of a 16-bit input, 32 of fp32) of kBulkPieces pieces, a warp-wide
+//     load is one contiguous 512-byte (1 KiB) run of the input, and all of a thread's loads are issued before the first
+//     is used: 2 to 4 KiB in flight per warp;
+//   * a 32-channel group is four lanes: the group maximum takes two shuffles, and the four lanes share the work on the
+//     scale exponents of their four pieces (lane q computes the exponent of piece q, a shuffle hands it round);
+//   * the codes come from the hardware conversion (cvt.rn.satfinite.e2m1x2.f32, two values per instruction) instead of
+//     seven comparisons per value.  That conversion rounds a value half way between two code points to the even code,
+//     the reference takes the smaller magnitude (first index of the minimum distance); the two differ at |y| = 0.75,
+//     1.75 and 3.5 only.  A 16-bit input has at most 11 significant bits and y = x / 2^e keeps them, so multiplying by
+//     the fp32 value just below 2^-e moves an exact half-way value one fp32 step down (where it rounds as the reference
+//     does) and moves no other value across or onto a boundary; an fp32 input takes 2^-e itself and the three half-way
+//     values are corrected by comparison.  The conversion keeps the sign of a negative value that rounds to zero, as
+//     the reference does (sign bit = y < 0); adding +0 turns y = -0 (an input -0, or an underflow) into +0 first.
+// Same bytes as the kernel above on every input (the tests run both on the same rows).  Not served here: rotated keys
+// (that transform wants a warp per row), inputs not aligned to 16 bytes, more than 2^31 pieces.
+constexpr int kBulkPieces = 4;
+constexpr long long kBulkMinRows = 4096;   // rows x streams from which a call goes to the bulk kernel
+
+template <typename T>
+UQ_DEV void load8(const T* p, float* x);
+template <>
+UQ_DEV void load8<float>(const float* p, float* x) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <>
+UQ_DEV void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
+  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) { x[2 * i] = __uint_as_float(w[i] << 16); x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <>
+UQ_DEV void load8<__half>(const __half* p, float* x) {
+  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i])); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
+
+// eight fp32 values -> eight e2m1 codes, value i in bits 4 i .. 4 i + 3 (round to nearest, half way to the even code, +-6 at most)
+UQ_DEV uint32_t cvt_e2m1x8(const float* y) {
+  uint32_t w;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(w)
+      : "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]), "f"(y[7]));
+  return w;
+}
+
+// n / d for n < 2^32 with m = floor(2^32 / d) (d >= 2; d = 1 takes m = 2^32 - 1): the estimate is short by one at most
+UQ_DEV uint32_t div_magic(uint32_t n, uint32_t d, uint32_t m, uint32_t& rem) {
+  uint32_t q = __umulhi(n, m);
+  uint32_t r = n - q * d;
+  if (r >= d) { q++; r -= d; }
+  rem = r;
+  return q;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
+                                                             uint8_t* __restrict__ vs, const T* __restrict__ key, const T* __restrict__ value,
+                                                             const int64_t* __restrict__ slots, uint32_t np, int HKV, uint32_t hkv_magic, int D,
+                                                             int PAGE, int page_shift, int paper, float c) {
+  constexpr bool kExactTies = sizeof(T) == 4;   // fp32 inputs can sit anywhere: half-way values are corrected by comparison
+  const int stream = blockIdx.y;
+  const T* __restrict__ src = stream ? value : key;
+  uint8_t* __restrict__ codes = stream ? vc : kc;
+  uint8_t* __restrict__ scales = stream ? vs : ks;
+  const int lane = threadIdx.x & 31;
+  const uint32_t p0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * kBulkPieces) + lane;   // this lane's first piece (8 channels)
+  const int ppr_shift = D == 64 ? 3 : (D == 128 ? 4 : 5);   // pieces per row = D / 8
+  float x[kBulkPieces][8];
+#pragma unroll
+  for (int j = 0; j < kBulkPieces; j++) {
+    const uint32_t p = p0 + 32u * j;
+    if (p < np) load8<T>(src + (size_t)p * 8, x[j]);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) x[j][i] = 0.f;
+    }
+  }
+  float amax[kBulkPieces];
+#pragma unroll
+  for (int j = 0; j < kBulkPieces; j++) {
+    float a = fmaxf(fmaxf(fmaxf(fabsf(x[j][0]), fabsf(x[j][1])), fmaxf(fabsf(x[j][2]), fabsf(x[j][3]))),
+                    fmaxf(fmaxf(fabsf(x[j][4]), fabsf(x[j][5])), fmaxf(fabsf(x[j][6]), fabsf(x[j][7]))));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    amax[j] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+  }
+  static_assert(kBulkPieces == 4, "the four lanes of a group take one exponent each");
+  const int q = lane & 3;
+  const float am = q == 0 ? amax[0] : (q == 1 ? amax[1] : (q == 2 ? amax[2] : amax[3]));
+  const int e_mine = group_exponent(am, paper != 0, c);
+  int ex[kBulkPieces];
+#pragma unroll
+  for (int j = 0; j < kBulkPieces; j++) ex[j] = __shfl_sync(0xffffffffu, e_mine, (lane & ~3) | j);
+#pragma unroll
+  for (int j = 0; j < kBulkPieces; j++) {
+    const int e = ex[j];
+    const uint32_t p = p0 + 32u * j;
+    if (p >= np) continue;
+    // 2^-e as fp32 (e = 127 gives the denormal 2^-127); a 16-bit input takes the fp32 value just below it
+    const uint32_t inv = (e == 127 ? 0x00400000u : (uint32_t)(127 - e) << 23) - (kExactTies ? 0u : 1u);
+    const float s = __uint_as_float(inv);
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[j][i], s), 0.0f);
+    uint32_t w = cvt_e2m1x8(y);
+    if (kExactTies) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float a = fabsf(y[i]);
+        if (a == 0.75f || a == 1.75f || a == 3.5f) w -= 1u << (4 * i);   // half way and rounded up to the even code: the reference stays below
+      }
+    }
+    const uint32_t row_in = p >> ppr_shift, piece = p & ((1u << ppr_shift) - 1u);
+    uint32_t h;
+    const uint32_t t = div_magic(row_in, (uint32_t)HKV, hkv_magic, h);
+    const int64_t slot = __ldg(slots + t);
+    if (slot < 0) continue;
+    int64_t page, off;
+    if (page_shift >= 0 && slot <= 0x7fffffffll) { page = (uint32_t)slot >> page_shift; off = (uint32_t)slot & ((1u << page_shift) - 1u); }
+    else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
+    else { page = slot / PAGE; off = slot % PAGE; }
+    const size_t row = ((size_t)page * HKV + h) * PAGE + off;
+    *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
+    if (q == 0) scales[row * (D / 32) + (piece >> 2)] = (uint8_t)(e + 127);
+  }
+}
+
+// the bulk kernel serves: no rotation, pointers aligned for the vector loads, piece count within 32 bits
+template <typename T>
+bool bulk_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const T* key, const T* value, const int64_t* slots, int T_tok, int HKV,
+                 int D, int PAGE, int nstream, int flags, float c, cudaStream_t s) {
+  const unsigned long long np = (unsigned long long)T_tok * HKV * (D / 8);
+  const uintptr_t al = 15;
+  if ((flags & kRotateK) || np >= (1ull << 31) || ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & al)) return false;
+  const uint32_t magic = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV);
+  int shift = -1;
+  if ((PAGE & (PAGE - 1)) == 0) { shift = 0; while ((1 << shift) < PAGE) shift++; }
+  const unsigned per_block = 8u * 32u * kBulkPieces;
+  const dim3 grid((unsigned)((np + per_block - 1) / per_block), (unsigned)nstream);
+  uq_append_bulk_kernel<T><<<grid, 256, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
+  return true;
+}
+
 // NVFP4 append (reference uqmt/quant.py:125-136 quantize_nvfp4 with the tensor scale given; the byte view and the paged
 // cache of uqmt/nvfp4.py:200-254): a block is 16 channels = four lanes; its scale is e4m3fn(clamp(amax / 6 / ts, 2^-9, 448))
 // (two fp32 divisions, the hardware's round-to-nearest-even conversion), the codes are the nearest e2m1 values to
@@ -290,7 +447,8 @@ cudaError_t uq_append_nvfp4_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint
   return cudaGetLastError();
 }
 
-// dtype: 0 fp32, 1 bf16, 2 fp16.  value/vc/vs may be null (single-stream form).  flags: 1 rotate the keys, 2 'paper' rule with constant c.
+// dtype: 0 fp32, 1 bf16, 2 fp16.  value/vc/vs may be null (single-stream form).  flags: 1 rotate the keys, 2 'paper' rule with constant c,
+// 4 / 8 take the bulk / the per-row kernel whatever the size of the call (neither: by size).
 cudaError_t uq_append_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                                const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, cudaStream_t s, int flags, float c) {
   if (T == 0) return cudaSuccess;   // nothing to write; empty tensors may come with null pointers
@@ -298,9 +456,23 @@ cudaError_t uq_append_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* v
   const bool two = value != nullptr;
   if (two && (!vc || !vs)) return cudaErrorInvalidValue;
   if (!(D == 64 || D == 128 || D == 256) || PAGE <= 0 || HKV <= 0 || T < 0 || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
-  if ((flags & ~3) || ((flags & 2) && !(c > 0.f))) return cudaErrorInvalidValue;
+  if ((flags & ~15) || (flags & 12) == 12 || ((flags & 2) && !(c > 0.f))) return cudaErrorInvalidValue;
+  const int route = flags & 12;
+  flags &= 3;
   const int nstream = two ? 2 : 1;
   const long long warps = (long long)T * HKV * nstream;
+  // many rows: the bulk kernel (flags & 4 sends the call there whatever its size, flags & 8 keeps it here: the tests
+  // compare the two on the same rows)
+  if (route == kRouteBulk || (route == 0 && warps >= kBulkMinRows)) {
+    bool done = false;
+    switch (dtype) {
+      case 0: done = bulk_launch<float>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, nstream, flags, c, s); break;
+      case 1: done = bulk_launch<__nv_bfloat16>(kc, ks, vc, vs, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, slots, T, HKV, D, PAGE, nstream, flags, c, s); break;
+      default: done = bulk_launch<__half>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, nstream, flags, c, s); break;
+    }
+    if (done) return cudaGetLastError();
+    if (route == kRouteBulk) return cudaErrorInvalidValue;   // asked for by name and not served (rotated keys, alignment, size)
+  }
   const int blocks = (int)((warps + 3) / 4);
   switch (dtype) {
     case 0: uq_append_kernel<float><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, nstream, flags, c); break;

@@ -350,10 +350,15 @@ _DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 PAPER_C = 0.156   # the constant of the 'paper' scale rule (reference uqmt/quant.py:35)
 
 
-def _rule_flags(rule, c, rotate_k=False):
+_KERNEL_FLAG = {None: 0, "bulk": 4, "rows": 8}
+
+
+def _rule_flags(rule, c, rotate_k=False, kernel=None):
     if rule not in ("ceil", "paper"):
         raise ValueError(rule)
-    return (1 if rotate_k else 0) | (2 if rule == "paper" else 0), float(PAPER_C if c is None else c)
+    if kernel not in _KERNEL_FLAG:
+        raise ValueError(f"append kernel {kernel!r}: None (by the size of the call), 'bulk' or 'rows'")
+    return (1 if rotate_k else 0) | (2 if rule == "paper" else 0) | _KERNEL_FLAG[kernel], float(PAPER_C if c is None else c)
 
 
 def fwht(x, out=None):
@@ -373,13 +378,15 @@ def fwht(x, out=None):
     return out
 
 
-def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule="ceil", c=None):
+def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule="ceil", c=None, kernel=None):
     """Quantize new key/value [T,Hkv,D] and write them at flat slots (slot = physical_page * PAGE + offset):
     the cache-append hook of an engine (reference uqmt/vllm_adapter.py:48-59).  One kernel launch for both streams;
     bytes identical to the reference encoder.  Negative slots are skipped.
     rotate_k: the keys go through the orthonormal Hadamard transform first (feed the verify call fwht(q));
-    rule / c: the scale rule of the reference's configurable quantiser (uqmt/quant.py:52-70), 'ceil' or 'paper'."""
-    flags, c = _rule_flags(rule, c, rotate_k)
+    rule / c: the scale rule of the reference's configurable quantiser (uqmt/quant.py:52-70), 'ceil' or 'paper'.
+    kernel: None picks by the size of the call (a prompt's worth of rows goes to the bulk kernel, which runs at memory
+    bandwidth; a decode step to the one-warp-per-row kernel), 'bulk' / 'rows' name one (same bytes)."""
+    flags, c = _rule_flags(rule, c, rotate_k, kernel)
     _need_cuda(kc, ks, vc, vs, key, value, slot_mapping)
     if key.dtype not in _DTYPE or value.dtype != key.dtype:
         raise RuntimeError("key/value must both be fp32, bf16 or fp16")
@@ -454,10 +461,11 @@ def from_upstream_layout(cache, D):
     return kc, ks, vc, vs
 
 
-def quantize_on_write(x, code, scale, slots, rule="ceil", c=None):
+def quantize_on_write(x, code, scale, slots, rule="ceil", c=None, kernel=None):
     """Quantize x [N,Hkv,D] and scatter into `code` [pages,Hkv,PAGE,D/2] / `scale` [pages,Hkv,PAGE,D/32] at flat
-    slots [N] (reference uqmt/quant.py:197-206); rule 'ceil' (the cache's own encoder) or 'paper' with constant c."""
-    flags, c = _rule_flags(rule, c)
+    slots [N] (reference uqmt/quant.py:197-206); rule 'ceil' (the cache's own encoder) or 'paper' with constant c;
+    kernel as in append_kv."""
+    flags, c = _rule_flags(rule, c, kernel=kernel)
     _need_cuda(x, code, scale, slots)
     if x.dtype not in _DTYPE:
         raise RuntimeError("x must be fp32, bf16 or fp16")
