@@ -17,6 +17,8 @@
 //      (reference uqmt/quant.py:52-60, quantize_on_write's rule argument :197-206) instead of ceil(log2(amax / 6)).
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "uq_common.cuh"
 
 namespace {
@@ -265,7 +267,8 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
   uint8_t* __restrict__ codes = stream ? vc : kc;
   uint8_t* __restrict__ scales = stream ? vs : ks;
   const int lane = threadIdx.x & 31;
-  const uint32_t p0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * kBulkPieces) + lane;   // this lane's first piece (8 channels)
+  const uint32_t wp0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * kBulkPieces);   // the warp's first piece (8 channels)
+  const uint32_t p0 = wp0 + lane;                                                                     // this lane's first piece
   const int ppr_shift = D == 64 ? 3 : (D == 128 ? 4 : 5);   // pieces per row = D / 8
   float x[kBulkPieces][8];
 #pragma unroll
@@ -275,6 +278,24 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
     else {
 #pragma unroll
       for (int i = 0; i < 8; i++) x[j][i] = 0.f;
+    }
+  }
+  // Where the rows go: the warp's 32 * kBulkPieces pieces are 4 / 8 / 16 whole rows, lane L looks up row L (token, head,
+  // slot, page) once and a piece fetches its row's answer by shuffle.  ~0 = no row (past the end, or a skipped token).
+  unsigned long long my_row = ~0ull;
+  {
+    const uint32_t r = (wp0 >> ppr_shift) + lane;
+    if (lane < ((32 * kBulkPieces) >> ppr_shift) && r < (np >> ppr_shift)) {
+      uint32_t h;
+      const uint32_t t = div_magic(r, (uint32_t)HKV, hkv_magic, h);
+      const int64_t slot = __ldg(slots + t);
+      if (slot >= 0) {
+        int64_t page, off;
+        if (page_shift >= 0) { page = slot >> page_shift; off = slot & ((1ll << page_shift) - 1); }
+        else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
+        else { page = slot / PAGE; off = slot % PAGE; }
+        my_row = ((unsigned long long)page * HKV + h) * PAGE + off;
+      }
     }
   }
   float amax[kBulkPieces];
@@ -290,19 +311,33 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
   const float am = q == 0 ? amax[0] : (q == 1 ? amax[1] : (q == 2 ? amax[2] : amax[3]));
   const int e_mine = group_exponent(am, paper != 0, c);
   int ex[kBulkPieces];
+  unsigned long long rows[kBulkPieces];
 #pragma unroll
-  for (int j = 0; j < kBulkPieces; j++) ex[j] = __shfl_sync(0xffffffffu, e_mine, (lane & ~3) | j);
+  for (int j = 0; j < kBulkPieces; j++) {
+    ex[j] = __shfl_sync(0xffffffffu, e_mine, (lane & ~3) | j);
+    rows[j] = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
+  }
 #pragma unroll
   for (int j = 0; j < kBulkPieces; j++) {
     const int e = ex[j];
-    const uint32_t p = p0 + 32u * j;
-    if (p >= np) continue;
+    const unsigned long long row = rows[j];
+    if (row == ~0ull) continue;
     // 2^-e as fp32 (e = 127 gives the denormal 2^-127); a 16-bit input takes the fp32 value just below it
     const uint32_t inv = (e == 127 ? 0x00400000u : (uint32_t)(127 - e) << 23) - (kExactTies ? 0u : 1u);
     const float s = __uint_as_float(inv);
     float y[8];
+    // y = -0 must become +0 (the reference's sign bit is y < 0).  x * s + (+0) does that for an input -0 at no cost, but a
+    // negative product too small for fp32 still rounds to -0: possible only when the smallest non-zero magnitude of the
+    // 16-bit input type (2^-133 bf16, 2^-24 fp16) times 2^-e does not exceed 2^-150, i.e. for bf16 groups whose maximum is
+    // beyond 6 * 2^16; those groups, and fp32 inputs, add +0 afterwards
+    constexpr int kTiny = std::is_same<T, __nv_bfloat16>::value ? -133 : -24;
+    if (sizeof(T) != 4 && kTiny - e > -150) {   // (2^-150 itself is half way between 0 and the smallest denormal and rounds to zero)
 #pragma unroll
-    for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[j][i], s), 0.0f);
+      for (int i = 0; i < 8; i++) y[i] = __fmaf_rn(x[j][i], s, 0.0f);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[j][i], s), 0.0f);
+    }
     uint32_t w = cvt_e2m1x8(y);
     if (kExactTies) {
 #pragma unroll
@@ -311,16 +346,7 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
         if (a == 0.75f || a == 1.75f || a == 3.5f) w -= 1u << (4 * i);   // half way and rounded up to the even code: the reference stays below
       }
     }
-    const uint32_t row_in = p >> ppr_shift, piece = p & ((1u << ppr_shift) - 1u);
-    uint32_t h;
-    const uint32_t t = div_magic(row_in, (uint32_t)HKV, hkv_magic, h);
-    const int64_t slot = __ldg(slots + t);
-    if (slot < 0) continue;
-    int64_t page, off;
-    if (page_shift >= 0 && slot <= 0x7fffffffll) { page = (uint32_t)slot >> page_shift; off = (uint32_t)slot & ((1u << page_shift) - 1u); }
-    else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
-    else { page = slot / PAGE; off = slot % PAGE; }
-    const size_t row = ((size_t)page * HKV + h) * PAGE + off;
+    const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
     *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
     if (q == 0) scales[row * (D / 32) + (piece >> 2)] = (uint8_t)(e + 127);
   }

@@ -112,6 +112,24 @@ def test_values_on_and_beside_every_code_boundary(dtype, kernel):
     assert np.array_equal(p.reshape(-1, 16), want_p)
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_negative_values_that_underflow_under_the_scale_take_code_zero(dtype, kernel):
+    """A negative value so far below the group's maximum that x / scale rounds to -0 is not 'y < 0' in the reference: code 0,
+    not the minus-zero code; a negative value that survives the division as a denormal keeps its sign bit."""
+    tiny = np.float32(2.0 ** -133)                    # representable in bf16 and fp32
+    g = np.zeros((4, 32), np.float32)
+    g[0, 0] = 6.0 * 2.0 ** 40; g[0, 1:5] = [-tiny, tiny, -0.0, -tiny * 4]          # y = -2^-173: gone
+    g[1, 0] = 6.0 * 2.0 ** 16; g[1, 1:5] = [-tiny, tiny, -0.0, -tiny * 4]          # y = -2^-149: the smallest denormal survives
+    g[2, 0] = 6.0 * 2.0 ** 17; g[2, 1:5] = [-tiny, tiny, -0.0, -tiny * 4]          # y = -2^-150: half way, rounds to -0
+    g[3, 0] = -6.0 * 2.0 ** 100; g[3, 1:5] = [-tiny, -1e-20, -0.0, 1e-20]
+    want_p, want_s = O.quantize(g, "ceil")
+    p, s = encode_on_gpu(g.reshape(-1, 64), dtype, kernel=kernel)
+    assert np.array_equal(s.reshape(-1), want_s.reshape(-1))
+    assert np.array_equal(p.reshape(-1, 16), want_p)
+    assert want_p[0, 0] >> 4 == 0 and want_p[1, 0] >> 4 == 8      # the oracle itself: gone / kept
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_bulk_kernel_on_every_16_bit_value_up_to_the_group_maximum(dtype):
     """All bit patterns of the input type with |x| <= 6 (and the same a few binades up and down), beside a 6 that fixes the
