@@ -191,11 +191,12 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 // The bulk form of the same encoder, for calls that write many tokens at once (a prompt's keys and values: hundreds of
 // megabytes in, a quarter of that out).  The kernel above spends a warp's whole life on one 8-byte load per lane, which
 // is right for a decode step (launch latency) and a tenth of the memory bandwidth for a prompt.  Here:
-//   * a lane owns 8 consecutive channels (16 bytes of a 16-bit input, 32 of fp32) of kBulkPieces pieces, a warp-wide
-//     load is one contiguous 512-byte (1 KiB) run of the input, and all of a thread's loads are issued before the first
-//     is used: 2 to 4 KiB in flight per warp;
+//   * a lane owns 8 consecutive channels (a piece: 16 bytes of a 16-bit input, 32 of fp32) of 8 (fp32: 4) runs of the
+//     input, a warp-wide load is one contiguous 512-byte (1 KiB) run, and all of a thread's loads are issued before the
+//     first is used: 4 KiB in flight per warp, 128 KiB per SM (with half of that the kernel waits on memory latency);
 //   * a 32-channel group is four lanes: the group maximum takes two shuffles, and the four lanes share the work on the
-//     scale exponents of their four pieces (lane q computes the exponent of piece q, a shuffle hands it round);
+//     scale exponents of their pieces (lane q computes those of pieces q, q + 4; a shuffle hands them round); the
+//     row a piece belongs to (token, head, slot, page) is looked up once per row by one lane and handed round likewise;
 //   * the codes come from the hardware conversion (cvt.rn.satfinite.e2m1x2.f32, two values per instruction) instead of
 //     seven comparisons per value.  That conversion rounds a value half way between two code points to the even code,
 //     the reference takes the smaller magnitude (first index of the minimum distance); the two differ at |y| = 0.75,
@@ -206,30 +207,60 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 //     the reference does (sign bit = y < 0); adding +0 turns y = -0 (an input -0, or an underflow) into +0 first.
 // Same bytes as the kernel above on every input (the tests run both on the same rows).  Not served here: rotated keys
 // (that transform wants a warp per row), inputs not aligned to 16 bytes, more than 2^31 pieces.
-constexpr int kBulkPieces = 4;
 constexpr long long kBulkMinRows = 4096;   // rows x streams from which a call goes to the bulk kernel
 
+// One piece = 8 consecutive channels as loaded (16 bytes of a 16-bit type, two float4 of fp32).  A thread keeps its pieces
+// in this form until it encodes them: 16-bit inputs stay packed (half the registers, so twice the pieces, and with them
+// twice the bytes, in flight per thread), and their maximum is taken on the packed pairs.
 template <typename T>
-UQ_DEV void load8(const T* p, float* x);
+struct Piece {
+  uint4 v;
+  UQ_DEV void load(const T* p) { v = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  UQ_DEV void zero() { v = make_uint4(0u, 0u, 0u, 0u); }
+  UQ_DEV float amax() const;
+  UQ_DEV void values(float* x) const;
+};
 template <>
-UQ_DEV void load8<float>(const float* p, float* x) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+struct Piece<float> {
+  float4 a, b;
+  UQ_DEV void load(const float* p) { a = __ldcs(reinterpret_cast<const float4*>(p)); b = __ldcs(reinterpret_cast<const float4*>(p) + 1); }
+  UQ_DEV void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+  UQ_DEV float amax() const {
+    return fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))), fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+  }
+  UQ_DEV void values(float* x) const { x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w; }
+};
+template <>
+UQ_DEV float Piece<__nv_bfloat16>::amax() const {
+  const uint32_t m0 = v.x & 0x7fff7fffu, m1 = v.y & 0x7fff7fffu, m2 = v.z & 0x7fff7fffu, m3 = v.w & 0x7fff7fffu;
+  const __nv_bfloat162 m = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m0), *reinterpret_cast<const __nv_bfloat162*>(&m1)),
+                                   __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m2), *reinterpret_cast<const __nv_bfloat162*>(&m3)));
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(&m);
+  return fmaxf(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 template <>
-UQ_DEV void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
-  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+UQ_DEV void Piece<__nv_bfloat16>::values(float* x) const {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; i++) { x[2 * i] = __uint_as_float(w[i] << 16); x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
 }
 template <>
-UQ_DEV void load8<__half>(const __half* p, float* x) {
-  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+UQ_DEV float Piece<__half>::amax() const {
+  const uint32_t m0 = v.x & 0x7fff7fffu, m1 = v.y & 0x7fff7fffu, m2 = v.z & 0x7fff7fffu, m3 = v.w & 0x7fff7fffu;
+  const __half2 m = __hmax2(__hmax2(*reinterpret_cast<const __half2*>(&m0), *reinterpret_cast<const __half2*>(&m1)),
+                            __hmax2(*reinterpret_cast<const __half2*>(&m2), *reinterpret_cast<const __half2*>(&m3)));
+  const float2 f = __half22float2(m);
+  return fmaxf(f.x, f.y);
+}
+template <>
+UQ_DEV void Piece<__half>::values(float* x) const {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; i++) { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i])); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
 }
+
+template <typename T>
+__host__ __device__ constexpr int bulk_pieces() { return sizeof(T) == 4 ? 4 : 8; }
 
 // eight fp32 values -> eight e2m1 codes, value i in bits 4 i .. 4 i + 3 (round to nearest, half way to the even code, +-6 at most)
 UQ_DEV uint32_t cvt_e2m1x8(const float* y) {
@@ -262,30 +293,28 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
                                                              const int64_t* __restrict__ slots, uint32_t np, int HKV, uint32_t hkv_magic, int D,
                                                              int PAGE, int page_shift, int paper, float c) {
   constexpr bool kExactTies = sizeof(T) == 4;   // fp32 inputs can sit anywhere: half-way values are corrected by comparison
+  constexpr int NP = bulk_pieces<T>();          // pieces per thread: 128 bytes of input in flight
   const int stream = blockIdx.y;
   const T* __restrict__ src = stream ? value : key;
   uint8_t* __restrict__ codes = stream ? vc : kc;
   uint8_t* __restrict__ scales = stream ? vs : ks;
   const int lane = threadIdx.x & 31;
-  const uint32_t wp0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * kBulkPieces);   // the warp's first piece (8 channels)
-  const uint32_t p0 = wp0 + lane;                                                                     // this lane's first piece
+  const uint32_t wp0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * NP);   // the warp's first piece (8 channels)
+  const uint32_t p0 = wp0 + lane;                                                            // this lane's first piece
   const int ppr_shift = D == 64 ? 3 : (D == 128 ? 4 : 5);   // pieces per row = D / 8
-  float x[kBulkPieces][8];
+  Piece<T> pc[NP];
 #pragma unroll
-  for (int j = 0; j < kBulkPieces; j++) {
+  for (int j = 0; j < NP; j++) {
     const uint32_t p = p0 + 32u * j;
-    if (p < np) load8<T>(src + (size_t)p * 8, x[j]);
-    else {
-#pragma unroll
-      for (int i = 0; i < 8; i++) x[j][i] = 0.f;
-    }
+    if (p < np) pc[j].load(src + (size_t)p * 8);
+    else pc[j].zero();
   }
-  // Where the rows go: the warp's 32 * kBulkPieces pieces are 4 / 8 / 16 whole rows, lane L looks up row L (token, head,
-  // slot, page) once and a piece fetches its row's answer by shuffle.  ~0 = no row (past the end, or a skipped token).
+  // Where the rows go: the warp's 32 * NP pieces are 4 .. 32 whole rows, lane L looks up row L (token, head, slot, page)
+  // once and a piece fetches its row's answer by shuffle.  ~0 = no row (past the end, or a skipped token).
   unsigned long long my_row = ~0ull;
   {
     const uint32_t r = (wp0 >> ppr_shift) + lane;
-    if (lane < ((32 * kBulkPieces) >> ppr_shift) && r < (np >> ppr_shift)) {
+    if (lane < ((32 * NP) >> ppr_shift) && r < (np >> ppr_shift)) {
       uint32_t h;
       const uint32_t t = div_magic(r, (uint32_t)HKV, hkv_magic, h);
       const int64_t slot = __ldg(slots + t);
@@ -298,34 +327,31 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
       }
     }
   }
-  float amax[kBulkPieces];
-#pragma unroll
-  for (int j = 0; j < kBulkPieces; j++) {
-    float a = fmaxf(fmaxf(fmaxf(fabsf(x[j][0]), fabsf(x[j][1])), fmaxf(fabsf(x[j][2]), fabsf(x[j][3]))),
-                    fmaxf(fmaxf(fabsf(x[j][4]), fabsf(x[j][5])), fmaxf(fabsf(x[j][6]), fabsf(x[j][7]))));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-    amax[j] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-  }
-  static_assert(kBulkPieces == 4, "the four lanes of a group take one exponent each");
+  // group maxima (a group = the four lanes of a piece), and the exponents: lane q of a group computes those of pieces
+  // q, q + 4, ...; the encoding loop fetches each piece's by shuffle
   const int q = lane & 3;
-  const float am = q == 0 ? amax[0] : (q == 1 ? amax[1] : (q == 2 ? amax[2] : amax[3]));
-  const int e_mine = group_exponent(am, paper != 0, c);
-  int ex[kBulkPieces];
-  unsigned long long rows[kBulkPieces];
+  int e_mine[NP / 4];
 #pragma unroll
-  for (int j = 0; j < kBulkPieces; j++) {
-    ex[j] = __shfl_sync(0xffffffffu, e_mine, (lane & ~3) | j);
-    rows[j] = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
+  for (int r = 0; r < NP / 4; r++) {
+    float am = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+      float a = pc[4 * r + jj].amax();
+      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+      if (q == jj) am = a;
+    }
+    e_mine[r] = group_exponent(am, paper != 0, c);
   }
 #pragma unroll
-  for (int j = 0; j < kBulkPieces; j++) {
-    const int e = ex[j];
-    const unsigned long long row = rows[j];
-    if (row == ~0ull) continue;
+  for (int j = 0; j < NP; j++) {
+    const int e = __shfl_sync(0xffffffffu, e_mine[j >> 2], (lane & ~3) | (j & 3));
+    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
     // 2^-e as fp32 (e = 127 gives the denormal 2^-127); a 16-bit input takes the fp32 value just below it
     const uint32_t inv = (e == 127 ? 0x00400000u : (uint32_t)(127 - e) << 23) - (kExactTies ? 0u : 1u);
     const float s = __uint_as_float(inv);
-    float y[8];
+    float x[8], y[8];
+    pc[j].values(x);
     // y = -0 must become +0 (the reference's sign bit is y < 0).  x * s + (+0) does that for an input -0 at no cost, but a
     // negative product too small for fp32 still rounds to -0: possible only when the smallest non-zero magnitude of the
     // 16-bit input type (2^-133 bf16, 2^-24 fp16) times 2^-e does not exceed 2^-150, i.e. for bf16 groups whose maximum is
@@ -333,10 +359,10 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
     constexpr int kTiny = std::is_same<T, __nv_bfloat16>::value ? -133 : -24;
     if (sizeof(T) != 4 && kTiny - e > -150) {   // (2^-150 itself is half way between 0 and the smallest denormal and rounds to zero)
 #pragma unroll
-      for (int i = 0; i < 8; i++) y[i] = __fmaf_rn(x[j][i], s, 0.0f);
+      for (int i = 0; i < 8; i++) y[i] = __fmaf_rn(x[i], s, 0.0f);
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[j][i], s), 0.0f);
+      for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[i], s), 0.0f);
     }
     uint32_t w = cvt_e2m1x8(y);
     if (kExactTies) {
@@ -346,9 +372,11 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
         if (a == 0.75f || a == 1.75f || a == 3.5f) w -= 1u << (4 * i);   // half way and rounded up to the even code: the reference stays below
       }
     }
-    const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
-    *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
-    if (q == 0) scales[row * (D / 32) + (piece >> 2)] = (uint8_t)(e + 127);
+    if (row != ~0ull) {
+      const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
+      *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
+      if (q == 0) scales[row * (D / 32) + (piece >> 2)] = (uint8_t)(e + 127);
+    }
   }
 }
 
@@ -362,7 +390,7 @@ bool bulk_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const T* ke
   const uint32_t magic = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV);
   int shift = -1;
   if ((PAGE & (PAGE - 1)) == 0) { shift = 0; while ((1 << shift) < PAGE) shift++; }
-  const unsigned per_block = 8u * 32u * kBulkPieces;
+  const unsigned per_block = 8u * 32u * bulk_pieces<T>();
   const dim3 grid((unsigned)((np + per_block - 1) / per_block), (unsigned)nstream);
   uq_append_bulk_kernel<T><<<grid, 256, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
   return true;
