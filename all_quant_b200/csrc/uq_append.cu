@@ -65,7 +65,7 @@ UQ_DEV void load4<__half>(const __half* p, bool vec, float* out) {
   } else { for (int i = 0; i < 4; i++) out[i] = __half2float(p[i]); }
 }
 
-constexpr int kRotateK = 1, kPaperRule = 2, kRouteBulk = 4, kRouteRows = 8;
+constexpr int kRotateK = 1, kPaperRule = 2, kRouteBulk = 4;   // (flags & 8 names the per-row kernel: nothing to do for it here)
 
 // Orthonormal Walsh-Hadamard transform of one row of D = 64 / 128 / 256 values held by a warp: lane l owns channels
 // 128 s + 4 l .. + 3 of slab s (lanes 16.. hold zeros at D = 64).  Stage h pairs (i, i + h) -> (a + b, a - b), h ascending.
@@ -207,6 +207,9 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 //     the reference does (sign bit = y < 0); adding +0 turns y = -0 (an input -0, or an underflow) into +0 first.
 // Same bytes as the kernel above on every input (the tests run both on the same rows).  Not served here: rotated keys
 // (that transform wants a warp per row), inputs not aligned to 16 bytes, more than 2^31 pieces.
+#ifndef UQ_BULK_THREADS
+#define UQ_BULK_THREADS 128
+#endif
 constexpr long long kBulkMinRows = 4096;   // rows x streams from which a call goes to the bulk kernel
 
 // One piece = 8 consecutive channels as loaded (16 bytes of a 16-bit type, two float4 of fp32).  A thread keeps its pieces
@@ -390,9 +393,9 @@ bool bulk_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const T* ke
   const uint32_t magic = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV);
   int shift = -1;
   if ((PAGE & (PAGE - 1)) == 0) { shift = 0; while ((1 << shift) < PAGE) shift++; }
-  const unsigned per_block = 8u * 32u * bulk_pieces<T>();
+  const unsigned per_block = (UQ_BULK_THREADS / 32u) * 32u * bulk_pieces<T>();
   const dim3 grid((unsigned)((np + per_block - 1) / per_block), (unsigned)nstream);
-  uq_append_bulk_kernel<T><<<grid, 256, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
+  uq_append_bulk_kernel<T><<<grid, UQ_BULK_THREADS, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
   return true;
 }
 

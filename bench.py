@@ -392,6 +392,57 @@ def parity_of(run, got):
             "ok": bool(d.max() <= 1e-2 * np.abs(ref).max() and d.mean() <= 1e-3), "checked": what}
 
 
+def append_prompt(dev, peak, HKV, D, PAGE, tokens, iters=10, seed=77):
+    """The append-quantize of a prompt: `tokens` tokens' keys and values (the benchmark's distributions: N(0,1), keys with a
+    lognormal(0, 0.5) multiplier per channel) encoded and scattered into randomly permuted pages, as bf16 and as fp32 input.
+    Algorithmic bytes = both input tensors + the codes and scale bytes written + the slot list; inputs (over a gigabyte at
+    the default size) and the cache written are larger than L2.  The rows of the first 512 tokens are checked against the
+    CPU oracle, and the per-row kernel (the one a decode step takes) is timed on the same call for contrast."""
+    import torch
+    from all_quant_b200 import uq_cuda
+    from oracle import uq_oracle as O
+    g = torch.Generator(device=dev).manual_seed(seed)
+    pages = (tokens + PAGE - 1) // PAGE
+    chan = torch.exp(0.5 * torch.randn(1, HKV, D, generator=g, device=dev))
+    k32 = torch.randn(tokens, HKV, D, generator=g, device=dev) * chan
+    v32 = torch.randn(tokens, HKV, D, generator=g, device=dev)
+    perm = torch.randperm(pages, generator=g, device=dev)
+    slots = (perm[:, None] * PAGE + torch.arange(PAGE, device=dev)[None, :]).reshape(-1)[:tokens].contiguous()
+    kc = torch.zeros(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device=dev)
+    ks = torch.zeros(pages, HKV, PAGE, D // 32, dtype=torch.uint8, device=dev)
+    vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
+    out = {"workload": f"append of {tokens} tokens x {HKV} kv heads x D{D}, keys and values, page {PAGE}, pages permuted", "peak_GBs": peak}
+    for name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        k, v = k32.to(dt), v32.to(dt)
+        by = 2 * tokens * HKV * (D * k.element_size() + D // 2 + D // 32) + tokens * 8
+        ent = {"algorithmic_bytes": by}
+        for kernel in ("bulk", "rows"):
+            n = iters if kernel == "bulk" else 3
+            for _ in range(3):
+                uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots, kernel=kernel)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots, kernel=kernel)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / n
+            ent[f"{kernel}_kernel_us"] = us
+            if kernel == "bulk":
+                ent["GB/s"] = by / us / 1e3
+                ent["frac"] = by / us / 1e3 / peak
+        n_chk = min(tokens, 512)
+        want_p, want_s = O.quantize_fp4(k[:n_chk].float().cpu().numpy().reshape(n_chk * HKV, D))
+        sl = slots[:n_chk].cpu().numpy()
+        got_p = kc.cpu().numpy()[sl // PAGE, :, sl % PAGE].reshape(n_chk * HKV, D // 2)
+        got_s = ks.cpu().numpy()[sl // PAGE, :, sl % PAGE].reshape(n_chk * HKV, D // 32)
+        ent["parity"] = {"rows_checked": n_chk * HKV, "bit_exact": bool((got_p == want_p).all() and (got_s == want_s).all())}
+        out[name] = ent
+        del k, v
+    return out
+
+
 def run_ours(args, cfg):
     import torch
     import torch.distributed as dist
@@ -413,6 +464,10 @@ def run_ours(args, cfg):
         dist.init_process_group("nccl", device_id=dev)
     lib = uq_cuda.lib()
     peak, peak_kind = peaks()
+    if args.append_only:   # the prompt-sized append alone (what the profiler capture of that kernel runs)
+        ent = append_prompt(dev, peak, cfg["HKV"], cfg["D"], cfg["PAGE"], args.append_tokens, iters=max(1, args.steps))
+        os.write(json_fd, (json.dumps({"append": ent, "peak_kind": peak_kind}) + "\n").encode())
+        return
 
     def barrier():
         if world > 1:
@@ -645,6 +700,8 @@ def run_ours(args, cfg):
             if rk is not run:
                 del rk
                 torch.cuda.empty_cache()
+        torch.cuda.empty_cache()
+        line["append"] = append_prompt(dev, peak, HKV, D, PAGE, B * cfg["ctx"])   # the prompt that fills this very cache: B x ctx tokens
         line["per_k"] = per_k
         line["k8_over_k1"] = per_k["8"]["us_per_layer_call"] / per_k["1"]["us_per_layer_call"]
         line["no_sharing"] = no_sharing
@@ -715,6 +772,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--fmt", type=int, default=0, choices=[0, 1], help="cache format: 0 UltraQuant (the headline), 1 NVFP4 (configurations 1 and 3)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="context split (configuration 4, N > 1): partials by peer stores and flags, or by an NCCL all-gather")
+    ap.add_argument("--append-only", action="store_true", help="time only the append-quantize of a prompt (--append-tokens tokens of the configuration's heads)")
+    ap.add_argument("--append-tokens", type=int, default=262144)
     ap.add_argument("--lean", action="store_true", help="only the headline measurement: no per-K table, no reference-GPU sweep, no sharded configurations")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
