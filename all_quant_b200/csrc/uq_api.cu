@@ -32,7 +32,7 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
 cudaError_t uq_append_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, cudaStream_t, int flags, float c);
 cudaError_t uq_fwht_dispatch(const void*, void*, long long, int, int, cudaStream_t);
-cudaError_t uq_append_nvfp4_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, float, float, cudaStream_t);
+cudaError_t uq_append_nvfp4_dispatch(uint8_t*, uint8_t*, uint8_t*, uint8_t*, const void*, const void*, const int64_t*, int, int, int, int, int, float, float, cudaStream_t, int route);
 cudaError_t uq_verify_fma_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 cudaError_t uq_verify_tc_dispatch(const UQParams&, const UQLaunch&, cudaStream_t);
 bool uq_verify_tc_serves(const UQParams&, const UQLaunch&);
@@ -265,7 +265,12 @@ int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, con
 
 int uqb_append_nvfp4_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value, const int64_t* slots,
                             int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, void* stream) {
-  cudaError_t e = uq_append_nvfp4_dispatch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, k_ts, v_ts, reinterpret_cast<cudaStream_t>(stream));
+  return uqb_append_nvfp4_ex_launch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, k_ts, v_ts, 0, stream);
+}
+
+int uqb_append_nvfp4_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value, const int64_t* slots,
+                               int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, int flags, void* stream) {
+  cudaError_t e = uq_append_nvfp4_dispatch(kc, ks, vc, vs, key, value, slots, T, HKV, D, PAGE, dtype, k_ts, v_ts, reinterpret_cast<cudaStream_t>(stream), flags);
   if (e == cudaSuccess && T > 0) g_launches += 1;
   return (int)e;
 }

@@ -450,6 +450,159 @@ __global__ void __launch_bounds__(128) uq_append_nvfp4_kernel(uint8_t* __restric
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The bulk form of the NVFP4 append: the layout of uq_append_bulk_kernel (pieces of 8 channels, a row lookup per lane), a
+// block of 16 channels = two lanes.  The reference divides every value by the block's scale (float(e4m3 byte) * ts, not a
+// power of two); an fp32 division is ten instructions, and the code only depends on which side of seven boundaries the
+// quotient falls.  So the quotient is bracketed instead: y_lo = x * r_lo and y_hi = x * r_hi with r_lo / r_hi a fast
+// reciprocal of the scale times (1 -+ 2^-21), which lie strictly below / above the reference's rounded quotient in
+// magnitude (the reciprocal is good to 2^-22, the factor is two to four fp32 steps).  Both go through the hardware
+// conversion; where the two codes of a value agree, no boundary lies inside its bracket and the code is the reference's
+// whatever the tie rule of the conversion (a quotient exactly on a boundary has y_lo below and y_hi above it, so the two
+// differ).  Where they differ the value is decided exactly: the reference's rounded quotient exceeds the boundary b iff
+// |x| / sf > b + ulp(b) / 2 (b has an even mantissa, so a quotient half way rounds to b itself), i.e. iff
+// |x| > (b + ulp(b) / 2) * sf, a product that is exact in double precision (25 x 24 bits); its sign bit is set iff x < 0 and
+// the quotient does not round to zero, |x| > 2^-150 * sf.  That happens often enough to matter with 16-bit inputs (a value
+// of 8 significant bits over a scale of 4 lands exactly on a boundary about once in a hundred), so the decision is a short
+// loop over the differing codes of a lane, not a second pass over the piece.  Blocks whose scale is too small or large
+// for the fast reciprocal (below 1e-30, above 1e30; for bf16 above 2^12, where a product could underflow to -0) are
+// encoded with the division and the comparisons of the per-row kernel.  +0 is added to both products of an fp32 input
+// (x * r + 0 for a 16-bit one), so a quotient that the reference rounds to -0 ("not < 0") and a bracket end that keeps a
+// negative denormal disagree and are decided as above.
+__constant__ double kNvBoundary[8] = {   // b + ulp_fp32(b) / 2 for the boundary above magnitude code c
+    0.25 + 0x1p-26, 0.75 + 0x1p-25, 1.25 + 0x1p-24, 1.75 + 0x1p-24, 2.5 + 0x1p-23, 3.5 + 0x1p-23, 5.0 + 0x1p-22, 1e300};
+
+__device__ __noinline__ uint32_t encode8_exact_nvfp4(const float* x, float sf) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    float y = __fdiv_rn(x[i], sf);
+    y = fminf(fmaxf(y, -6.0f), 6.0f);
+    const float a = fabsf(y);
+    const uint32_t c = ((a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f)) | (y < 0.0f ? 8u : 0u);
+    w |= c << (4 * i);
+  }
+  return w;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) uq_append_nvfp4_bulk_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
+                                                                   uint8_t* __restrict__ vs, const T* __restrict__ key, const T* __restrict__ value,
+                                                                   const int64_t* __restrict__ slots, uint32_t np, int HKV, uint32_t hkv_magic, int D,
+                                                                   int PAGE, int page_shift, float k_ts, float v_ts) {
+  constexpr int NP = bulk_pieces<T>();
+  constexpr bool kAddZero = sizeof(T) == 4;   // fp32 inputs: any product can underflow, +0 is added after the multiplication
+  // a 16-bit input's smallest non-zero magnitude (2^-133 bf16, 2^-24 fp16) times the reciprocal stays a normal number
+  // as long as the scale is below this; beyond it the piece takes the exact path
+  constexpr float kSfMax = std::is_same<T, __nv_bfloat16>::value ? 4096.0f /* 2^12 */ : 1e30f;
+  const int stream = blockIdx.y;
+  const T* __restrict__ src = stream ? value : key;
+  uint8_t* __restrict__ codes = stream ? vc : kc;
+  uint8_t* __restrict__ scales = stream ? vs : ks;
+  const float ts = stream ? v_ts : k_ts;
+  const int lane = threadIdx.x & 31;
+  const uint32_t wp0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32u * NP);
+  const uint32_t p0 = wp0 + lane;
+  const int ppr_shift = D == 64 ? 3 : (D == 128 ? 4 : 5);
+  Piece<T> pc[NP];
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const uint32_t p = p0 + 32u * j;
+    if (p < np) pc[j].load(src + (size_t)p * 8);
+    else pc[j].zero();
+  }
+  unsigned long long my_row = ~0ull;
+  {
+    const uint32_t r = (wp0 >> ppr_shift) + lane;
+    if (lane < ((32 * NP) >> ppr_shift) && r < (np >> ppr_shift)) {
+      uint32_t h;
+      const uint32_t t = div_magic(r, (uint32_t)HKV, hkv_magic, h);
+      const int64_t slot = __ldg(slots + t);
+      if (slot >= 0) {
+        int64_t page, off;
+        if (page_shift >= 0) { page = slot >> page_shift; off = slot & ((1ll << page_shift) - 1); }
+        else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
+        else { page = slot / PAGE; off = slot % PAGE; }
+        my_row = ((unsigned long long)page * HKV + h) * PAGE + off;
+      }
+    }
+  }
+  // block maxima (a block = the two lanes of a piece); the two lanes share the work on the scales: the even lane takes
+  // the even pieces, the odd lane the odd ones, a shuffle hands the results round
+  const int par = lane & 1;
+  float r_lo[NP / 2], r_hi[NP / 2], sf_m[NP / 2];
+  uint32_t sb_m[NP / 2];   // scale byte | 0x100 when the fast path does not serve this block
+#pragma unroll
+  for (int i = 0; i < NP / 2; i++) {
+    float a0 = pc[2 * i].amax(), a1 = pc[2 * i + 1].amax();
+    a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, 1));
+    a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, 1));
+    const float amax = par ? a1 : a0;
+    float r = __fdiv_rn(__fdiv_rn(amax, 6.0f), ts);
+    r = fminf(fmaxf(r, 0.001953125f), 448.0f);   // (NaN inputs are not reproduced: here they vanish from the maximum, torch carries them into the scale)
+    const uint32_t sb = (uint32_t)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+    const float sf = __fmul_rn(uq_e4m3_f32(sb), ts);
+    float rc;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(sf));
+    const bool fast = sf > 1e-30f && sf < kSfMax;   // (also false for a scale that is not a number)
+    r_lo[i] = __fmul_rn(rc, 0x1.fffffp-1f);    // 1 - 2^-21
+    r_hi[i] = __fmul_rn(rc, 0x1.000008p+0f);   // 1 + 2^-21
+    sf_m[i] = sf;
+    sb_m[i] = sb | (fast ? 0u : 0x100u);
+  }
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const int from = (lane & ~1) | (j & 1);
+    const float lo = __shfl_sync(0xffffffffu, r_lo[j >> 1], from), hi = __shfl_sync(0xffffffffu, r_hi[j >> 1], from);
+    const uint32_t sbf = __shfl_sync(0xffffffffu, sb_m[j >> 1], from);
+    const float sf = __shfl_sync(0xffffffffu, sf_m[j >> 1], from);
+    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
+    float x[8], y[8];
+    pc[j].values(x);
+#pragma unroll
+    for (int i = 0; i < 8; i++) y[i] = kAddZero ? __fadd_rn(__fmul_rn(x[i], lo), 0.0f) : __fmaf_rn(x[i], lo, 0.0f);
+    uint32_t w = cvt_e2m1x8(y);
+#pragma unroll
+    for (int i = 0; i < 8; i++) y[i] = kAddZero ? __fadd_rn(__fmul_rn(x[i], hi), 0.0f) : __fmaf_rn(x[i], hi, 0.0f);
+    const uint32_t w_hi = cvt_e2m1x8(y);
+    if (sbf & 0x100u) {
+      w = encode8_exact_nvfp4(x, sf);
+    } else {
+      uint32_t d = w ^ w_hi;
+      while (d) {   // the values whose bracket holds a boundary (or the edge of zero): decided exactly, one at a time
+        const int sh = (__ffs(d) - 1) & ~3, idx = sh >> 2;
+        const float xv = idx < 4 ? (idx < 2 ? (idx == 0 ? x[0] : x[1]) : (idx == 2 ? x[2] : x[3]))
+                                 : (idx < 6 ? (idx == 4 ? x[4] : x[5]) : (idx == 6 ? x[6] : x[7]));
+        const uint32_t c = (w >> sh) & 7u, c_hi = (w_hi >> sh) & 7u;
+        const double ax = (double)fabsf(xv), sfd = (double)sf;
+        const uint32_t mag = c + ((c_hi != c && ax > kNvBoundary[c] * sfd) ? 1u : 0u);
+        const uint32_t neg = (xv < 0.0f && ax > sfd * 0x1p-150) ? 8u : 0u;
+        w = (w & ~(0xFu << sh)) | ((mag | neg) << sh);
+        d &= ~(0xFu << sh);
+      }
+    }
+    if (row != ~0ull) {
+      const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
+      *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
+      if (par == 0) scales[row * (D / 16) + (piece >> 1)] = (uint8_t)sbf;
+    }
+  }
+}
+
+template <typename T>
+bool bulk_nvfp4_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const T* key, const T* value, const int64_t* slots, int T_tok, int HKV,
+                       int D, int PAGE, float k_ts, float v_ts, cudaStream_t s) {
+  const unsigned long long np = (unsigned long long)T_tok * HKV * (D / 8);
+  if (np >= (1ull << 31) || ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15)) return false;
+  const uint32_t magic = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV);
+  int shift = -1;
+  if ((PAGE & (PAGE - 1)) == 0) { shift = 0; while ((1 << shift) < PAGE) shift++; }
+  const unsigned per_block = (UQ_BULK_THREADS / 32u) * 32u * bulk_pieces<T>();
+  const dim3 grid((unsigned)((np + per_block - 1) / per_block), 2u);
+  uq_append_nvfp4_bulk_kernel<T><<<grid, UQ_BULK_THREADS, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, k_ts, v_ts);
+  return true;
+}
+
 // The transform alone (the queries of a cache whose keys were rotated): one warp per row, out may be x.
 template <typename T>
 __global__ void __launch_bounds__(128) uq_fwht_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows, int D) {
@@ -488,13 +641,24 @@ cudaError_t uq_fwht_dispatch(const void* x, void* out, long long rows, int D, in
   return cudaGetLastError();
 }
 
+// route: 0 by the size of the call, 4 the bulk kernel, 8 the per-row kernel (as the flags of uq_append_dispatch)
 cudaError_t uq_append_nvfp4_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
-                                     const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, cudaStream_t s) {
+                                     const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, cudaStream_t s, int route) {
   if (T == 0) return cudaSuccess;
   if (!kc || !ks || !vc || !vs || !key || !value || !slots) return cudaErrorInvalidValue;
   if (!(D == 64 || D == 128 || D == 256) || PAGE <= 0 || HKV <= 0 || T < 0 || dtype < 0 || dtype > 2) return cudaErrorInvalidValue;
-  if (!(k_ts > 0.f) || !(v_ts > 0.f)) return cudaErrorInvalidValue;
+  if (!(k_ts > 0.f) || !(v_ts > 0.f) || (route != 0 && route != 4 && route != 8)) return cudaErrorInvalidValue;
   const long long warps = (long long)T * HKV * 2;
+  if (route == kRouteBulk || (route == 0 && warps >= kBulkMinRows)) {
+    bool done = false;
+    switch (dtype) {
+      case 0: done = bulk_nvfp4_launch<float>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, k_ts, v_ts, s); break;
+      case 1: done = bulk_nvfp4_launch<__nv_bfloat16>(kc, ks, vc, vs, (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, slots, T, HKV, D, PAGE, k_ts, v_ts, s); break;
+      default: done = bulk_nvfp4_launch<__half>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, k_ts, v_ts, s); break;
+    }
+    if (done) return cudaGetLastError();
+    if (route == kRouteBulk) return cudaErrorInvalidValue;
+  }
   const int blocks = (int)((warps + 3) / 4);
   switch (dtype) {
     case 0: uq_append_nvfp4_kernel<float><<<blocks, 128, 0, s>>>(kc, ks, vc, vs, (const float*)key, (const float*)value, slots, T, HKV, D, PAGE, k_ts, v_ts); break;

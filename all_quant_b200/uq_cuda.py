@@ -33,7 +33,7 @@ class UQParams(ctypes.Structure):
 
 
 EXPORTS = ("uqb_block_m", "uqb_mo_elems", "uqb_ml_elems", "uqb_workspace_bytes", "uqb_decode_launch", "uqb_decode_launch_ws",
-           "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_append_nvfp4_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
+           "uqb_has_sm90", "uqb_append_launch", "uqb_append_ex_launch", "uqb_append_nvfp4_launch", "uqb_append_nvfp4_ex_launch", "uqb_fwht_launch", "uqb_decode_partial_launch", "uqb_tree_decode_launch", "uqb_merge_launch", "uqb_merge_packed_launch", "uqb_last_status",
            "uqb_last_path", "uqb_launch_count", "uqb_debug_events",
            "uqb_decode_launch_static", "uqb_static_scratch_bytes",
            "uqb_peer_bytes", "uqb_peer_alloc", "uqb_peer_open", "uqb_peer_close", "uqb_peer_free", "uqb_decode_partial_push_launch", "uqb_merge_wait_launch",
@@ -59,6 +59,7 @@ def lib():
         L.uqb_append_ex_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, ctypes.c_float, vp]
         L.uqb_fwht_launch.argtypes = [vp, vp, ctypes.c_longlong, i, i, vp]
         L.uqb_append_nvfp4_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, ctypes.c_float, ctypes.c_float, vp]
+        L.uqb_append_nvfp4_ex_launch.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, ctypes.c_float, ctypes.c_float, i, vp]
         L.uqb_decode_partial_launch.argtypes = [pp, vp, vp, vp, vp]
         L.uqb_merge_launch.argtypes = [vp, vp, i, sz, i, vp, vp]
         L.uqb_tree_decode_launch.argtypes = [pp, vp, vp]
@@ -402,10 +403,13 @@ def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule=
     _check(err, "uq_append_launch")
 
 
-def append_kv_nvfp4(kc, ks, vc, vs, key, value, slot_mapping, k_ts, v_ts):
+def append_kv_nvfp4(kc, ks, vc, vs, key, value, slot_mapping, k_ts, v_ts, kernel=None):
     """The append for an NVFP4 cache (fmt=1): key/value [T,Hkv,D] -> e2m1 codes and one e4m3fn scale byte per 16 channels
     (ks/vs [pages,Hkv,PAGE,D/16]) for the per-tensor scales k_ts / v_ts, which the decode call takes as well.  Bytes
-    identical to the reference's quantize_nvfp4(x, tensor_scale) (uqmt/quant.py:125-136); one kernel launch."""
+    identical to the reference's quantize_nvfp4(x, tensor_scale) (uqmt/quant.py:125-136); one kernel launch (kernel as in
+    append_kv: by the size of the call, or 'bulk' / 'rows')."""
+    if kernel not in _KERNEL_FLAG:
+        raise ValueError(f"append kernel {kernel!r}: None (by the size of the call), 'bulk' or 'rows'")
     _need_cuda(kc, ks, vc, vs, key, value, slot_mapping)
     if key.dtype not in _DTYPE or value.dtype != key.dtype:
         raise RuntimeError("key/value must both be fp32, bf16 or fp16")
@@ -418,8 +422,9 @@ def append_kv_nvfp4(kc, ks, vc, vs, key, value, slot_mapping, k_ts, v_ts):
         if not t.is_contiguous() or t.dtype != torch.uint8:
             raise RuntimeError("cache tensors must be contiguous uint8")
     with torch.cuda.device(key.device):
-        err = lib().uqb_append_nvfp4_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
-                                            slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], float(k_ts), float(v_ts), _stream(key))
+        err = lib().uqb_append_nvfp4_ex_launch(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                               slots.data_ptr(), T, HKV, D, kc.shape[2], _DTYPE[key.dtype], float(k_ts), float(v_ts),
+                                               _KERNEL_FLAG[kernel], _stream(key))
     _check(err, "uq_append_nvfp4_launch")
 
 

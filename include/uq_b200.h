@@ -71,6 +71,11 @@ int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, con
  * cache uqmt/nvfp4.py:229-254); the reference has no kernel for it.  key and value both required. */
 int uqb_append_nvfp4_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                             const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, void* stream);
+/* The same with a choice of kernel: flags 0 = by the size of the call (uqb_append_nvfp4_launch), 4 = the bulk kernel,
+ * 8 = the kernel with one warp per row; same bytes (see uqb_append_ex_launch). */
+int uqb_append_nvfp4_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
+                               const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, float k_ts, float v_ts, int flags,
+                               void* stream);
 
 /* Orthonormal Walsh-Hadamard transform along the last axis of x [rows, D] (D in {64,128,256}; dtype as above),
  * out may be x: the reference's fwht (uqmt/quant.py:84-98, rotate_kq :105-107) for the queries. */

@@ -152,9 +152,10 @@ def test_oracle_nvfp4_quantiser_matches_the_reference_bytes(D):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["rows", "bulk"])
 @pytest.mark.parametrize("D", (64, 128, 256))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_nvfp4_append_kernel_bit_exact(D, dtype):
+def test_nvfp4_append_kernel_bit_exact(D, dtype, kernel):
     from all_quant_b200 import uq_cuda
     z = _qz()
     x = torch.from_numpy(z[f"d{D}_x"]).to(dtype)
@@ -169,11 +170,96 @@ def test_nvfp4_append_kernel_bit_exact(D, dtype):
     ks = torch.zeros(pages, HKV, PAGE, D // 16, dtype=torch.uint8, device="cuda")
     vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
     slots = torch.from_numpy(np.random.default_rng(4).permutation(pages * PAGE)[:T].astype(np.int64)).cuda()
-    uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, x.cuda(), x.cuda(), slots, ts, ts)
+    uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, x.cuda(), x.cuda(), slots, ts, ts, kernel=kernel)
     pg, at = (slots // PAGE).cpu(), (slots % PAGE).cpu()
     for codes, scales in ((kc, ks), (vc, vs)):
         assert np.array_equal(codes.cpu()[pg, :, at].numpy(), want_c)
         assert np.array_equal(scales.cpu()[pg, :, at].numpy(), want_s)
+
+
+def _nv_steps(v, dtype, k):
+    """v (fp32 numpy, > 0) moved k representable steps of `dtype`."""
+    if dtype == torch.bfloat16:
+        b = (v.view(np.uint32) >> 16).astype(np.int64) + k
+        return (b.astype(np.uint32) << 16).view(np.float32)
+    t, iv = (np.float32, np.int32) if dtype == torch.float32 else (np.float16, np.int16)
+    return (v.astype(t).view(iv) + iv(k)).view(t).astype(np.float32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["rows", "bulk"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_nvfp4_append_on_and_beside_every_code_boundary(dtype, kernel):
+    """Blocks whose scale is exactly a power of two (maximum 6 * 2^k, ts = 1) hold the code boundaries themselves, where the
+    reference takes the smaller magnitude, their nearest neighbours in the input's type, zeros of both signs and tiny values;
+    the bulk kernel brackets the quotient and must fall back to the division exactly there.  A second tensor scale (0.3:
+    quotients that are not exact) runs the same values through rounded quotients."""
+    from all_quant_b200 import uq_cuda
+    thr = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+    cand = np.concatenate([_nv_steps(thr, dtype, k) for k in (-2, -1, 0, 1, 2)])
+    cand = np.concatenate([cand, -cand, np.array([0.0, -0.0, 1e-30, -1e-30, 6.0, -6.0, 0.5, -1.0, 4.0, -3.0, -1e-38, 2e-45, -2e-45], np.float32)])
+    blocks = []
+    for k in (-6, -1, 0, 3, 7):
+        v = cand * np.float32(2.0 ** k)
+        n = (v.size + 14) // 15
+        g = np.zeros((n, 16), np.float32)
+        g[:, 0] = 6.0 * 2.0 ** k
+        g[:, 1:].reshape(-1)[: v.size] = v
+        blocks.append(g)
+    x = np.concatenate(blocks)
+    x = np.concatenate([x, np.zeros(((-x.shape[0]) % 4, 16), np.float32)]).reshape(-1, 1, 64)
+    xt = torch.from_numpy(x).to(dtype)
+    T = xt.shape[0]
+    for ts in (1.0, 0.3):
+        want_c, want_s = O.quantize_nvfp4(xt.float().numpy(), ts)
+        PAGE = 16
+        pages = (T + PAGE - 1) // PAGE
+        kc = torch.zeros(pages, 1, PAGE, 32, dtype=torch.uint8, device="cuda")
+        ks = torch.zeros(pages, 1, PAGE, 4, dtype=torch.uint8, device="cuda")
+        vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
+        uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, xt.cuda(), xt.cuda(), torch.arange(T, device="cuda"), ts, ts, kernel=kernel)
+        assert np.array_equal(ks.reshape(-1, 1, 4)[:T].cpu().numpy(), want_s)
+        assert np.array_equal(kc.reshape(-1, 1, 32)[:T].cpu().numpy(), want_c)
+        assert np.array_equal(vc.reshape(-1, 1, 32)[:T].cpu().numpy(), want_c)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,HKV,PAGE", [(64, 1, 16), (128, 3, 48), (128, 8, 64), (256, 5, 32)])
+def test_nvfp4_bulk_kernel_writes_the_bytes_of_the_row_kernel_and_the_oracle(D, HKV, PAGE, dtype):
+    """Seeded keys and values of very different magnitude (scale bytes from the lower clamp to the upper one), scattered
+    slots with skipped tokens, head counts and page sizes that do not line up with a warp's run of rows."""
+    from all_quant_b200 import uq_cuda
+    g = torch.Generator(device="cuda").manual_seed(3 * D + HKV + PAGE)
+    T = 1000 + HKV
+    pages = (T + PAGE - 1) // PAGE + 2
+    mag = torch.exp2(torch.randint(-12, 9, (T, HKV, D // 16, 1), generator=g, device="cuda").float())
+    k = (torch.randn(T, HKV, D // 16, 16, generator=g, device="cuda") * mag).reshape(T, HKV, D).to(dtype)
+    v = (torch.randn(T, HKV, D, generator=g, device="cuda") * 0.3).to(dtype)
+    slots = torch.randperm(pages * PAGE, generator=g, device="cuda")[:T]
+    slots[::11] = -1
+    k_ts, v_ts = 0.013, 0.0021
+    out = {}
+    for kernel in ("rows", "bulk"):
+        kc = torch.full((pages, HKV, PAGE, D // 2), 0xA5, dtype=torch.uint8, device="cuda")
+        ks = torch.full((pages, HKV, PAGE, D // 16), 0x5A, dtype=torch.uint8, device="cuda")
+        vc, vs = kc.clone(), ks.clone()
+        uq_cuda.append_kv_nvfp4(kc, ks, vc, vs, k, v, slots, k_ts, v_ts, kernel=kernel)
+        torch.cuda.synchronize()
+        out[kernel] = [t.cpu().numpy() for t in (kc, ks, vc, vs)]
+    for a, b in zip(out["rows"], out["bulk"]):
+        assert np.array_equal(a, b)
+    sl = slots.cpu().numpy()
+    keep = sl >= 0
+    for x, ts, (codes, scales) in ((k, k_ts, out["bulk"][:2]), (v, v_ts, out["bulk"][2:])):
+        want_c, want_s = O.quantize_nvfp4(x.float().cpu().numpy(), ts)
+        ref_c = np.full((pages, HKV, PAGE, D // 2), 0xA5, np.uint8)
+        ref_s = np.full((pages, HKV, PAGE, D // 16), 0x5A, np.uint8)
+        ref_c[sl[keep] // PAGE, :, sl[keep] % PAGE] = want_c[keep]
+        ref_s[sl[keep] // PAGE, :, sl[keep] % PAGE] = want_s[keep]
+        assert np.array_equal(codes, ref_c) and np.array_equal(scales, ref_s)
+    ks_written = out["bulk"][1][sl[keep] // PAGE, :, sl[keep] % PAGE]
+    assert ks_written.min() <= 0x08 and ks_written.max() >= 0x70      # both ends of the scale's range are in the data
 
 
 @pytest.mark.gpu
