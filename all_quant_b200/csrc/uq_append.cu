@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
   }
   // Where the rows go: the warp's 32 * NP pieces are 4 .. 32 whole rows, lane L looks up row L (token, head, slot, page)
   // once and a piece fetches its row's answer by shuffle.  ~0 = no row (past the end, or a skipped token).
-  unsigned long long my_row = ~0ull;
+  unsigned long long my_off = ~0ull;   // byte offset of the row's codes in the cache
   {
     const uint32_t r = (wp0 >> ppr_shift) + lane;
     if (lane < ((32 * NP) >> ppr_shift) && r < (np >> ppr_shift)) {
@@ -326,14 +326,23 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
         if (page_shift >= 0) { page = slot >> page_shift; off = slot & ((1ll << page_shift) - 1); }
         else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
         else { page = slot / PAGE; off = slot % PAGE; }
-        my_row = ((unsigned long long)page * HKV + h) * PAGE + off;
+        my_off = (((unsigned long long)page * HKV + h) * PAGE + off) * (unsigned)(D / 2);
       }
     }
   }
-  // group maxima (a group = the four lanes of a piece), and the exponents: lane q of a group computes those of pieces
-  // q, q + 4, ...; the encoding loop fetches each piece's by shuffle
+  // group maxima (a group = the four lanes of a piece), and the scales: lane q of a group computes the exponents of pieces
+  // q, q + 4, ... and from them the multipliers 2^-e (e = 127 gives the denormal 2^-127; a 16-bit input takes the fp32
+  // value just below 2^-e); the encoding loop fetches each piece's multiplier by shuffle and reads the scale byte off it
   const int q = lane & 3;
-  int e_mine[NP / 4];
+  constexpr uint32_t kBelow = kExactTies ? 0u : 1u;
+  uint32_t inv_mine[NP / 4];
+  // y = -0 must become +0 (the reference's sign bit is y < 0).  x * s + (+0) does that for an input -0 at no cost, but a
+  // negative product too small for fp32 still rounds to -0: possible only when the smallest non-zero magnitude of the
+  // 16-bit input type (2^-133 bf16, 2^-24 fp16) times 2^-e does not exceed 2^-150 (2^-150 itself is half way between 0
+  // and the smallest denormal and rounds to zero), i.e. for bf16 groups whose maximum is beyond 6 * 2^16; a warp that
+  // holds such a group, and every warp of an fp32 input, adds +0 after the multiplication instead
+  constexpr int kTiny = std::is_same<T, __nv_bfloat16>::value ? -133 : -24;
+  bool tiny = sizeof(T) == 4;
 #pragma unroll
   for (int r = 0; r < NP / 4; r++) {
     float am = 0.f;
@@ -344,43 +353,40 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
       a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
       if (q == jj) am = a;
     }
-    e_mine[r] = group_exponent(am, paper != 0, c);
+    const int e = group_exponent(am, paper != 0, c);
+    inv_mine[r] = (e == 127 ? 0x00400000u : (uint32_t)(127 - e) << 23) - kBelow;
+    tiny |= kTiny - e <= -150;
   }
+  const bool add_zero = sizeof(T) == 4 || __any_sync(0xffffffffu, tiny);
+  auto encode = [&](auto add_zero_c) {
 #pragma unroll
-  for (int j = 0; j < NP; j++) {
-    const int e = __shfl_sync(0xffffffffu, e_mine[j >> 2], (lane & ~3) | (j & 3));
-    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
-    // 2^-e as fp32 (e = 127 gives the denormal 2^-127); a 16-bit input takes the fp32 value just below it
-    const uint32_t inv = (e == 127 ? 0x00400000u : (uint32_t)(127 - e) << 23) - (kExactTies ? 0u : 1u);
-    const float s = __uint_as_float(inv);
-    float x[8], y[8];
-    pc[j].values(x);
-    // y = -0 must become +0 (the reference's sign bit is y < 0).  x * s + (+0) does that for an input -0 at no cost, but a
-    // negative product too small for fp32 still rounds to -0: possible only when the smallest non-zero magnitude of the
-    // 16-bit input type (2^-133 bf16, 2^-24 fp16) times 2^-e does not exceed 2^-150, i.e. for bf16 groups whose maximum is
-    // beyond 6 * 2^16; those groups, and fp32 inputs, add +0 afterwards
-    constexpr int kTiny = std::is_same<T, __nv_bfloat16>::value ? -133 : -24;
-    if (sizeof(T) != 4 && kTiny - e > -150) {   // (2^-150 itself is half way between 0 and the smallest denormal and rounds to zero)
+    for (int j = 0; j < NP; j++) {
+      const uint32_t inv = __shfl_sync(0xffffffffu, inv_mine[j >> 2], (lane & ~3) | (j & 3));
+      const unsigned long long off = __shfl_sync(0xffffffffu, my_off, (32 * j + lane) >> ppr_shift);
+      const float s = __uint_as_float(inv);
+      float x[8], y[8];
+      pc[j].values(x);
 #pragma unroll
-      for (int i = 0; i < 8; i++) y[i] = __fmaf_rn(x[i], s, 0.0f);
-    } else {
+      for (int i = 0; i < 8; i++) y[i] = decltype(add_zero_c)::value ? __fadd_rn(__fmul_rn(x[i], s), 0.0f) : __fmaf_rn(x[i], s, 0.0f);
+      uint32_t w = cvt_e2m1x8(y);
+      if (kExactTies) {
 #pragma unroll
-      for (int i = 0; i < 8; i++) y[i] = __fadd_rn(__fmul_rn(x[i], s), 0.0f);
-    }
-    uint32_t w = cvt_e2m1x8(y);
-    if (kExactTies) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const float a = fabsf(y[i]);
-        if (a == 0.75f || a == 1.75f || a == 3.5f) w -= 1u << (4 * i);   // half way and rounded up to the even code: the reference stays below
+        for (int i = 0; i < 8; i++) {
+          const float a = fabsf(y[i]);
+          if (a == 0.75f || a == 1.75f || a == 3.5f) w -= 1u << (4 * i);   // half way and rounded up to the even code: the reference stays below
+        }
+      }
+      if (off != ~0ull) {
+        const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
+        *reinterpret_cast<uint32_t*>(codes + off + piece * 4) = w;
+        // scale byte e + 127 = 254 - (exponent field of 2^-e), which is 0 for the denormal 2^-127; a row's scale bytes
+        // start at 1/16 of its codes' offset
+        if (q == 0) scales[(off >> 4) + (piece >> 2)] = (uint8_t)(254u - ((inv + kBelow) >> 23));
       }
     }
-    if (row != ~0ull) {
-      const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
-      *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
-      if (q == 0) scales[row * (D / 32) + (piece >> 2)] = (uint8_t)(e + 127);
-    }
-  }
+  };
+  if (add_zero) encode(std::true_type{});
+  else encode(std::false_type{});
 }
 
 // the bulk kernel serves: no rotation, pointers aligned for the vector loads, piece count within 32 bits
