@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(256) uq_append_nvfp4_bulk_kernel(uint8_t* __re
     if (p < np) pc[j].load(src + (size_t)p * 8);
     else pc[j].zero();
   }
-  unsigned long long my_row = ~0ull;
+  unsigned long long my_off = ~0ull;   // byte offset of the row's codes in the cache
   {
     const uint32_t r = (wp0 >> ppr_shift) + lane;
     if (lane < ((32 * NP) >> ppr_shift) && r < (np >> ppr_shift)) {
@@ -529,7 +529,7 @@ __global__ void __launch_bounds__(256) uq_append_nvfp4_bulk_kernel(uint8_t* __re
         if (page_shift >= 0) { page = slot >> page_shift; off = slot & ((1ll << page_shift) - 1); }
         else if (slot <= 0x7fffffffll) { page = (uint32_t)slot / (uint32_t)PAGE; off = (uint32_t)slot % (uint32_t)PAGE; }
         else { page = slot / PAGE; off = slot % PAGE; }
-        my_row = ((unsigned long long)page * HKV + h) * PAGE + off;
+        my_off = (((unsigned long long)page * HKV + h) * PAGE + off) * (unsigned)(D / 2);
       }
     }
   }
@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(256) uq_append_nvfp4_bulk_kernel(uint8_t* __re
     const float lo = __shfl_sync(0xffffffffu, r_lo[j >> 1], from), hi = __shfl_sync(0xffffffffu, r_hi[j >> 1], from);
     const uint32_t sbf = __shfl_sync(0xffffffffu, sb_m[j >> 1], from);
     const float sf = __shfl_sync(0xffffffffu, sf_m[j >> 1], from);
-    const unsigned long long row = __shfl_sync(0xffffffffu, my_row, (32 * j + lane) >> ppr_shift);
+    const unsigned long long off = __shfl_sync(0xffffffffu, my_off, (32 * j + lane) >> ppr_shift);
     float x[8], y[8];
     pc[j].values(x);
 #pragma unroll
@@ -587,10 +587,10 @@ __global__ void __launch_bounds__(256) uq_append_nvfp4_bulk_kernel(uint8_t* __re
         d &= ~(0xFu << sh);
       }
     }
-    if (row != ~0ull) {
+    if (off != ~0ull) {
       const uint32_t piece = (p0 + 32u * j) & ((1u << ppr_shift) - 1u);
-      *reinterpret_cast<uint32_t*>(codes + row * (D / 2) + piece * 4) = w;
-      if (par == 0) scales[row * (D / 16) + (piece >> 1)] = (uint8_t)sbf;
+      *reinterpret_cast<uint32_t*>(codes + off + piece * 4) = w;
+      if (par == 0) scales[(off >> 3) + (piece >> 1)] = (uint8_t)sbf;   // (a row's scale bytes start at 1/8 of its codes' offset)
     }
   }
 }
