@@ -65,6 +65,122 @@ __global__ void __launch_bounds__(256) uq_layout_kernel(uint8_t* kc, uint8_t* ks
   }
 }
 
+// The same permute staged through shared memory, for caches of any size that matters: a block owns 64 consecutive slots,
+// which are one contiguous run of the upstream array that starts on a 64-byte boundary whatever the slot size, so that side
+// is moved with whole 16-byte vectors by consecutive threads; the pieces of a slot (a stream's codes start 4, 2 or 1 bytes
+// aligned inside it: 68 bytes into a slot of head_dim 128) are picked out of shared memory, where alignment costs nothing,
+// and this library's side is written / read as 16-byte vectors of 64-byte code rows.  W = the widest access every piece
+// of a slot is aligned to inside the staged run.
+constexpr int kStagedSlots = 64;
+
+// n / d for n < 2^32 with m = floor(2^32 / d) (d = 1 takes m = 2^32 - 1): the estimate is short by one at most
+UQ_DEV uint32_t div_magic(uint32_t n, uint32_t d, uint32_t m, uint32_t& rem) {
+  uint32_t q = __umulhi(n, m);
+  uint32_t r = n - q * d;
+  if (r >= d) { q++; r -= d; }
+  rem = r;
+  return q;
+}
+
+template <int W>
+UQ_DEV uint4 stage_load16(const uint8_t* p) {
+  uint32_t w[4];
+  if (W == 4) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) w[k] = *reinterpret_cast<const uint32_t*>(p + 4 * k);
+  } else if (W == 2) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) w[k] = (uint32_t) * reinterpret_cast<const uint16_t*>(p + 4 * k) | ((uint32_t) * reinterpret_cast<const uint16_t*>(p + 4 * k + 2) << 16);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; k++) w[k] = (uint32_t)p[4 * k] | ((uint32_t)p[4 * k + 1] << 8) | ((uint32_t)p[4 * k + 2] << 16) | ((uint32_t)p[4 * k + 3] << 24);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <int W>
+UQ_DEV void stage_store16(uint8_t* p, uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (W == 4) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) *reinterpret_cast<uint32_t*>(p + 4 * k) = w[k];
+  } else if (W == 2) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) *reinterpret_cast<uint16_t*>(p + 2 * k) = (uint16_t)(w[k >> 1] >> (16 * (k & 1)));
+  } else {
+#pragma unroll
+    for (int k = 0; k < 16; k++) p[k] = (uint8_t)(w[k >> 2] >> (8 * (k & 3)));
+  }
+}
+
+template <bool kToUpstream, int W>
+__global__ void __launch_bounds__(256) uq_layout_staged_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
+                                                               uint8_t* __restrict__ vs, uint8_t* __restrict__ aos, uint32_t slots, int HKV,
+                                                               uint32_t hkv_magic, int PAGE, uint32_t page_magic, int D, int slot_bytes, int flags) {
+  extern __shared__ __align__(16) uint8_t stage[];   // the block's slots as they lie in the upstream array
+  const int G = D / 32, half = D / 2, stream_bytes = half + G;
+  const int g_shift = D == 64 ? 1 : (D == 128 ? 2 : 3);
+  const uint32_t s0 = blockIdx.x * (uint32_t)kStagedSlots;
+  const int count = (int)min((uint32_t)kStagedSlots, slots - s0);
+  const int bytes = count * slot_bytes, vecs = bytes >> 4;
+  uint8_t* region = aos + (size_t)s0 * slot_bytes;
+  if (!kToUpstream) {
+    for (int i = threadIdx.x; i < vecs; i += blockDim.x) reinterpret_cast<uint4*>(stage)[i] = __ldcs(reinterpret_cast<const uint4*>(region) + i);
+    for (int i = (vecs << 4) + threadIdx.x; i < bytes; i += blockDim.x) stage[i] = region[i];   // (a last block of fewer slots may end inside a vector)
+  } else if (slot_bytes > 2 * stream_bytes) {
+    for (int i = threadIdx.x; i < (bytes + 15) >> 4; i += blockDim.x) reinterpret_cast<uint4*>(stage)[i] = make_uint4(0u, 0u, 0u, 0u);   // the allocator's padding
+  }
+  __syncthreads();
+  for (int it = threadIdx.x; it < count * 2 * G; it += blockDim.x) {
+    const int g = it & (G - 1), stream = (it >> g_shift) & 1, sl = it >> (g_shift + 1);
+    uint32_t h, t;
+    const uint32_t qs = div_magic(s0 + sl, (uint32_t)HKV, hkv_magic, h);   // slot = (page * PAGE + token) * HKV + head
+    const uint32_t page = div_magic(qs, (uint32_t)PAGE, page_magic, t);
+    const size_t row = ((size_t)page * HKV + h) * PAGE + t;                // the same token in this library's order
+    uint8_t* st = stage + sl * slot_bytes + stream * stream_bytes;
+    uint8_t* codes = (stream ? vc : kc) + row * half + g * 16;
+    uint8_t* scale = (stream ? vs : ks) + row * G + g;
+    if (kToUpstream) {
+      const uint4 c = *reinterpret_cast<const uint4*>(codes);
+      uint32_t w[4] = {c.x, c.y, c.z, c.w};
+      uint8_t sb = *scale;
+      uint32_t any = 0;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const uint32_t mag = w[k] & 0x77777777u;
+        any |= mag;
+        if (flags & 1) w[k] &= 0x77777777u | ((mag + 0x77777777u) & 0x88888888u);   // bit 3 of a nibble survives only where its magnitude is not zero
+      }
+      if ((flags & 2) && any == 0) sb = 0;
+      stage_store16<W>(st + g * 16, make_uint4(w[0], w[1], w[2], w[3]));
+      st[half + g] = sb;
+    } else {
+      *reinterpret_cast<uint4*>(codes) = stage_load16<W>(st + g * 16);
+      *scale = st[half + g];
+    }
+  }
+  if (kToUpstream) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < vecs; i += blockDim.x) reinterpret_cast<uint4*>(region)[i] = reinterpret_cast<const uint4*>(stage)[i];
+    for (int i = (vecs << 4) + threadIdx.x; i < bytes; i += blockDim.x) region[i] = stage[i];
+  }
+}
+
+template <bool kToUpstream>
+bool staged_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, uint8_t* aos, long long slots, int HKV, int PAGE, int D, int slot_bytes, int flags,
+                   cudaStream_t s) {
+  const size_t smem = (size_t)kStagedSlots * slot_bytes;
+  if (slots >= (1ll << 31) || smem > 48 * 1024 || (reinterpret_cast<uintptr_t>(aos) & 15)) return false;
+  const uint32_t hm = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV), pm = PAGE == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)PAGE);
+  const unsigned blocks = (unsigned)((slots + kStagedSlots - 1) / kStagedSlots);
+  const int sb = D / 2 + D / 32;
+  const int w = ((slot_bytes | sb) & 3) == 0 ? 4 : (((slot_bytes | sb) & 1) == 0 ? 2 : 1);
+  if (w == 4) uq_layout_staged_kernel<kToUpstream, 4><<<blocks, 256, smem, s>>>(kc, ks, vc, vs, aos, (uint32_t)slots, HKV, hm, PAGE, pm, D, slot_bytes, flags);
+  else if (w == 2) uq_layout_staged_kernel<kToUpstream, 2><<<blocks, 256, smem, s>>>(kc, ks, vc, vs, aos, (uint32_t)slots, HKV, hm, PAGE, pm, D, slot_bytes, flags);
+  else uq_layout_staged_kernel<kToUpstream, 1><<<blocks, 256, smem, s>>>(kc, ks, vc, vs, aos, (uint32_t)slots, HKV, hm, PAGE, pm, D, slot_bytes, flags);
+  return true;
+}
+
 }  // namespace
 
 // dir 0: this library's arrays -> upstream slots (flags: 1 minus-zero codes become zero, 2 all-zero groups get scale byte 0);
@@ -76,6 +192,10 @@ cudaError_t uq_layout_dispatch(int dir, uint8_t* kc, uint8_t* ks, uint8_t* vc, u
   if ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) return cudaErrorInvalidValue;   // code rows are read and written as 16-byte vectors
   const long long slots = pages * PAGE * HKV, threads = slots * 2 * (D / 32);
   if (threads == 0) return cudaSuccess;
+  if (dir == 0 ? staged_launch<true>(kc, ks, vc, vs, aos, slots, HKV, PAGE, D, slot_bytes, flags, s)
+               : staged_launch<false>(kc, ks, vc, vs, aos, slots, HKV, PAGE, D, slot_bytes, 0, s))
+    return cudaGetLastError();
+  // (slot arrays that are not 16-byte aligned, slots beyond 768 bytes, more than 2^31 slots: one thread per group)
   const long long blocks = (threads + 255) / 256;
   if (blocks > 0x7fffffffll) return cudaErrorInvalidValue;
   if (dir == 0)

@@ -57,3 +57,35 @@ def test_layout_kernels_match_the_fixture_byte_for_byte(D):
     # a cache that came in from upstream decodes as it is: round trip through both kernels
     back = uq_cuda.from_upstream_layout(dev(got), D)
     assert np.array_equal(back[0].cpu().numpy(), Z[f"d{D}_canon_kc"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,HKV,PAGE,pages,pad", [(128, 8, 64, 5, 0), (128, 3, 16, 7, 8), (128, 5, 48, 3, 1), (128, 2, 16, 9, 2),
+                                                    (64, 1, 16, 5, 0), (64, 7, 32, 3, 3), (256, 4, 16, 3, 0), (256, 3, 80, 2, 5),
+                                                    (128, 1, 16, 1, 0), (128, 2, 64, 1, 700)])
+def test_layout_kernels_on_sizes_that_do_not_line_up(D, HKV, PAGE, pages, pad):
+    """Slot counts that are not a multiple of a block's 64, slot sizes whose pieces are only 2- or 1-byte aligned inside the
+    slot, head counts and page sizes that are not powers of two, a slot too large for the staged kernel: against the numpy
+    restatement, both directions, with a fifth of the groups all zero and minus-zero codes in the data."""
+    from all_quant_b200 import uq_cuda
+    rng = np.random.default_rng(D + HKV + PAGE + pad)
+    G = D // 32
+    kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    for c in (kc, vc):
+        z = rng.random((pages, HKV, PAGE, G)) < 0.2
+        c.reshape(pages, HKV, PAGE, G, 16)[z] = 0
+        c.reshape(pages, HKV, PAGE, G, 16)[rng.random((pages, HKV, PAGE, G)) < 0.1] = 0x88
+    ks = rng.integers(1, 255, (pages, HKV, PAGE, G), dtype=np.uint8)
+    vs = rng.integers(1, 255, (pages, HKV, PAGE, G), dtype=np.uint8)
+    slot = D + 2 * G + pad
+    dev = lambda a: torch.from_numpy(a).cuda()
+    d = tuple(dev(a) for a in (kc, ks, vc, vs))
+    for canon, sentinel in ((False, False), (True, True)):
+        out = torch.full((pages, PAGE, HKV, slot), 0xCD, dtype=torch.uint8, device="cuda")
+        got = uq_cuda.to_upstream_layout(*d, slot_bytes=slot, canon_negzero=canon, zero_sentinel=sentinel, out=out).cpu().numpy()
+        assert np.array_equal(got, O.to_upstream(kc, ks, vc, vs, slot_bytes=slot, canon=canon, sentinel=sentinel))
+    plain = O.to_upstream(kc, ks, vc, vs, slot_bytes=slot)
+    plain[..., D + 2 * G:] = 0x5A                       # whatever the allocator left in the padding is ignored on the way in
+    for a, b in zip(uq_cuda.from_upstream_layout(dev(plain), D), (kc, ks, vc, vs)):
+        assert np.array_equal(a.cpu().numpy(), b)
