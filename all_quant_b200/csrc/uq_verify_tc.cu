@@ -422,6 +422,25 @@ __device__ __noinline__ uint32_t draft_rows(const int32_t* tree_mask, int K, int
 }
 
 // ---------------------------------------------------------------------------------------------- layout
+struct Seg {
+  int b, hk, t0, t1;   // tiles [t0, t1) of item (b, hk)
+  int slot;            // partial slot of this segment
+  int nseg;            // slots the item uses (valid when t0 == 0)
+  int ntiles;          // tiles of the whole item
+};
+
+// A CTA's segments, worked out once at set-up by one warp (a candidate item per lane) and read by every role from shared
+// memory: walking the list costs a role over a microsecond per call (an out-of-line call on a struct in local memory;
+// inlined, its registers would be held across every role's tile loop), which each role used to pay before its first
+// tile, between segments and once more to learn that the list had ended.
+constexpr int kSegCap = 32;
+struct SegList {
+  int n;          // segments listed
+  int more;       // 1: the CTA's chunk goes on past the listed candidates (roles continue with the walker from pos_after / it_after)
+  int pos_after, it_after;
+  Seg seg[kSegCap];
+};
+
 template <int D, int NT, int FMT = 0>
 struct Cfg {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64 / 128 / 256");
@@ -481,7 +500,8 @@ struct Cfg {
   static constexpr int oPrefix = oRef + 8 * kKeys * 2;
   static constexpr int kMaxB = 1024;
   static constexpr int oRedo = oPrefix + (kMaxB + 1) * 4;   // kRedoWords words of per-segment "run again" bits, then one word "any bit set"
-  static constexpr int kSmem = oRedo + (kRedoWords + 1) * 4;
+  static constexpr int oSegs = oRedo + (kRedoWords + 1) * 4;   // the CTA's first kSegCap segments (SegList), listed once at set-up
+  static constexpr int kSmem = oSegs + (int)sizeof(SegList);
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // TMEM columns
   static constexpr int kKCols = kBS ? 4 : D / 2;         // fp16 A operand of S^T: two channels per 32-bit column; block-scaled: the keys' scale bytes
@@ -515,12 +535,6 @@ struct RingPos {
 };
 
 // ---------------------------------------------------------------------------------------------- work list
-struct Seg {
-  int b, hk, t0, t1;   // tiles [t0, t1) of item (b, hk)
-  int slot;            // partial slot of this segment
-  int nseg;            // slots the item uses (valid when t0 == 0)
-  int ntiles;          // tiles of the whole item
-};
 
 // The list is cut in WEIGHTED units: an item of n tiles counts n + kSegW, the extra units standing for what the start of
 // a segment costs (query conversion, first-tile reference, epilogue), so that a CTA whose chunk crosses into a second item
@@ -533,6 +547,17 @@ struct Seg {
 #define UQ_SEGW 8
 #endif
 __host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? UQ_SEGW64 : UQ_SEGW; }
+
+// n / d for a quotient known to be small (below 2^16: a CTA index, a head index): one fp32 division and a correction
+// instead of the 32-bit integer division's long dependent sequence.  0 <= n < 2^31, 0 < d; the fp32 estimate is off by
+// less than 2^-6 for such quotients, so at most one step either way puts it right.
+UQ_DEV int small_quotient(int n, int d) {
+  int q = (int)__fdividef((float)n, (float)d);
+  const long long r = (long long)n - (long long)q * d;
+  if (r < 0) q--;
+  else if (r >= d) q++;
+  return q;
+}
 
 struct Walker {
   const int* prefix;   // prefix[b] = weighted units of sequences < b (one kv head): tiles + kSegW per non-empty sequence
@@ -552,6 +577,59 @@ struct Walker {
     it = 0;
   }
   UQ_DEV int item_tiles(int item) const { const int b = item / HKV; return max(prefix[b + 1] - prefix[b] - kSegW, 0); }
+  // Past the listed segments (out of line, like next(): the roles' loops should not carry this code or its registers)
+  __device__ __noinline__ bool next_after(Seg& s, const SegList* L, bool& walking, const int* pre, int B_, int HKV_, int ns_eff, int chunk_min, int seg_w) {
+    if (!walking) {
+      init(pre, B_, HKV_, ns_eff, chunk_min, seg_w);
+      if (per_item) it = L->it_after; else pos = min(L->pos_after, end);
+      walking = true;
+    }
+    return next(s);
+  }
+  // The same walk as next(), done by one warp in one step: lane j takes the j-th candidate item from the chunk's start
+  // (its item index is known without the items before it: unit position of item (b, hk) = HKV * prefix[b] + hk * width of b),
+  // the lanes whose item has tiles in the chunk are the segments, in lane order.  Called after init() by all 32 lanes.
+  UQ_DEV void list(SegList* L, int lane) {
+    Seg s;
+    bool valid = false, beyond = false;   // beyond: this candidate starts at or past the chunk's end (so do all later ones)
+    if (per_item) {
+      const int item = cta + lane * (int)gridDim.x;
+      beyond = item >= nitems;
+      if (!beyond) {
+        const int n = item_tiles(item);
+        if (n > 0) { s.b = item / HKV; s.hk = item - s.b * HKV; s.t0 = 0; s.t1 = n; s.slot = 0; s.nseg = 1; s.ntiles = n; valid = true; }
+      }
+    } else if (pos < end) {
+      int lo = 0, hi = B;                 // sequence containing unit `pos`: largest b with HKV * prefix[b] <= pos
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (HKV * prefix[mid] <= pos) lo = mid; else hi = mid;
+      }
+      const int nv0 = prefix[lo + 1] - prefix[lo];
+      const int item = lo * HKV + small_quotient(pos - HKV * prefix[lo], nv0) + lane;
+      const int b = small_quotient(item, HKV), hk = item - b * HKV;
+      beyond = b >= B;
+      if (!beyond) {
+        const int nv = prefix[b + 1] - prefix[b], n = nv - kSegW;
+        const int start = HKV * prefix[b] + hk * nv, first = start + kSegW;
+        beyond = start >= end;
+        if (!beyond && nv > 0) {
+          const int t0 = max(pos, first) - first, t1 = min(first + n, end) - first;
+          if (t1 > t0) {
+            const int c0 = small_quotient(first, chunk);
+            s.b = b; s.hk = hk; s.ntiles = n; s.t0 = t0; s.t1 = t1; s.slot = cta - c0;
+            s.nseg = small_quotient(first + n - 1, chunk) - c0 + 1;
+            valid = true;
+          }
+        }
+        if (lane == 31 && !beyond) { L->pos_after = start + nv; L->it_after = 0; }   // where a 33rd candidate would begin
+      }
+    } else beyond = true;
+    if (per_item && lane == 31 && !beyond) { L->pos_after = 0; L->it_after = cta + 31 * (int)gridDim.x; }
+    const unsigned vm = __ballot_sync(0xffffffffu, valid), bm = __ballot_sync(0xffffffffu, beyond);
+    if (valid) L->seg[__popc(vm & ((1u << lane) - 1u))] = s;
+    if (lane == 0) { L->n = __popc(vm); L->more = (bm >> 31) ? 0 : 1; }
+  }
   __device__ __noinline__ bool next(Seg& s) {
     if (per_item) {
       for (it += (int)gridDim.x; it < nitems; it += (int)gridDim.x) {
@@ -679,6 +757,13 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     prefix[0] = 0;
     for (int b = 0; b < p.B; b++) prefix[b + 1] += prefix[b];
   }
+  SegList* seglist = reinterpret_cast<SegList*>(sm + C::oSegs);
+  if (warp == 0) {   // the CTA's segments, once, for every role (the walker's struct lives in registers here)
+    __syncwarp();
+    Walker w0;
+    w0.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min, seg_weight(NT));
+    w0.list(seglist, lane);
+  }
   if (warp == kWarpMma) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sm_a + C::oTmemSlot) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -702,7 +787,15 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
   int mcur = 0, nvote = 0;         // softmax role: live copy of the double-buffered references, rendezvous count
   float csc0 = x.sc2;
   for (int pass = 0; pass < 2; pass++) {
-  wk.init(prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min, seg_weight(NT));
+  // the listed segments first; a chunk that goes on past them (more than kSegCap candidate items: very short sequences)
+  // is walked from there
+  int seg_at = 0;
+  bool walking = false;
+  auto next_seg = [&](Seg& s) -> bool {
+    if (seg_at < seglist->n) { s = seglist->seg[seg_at++]; return true; }
+    if (!seglist->more) return false;
+    return wk.next_after(s, seglist, walking, prefix, p.B, p.HKV, x.ns_eff, prm.chunk_min, seg_weight(NT));
+  };
   int ord = -1;                    // ordinal of the segment in the CTA's list
   // does this pass run segment `ord`?  (pass 1: the marked ones)
   auto take = [&]() -> bool { ord++; return pass == 0 || (ord < 32 * kRedoWords && ((redo[ord >> 5] >> (ord & 31)) & 1u)); };
@@ -718,7 +811,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     const int spp_sh = __ffs(spp) - 1;
     UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)unit * C::kCodeRow, page_bytes_scales = (uint32_t)unit * C::kScaleB;
-    while (ok && wk.next(sg)) {
+    while (ok && next_seg(sg)) {
       if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
@@ -785,7 +878,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     // A = V^T: M = 128 channels = two 64-channel halves (leading-dimension offset = one half).  head_dim 64 has one half only:
     // offset 0 makes the upper 64 accumulator lanes a copy of the lower ones, which the epilogue ignores.
     const uint64_t v_desc = smem_desc(sm_a + C::oV, D == 64 ? 0 : C::kVHalf, 1024), p_desc = smem_desc(sm_a + C::oP, C::kVHalf, 1024);
-    while (ok && wk.next(sg)) {
+    while (ok && next_seg(sg)) {
       if (!take()) continue;
       const int n = sg.t1 - sg.t0, c0 = cnt;
       if (elect_one()) {
@@ -863,7 +956,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     RingPos<kSB> sp;
     rp.set(cnt);
     sp.set(cnt);
-    while (ok && wk.next(sg)) {
+    while (ok && next_seg(sg)) {
       if (!take()) continue;
       for (int t = sg.t0; t < sg.t1; t++, cnt++, rp.next(), sp.next()) {
         const int stage = rp.slot, buf = sp.slot;
@@ -937,7 +1030,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     RingPos<kVB> vp;
     rp.set(cnt);
     vp.set(cnt);
-    while (ok && wk.next(sg)) {
+    while (ok && next_seg(sg)) {
       if (!take()) continue;
       int off;
       const int n_loc = uq_n_local(p, x, sg.b, &off);
@@ -1058,12 +1151,12 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
       tc_wait_st();
     };
     // items without a single key: nobody computes them, their slots must read as empty
-    for (int it = blockIdx.x; pass == 0 && it < wk.nitems; it += gridDim.x) {
-      if (wk.item_tiles(it) != 0) continue;
+    for (int it = blockIdx.x; pass == 0 && it < p.B * p.HKV; it += gridDim.x) {
+      { const int b = it / p.HKV; if (prefix[b + 1] - prefix[b] != 0) continue; }   // (an item with keys has tiles + the start-up weight)
       for (int i = st; i < x.ns_eff * rows; i += kSm)
         p.ml[uq_slot(p, it / p.HKV, it % p.HKV, i / rows) * x.BM + i % rows] = -INFINITY;
     }
-    while (ok && wk.next(sg)) {
+    while (ok && next_seg(sg)) {
       if (!take()) continue;
       UQ_TRACE_SEG(0)
       const bool careful = pass == 1 || ord >= 32 * kRedoWords;

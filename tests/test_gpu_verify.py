@@ -165,6 +165,34 @@ def test_page_sizes_from_16_to_1024_tokens(PAGE, D, fmt):
         check_close(out.float().cpu().numpy() / mx, ref / mx, f"PAGE={PAGE} D={D} fmt={fmt} nsplit={nsplit}")
 
 
+@pytest.mark.parametrize("B,HKV,G,K", [(700, 8, 2, 2), (1000, 4, 8, 1), (300, 8, 8, 8)])
+def test_many_short_sequences_put_more_segments_on_a_cta_than_its_list_holds(B, HKV, G, K):
+    """Hundreds of sequences of one or two tiles (some empty): a CTA's share of the work list then spans more items than the 32
+    candidates listed at set-up, so every role goes on with the walker from where the list ends; with one partial slot per item
+    (nsplit 1) the items are dealt out by index, the list's other form."""
+    rng = np.random.default_rng(B + HKV)
+    D, PAGE = 128, 64
+    HQ = HKV * G
+    sl = rng.integers(1, 4 * PAGE, B).astype(np.int32)
+    sl[rng.random(B) < 0.05] = 0
+    sl[rng.random(B) < 0.05] = K
+    npg = -(-int(sl.max()) // PAGE)
+    pages = B * npg
+    kc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    vc = rng.integers(0, 256, (pages, HKV, PAGE, D // 2), dtype=np.uint8)
+    ks = rng.integers(125, 130, (pages, HKV, PAGE, D // 32)).astype(np.uint8)
+    vs = rng.integers(125, 130, (pages, HKV, PAGE, D // 32)).astype(np.uint8)
+    bt = rng.permutation(pages).astype(np.int32).reshape(B, npg)
+    qb = O.bf16_bits(0.3 * rng.standard_normal((B, K, HQ, D)).astype(np.float32))
+    ref = O.reference(qb, kc, ks, vc, vs, bt, sl)
+    q = dev(qb.view(np.int16), torch.bfloat16)
+    mx = np.abs(ref).max()
+    for nsplit in (None, 1, 2):
+        out = uq_cuda.uq_decode_cuda(q, dev(kc), dev(ks), dev(vc), dev(vs), dev(bt), dev(sl), nsplit=nsplit)
+        assert uq_cuda.last_status() == (0, 0, 0, 0) and uq_cuda.last_path() == 2
+        check_close(out.float().cpu().numpy() / mx, ref / mx, f"B={B} HKV={HKV} nsplit={nsplit}")
+
+
 def test_late_outliers_take_the_second_pass():
     """Keys whose scores (and V scales) dwarf those of a segment's first tile arrive late in every sequence: the quick path
     marks the segment and the careful pass redoes it; outputs follow the oracle on the same bytes."""
