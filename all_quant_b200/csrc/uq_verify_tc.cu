@@ -1543,19 +1543,26 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
         const float* mr = mref + mcur * NT;
         const float osc = pow2_f32((int)wr[4 + mcur] - 127);   // O^T was accumulated relative to the segment's V reference
         bool bad = false;   // an infinity or a NaN in the sums: a probability or a V value overflowed fp16 somewhere in the segment
+        // a warp's threads share their HW rows: lane i works out row r0 + i's factor osc / sum once (-1: the row saw nothing),
+        // the stores fetch it by shuffle
+        float f_mine = -1.f;
+        if (lane < HW && r0 + lane < rows) {
+          const int r = r0 + lane;
+          const float lr = (lsum[r] + lsum[NT + r]) + (lsum[2 * NT + r] + lsum[3 * NT + r]);
+          bad = !(lr <= 3.0e38f);
+          if (lr > 0.f) f_mine = __fdividef(osc, lr);
+        }
 #pragma unroll
         for (int db = 0; db < C::kDB; db++) {
           float ov[HW];
           load_scores(lane_addr + C::cO + db * NT + r0, ov);   // accumulator lane kk of block db = channel 128 db + kk
-          if (db * 128 + kk < D) {                              // head_dim 64: the upper 64 lanes are a copy
 #pragma unroll
-            for (int i = 0; i < HW; i++) {
-              const int r = r0 + i;
-              if (r < rows) {
-                const float lr = (lsum[r] + lsum[NT + r]) + (lsum[2 * NT + r] + lsum[3 * NT + r]);
-                bad |= !(fabsf(ov[i]) <= 3.0e38f) || !(lr <= 3.0e38f);
-                mo[(size_t)r * D + db * 128 + kk] = lr > 0.f ? ov[i] * __fdividef(osc, lr) : 0.f;
-              }
+          for (int i = 0; i < HW; i++) {
+            const float f = __shfl_sync(0xffffffffu, f_mine, i);
+            const int r = r0 + i;
+            if (r < rows && db * 128 + kk < D) {                // head_dim 64: the upper 64 lanes are a copy
+              bad |= !(fabsf(ov[i]) <= 3.0e38f);
+              mo[(size_t)r * D + db * 128 + kk] = f >= 0.f ? ov[i] * f : 0.f;
             }
           }
         }
