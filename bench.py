@@ -513,12 +513,14 @@ def run_ours(args, cfg):
     q, bt, sl, caches, case, fmt, nsplit = run.q, run.bt, run.sl, run.caches, run.case, run.fmt, run.nsplit
     step = run.step
 
-    for i in range(max(3, args.warmup)):
-        step(i)
-    barrier()
-    # ---- device-resident timing: exactly `steps` steps
-    n0 = uq_cuda.launch_count()
+    # ---- device-resident timing: exactly `steps` steps.  The clock sampler is a child process that takes a few hundred
+    # milliseconds to come up, during which the GPU would idle down: the warm-up steps run once it is sampling, directly
+    # before the timed region
     with ClockSampler(local) as clk:
+        for i in range(max(3, args.warmup)):
+            step(i)
+        barrier()
+        n0 = uq_cuda.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
