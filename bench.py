@@ -92,7 +92,7 @@ def peaks():
 
 # DRAM traffic of one launch of the attention kernel from the ncu capture summarised in the named file (dram__bytes_read.sum +
 # dram__bytes_write.sum of a half-size headline call, whose algorithmic bytes are given beside it); None = no capture on record
-TRAFFIC_PROFILE = {"source": "profiles/uq_verify_tc_kernel_ctx16384_K8_ncu_full.md", "dram_bytes": 147.2e6 + 21.1e6, "algorithmic_bytes": 142606336}
+TRAFFIC_PROFILE = {"source": "profiles/uq_verify_tc_kernel_ctx16384_K8_ncu_full.md", "dram_bytes": 145.7e6 + 12.5e6, "algorithmic_bytes": 142606336}
 
 
 def kv_bytes(cfg, seq_lens):
