@@ -205,8 +205,9 @@ __global__ void __launch_bounds__(128) uq_append_kernel(uint8_t* __restrict__ kc
 //     does) and moves no other value across or onto a boundary; an fp32 input takes 2^-e itself and the three half-way
 //     values are corrected by comparison.  The conversion keeps the sign of a negative value that rounds to zero, as
 //     the reference does (sign bit = y < 0); adding +0 turns y = -0 (an input -0, or an underflow) into +0 first.
-// Same bytes as the kernel above on every input (the tests run both on the same rows).  Not served here: rotated keys
-// (that transform wants a warp per row), inputs not aligned to 16 bytes, more than 2^31 pieces.
+// Same bytes as the kernel above on every input (the tests run both on the same rows), rotated keys included (the transform
+// runs across the D / 8 lanes of a row before anything else).  Not served here: inputs not aligned to 16 bytes, more than
+// 2^31 pieces.
 #ifndef UQ_BULK_THREADS
 #define UQ_BULK_THREADS 128
 #endif
@@ -233,6 +234,58 @@ struct Piece<float> {
   }
   UQ_DEV void values(float* x) const { x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w; }
 };
+// (set(): eight fp32 values rounded to the piece's type, the rounding the reference's transform applies to its result)
+template <typename T>
+UQ_DEV void piece_set(Piece<T>& pc, const float* x);
+template <>
+UQ_DEV void piece_set<float>(Piece<float>& pc, const float* x) {
+  pc.a = make_float4(x[0], x[1], x[2], x[3]);
+  pc.b = make_float4(x[4], x[5], x[6], x[7]);
+}
+template <>
+UQ_DEV void piece_set<__nv_bfloat16>(Piece<__nv_bfloat16>& pc, const float* x) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  pc.v = make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+UQ_DEV void piece_set<__half>(Piece<__half>& pc, const float* x) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const __half2 v = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  pc.v = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Orthonormal Walsh-Hadamard transform of rows of D channels whose lanes hold 8 consecutive channels each (D / 8 lanes per
+// row, aligned): the butterfly order of warp_fwht (stage h pairs (i, i + h) -> (a + b, a - b), h ascending): h = 1, 2, 4
+// inside the lane's eight values, h = 8 .. D / 2 across the row's lanes, then one division by (float)sqrt(D).
+UQ_DEV void piece_fwht(float (&x)[8], int D, int lane) {
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      if (!(i & h)) { const float a = x[i], b = x[i | h]; x[i] = a + b; x[i | h] = a - b; }
+    }
+  }
+  for (int m = 1; 8 * m < D; m <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float p = __shfl_xor_sync(0xffffffffu, x[i], m);
+      x[i] = (lane & m) ? p - x[i] : x[i] + p;
+    }
+  }
+  const float div = (float)sqrt((double)D);
+#pragma unroll
+  for (int i = 0; i < 8; i++) x[i] = __fdiv_rn(x[i], div);
+}
+
 template <>
 UQ_DEV float Piece<__nv_bfloat16>::amax() const {
   const uint32_t m0 = v.x & 0x7fff7fffu, m1 = v.y & 0x7fff7fffu, m2 = v.z & 0x7fff7fffu, m3 = v.w & 0x7fff7fffu;
@@ -290,7 +343,7 @@ UQ_DEV uint32_t div_magic(uint32_t n, uint32_t d, uint32_t m, uint32_t& rem) {
   return q;
 }
 
-template <typename T>
+template <typename T, bool kRot>
 __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict__ kc, uint8_t* __restrict__ ks, uint8_t* __restrict__ vc,
                                                              uint8_t* __restrict__ vs, const T* __restrict__ key, const T* __restrict__ value,
                                                              const int64_t* __restrict__ slots, uint32_t np, int HKV, uint32_t hkv_magic, int D,
@@ -311,6 +364,17 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
     const uint32_t p = p0 + 32u * j;
     if (p < np) pc[j].load(src + (size_t)p * 8);
     else pc[j].zero();
+  }
+  // rotated keys: every row of the key stream goes through the transform first and is rounded to the input's type, as the
+  // reference's function returns it; the pieces then hold the rotated row and everything below is unchanged
+  if (kRot && stream == 0) {
+#pragma unroll
+    for (int j = 0; j < NP; j++) {
+      float x[8];
+      pc[j].values(x);
+      piece_fwht(x, D, lane);
+      piece_set<T>(pc[j], x);
+    }
   }
   // Where the rows go: the warp's 32 * NP pieces are 4 .. 32 whole rows, lane L looks up row L (token, head, slot, page)
   // once and a piece fetches its row's answer by shuffle.  ~0 = no row (past the end, or a skipped token).
@@ -389,19 +453,22 @@ __global__ void __launch_bounds__(256) uq_append_bulk_kernel(uint8_t* __restrict
   else encode(std::false_type{});
 }
 
-// the bulk kernel serves: no rotation, pointers aligned for the vector loads, piece count within 32 bits
+// the bulk kernel serves: pointers aligned for the vector loads, piece count within 32 bits
 template <typename T>
 bool bulk_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const T* key, const T* value, const int64_t* slots, int T_tok, int HKV,
                  int D, int PAGE, int nstream, int flags, float c, cudaStream_t s) {
   const unsigned long long np = (unsigned long long)T_tok * HKV * (D / 8);
   const uintptr_t al = 15;
-  if ((flags & kRotateK) || np >= (1ull << 31) || ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & al)) return false;
+  if (np >= (1ull << 31) || ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & al)) return false;
   const uint32_t magic = HKV == 1 ? 0xffffffffu : (uint32_t)((1ull << 32) / (unsigned)HKV);
   int shift = -1;
   if ((PAGE & (PAGE - 1)) == 0) { shift = 0; while ((1 << shift) < PAGE) shift++; }
   const unsigned per_block = (UQ_BULK_THREADS / 32u) * 32u * bulk_pieces<T>();
   const dim3 grid((unsigned)((np + per_block - 1) / per_block), (unsigned)nstream);
-  uq_append_bulk_kernel<T><<<grid, UQ_BULK_THREADS, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
+  if (flags & kRotateK)
+    uq_append_bulk_kernel<T, true><<<grid, UQ_BULK_THREADS, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
+  else
+    uq_append_bulk_kernel<T, false><<<grid, UQ_BULK_THREADS, 0, s>>>(kc, ks, vc, vs, key, value, slots, (uint32_t)np, HKV, magic, D, PAGE, shift, (flags & kPaperRule) ? 1 : 0, c);
   return true;
 }
 
@@ -698,7 +765,7 @@ cudaError_t uq_append_dispatch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* v
       default: done = bulk_launch<__half>(kc, ks, vc, vs, (const __half*)key, (const __half*)value, slots, T, HKV, D, PAGE, nstream, flags, c, s); break;
     }
     if (done) return cudaGetLastError();
-    if (route == kRouteBulk) return cudaErrorInvalidValue;   // asked for by name and not served (rotated keys, alignment, size)
+    if (route == kRouteBulk) return cudaErrorInvalidValue;   // asked for by name and not served (alignment, size)
   }
   const int blocks = (int)((warps + 3) / 4);
   switch (dtype) {

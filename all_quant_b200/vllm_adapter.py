@@ -69,8 +69,9 @@ def _slots_for(workspace, B, K, HQ, HKV, D, n_pages, device):
     return want
 
 
-def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule="ceil", c=None):
+def append_kv(kc, ks, vc, vs, key, value, slot_mapping, *, rotate_k=False, rule="ceil", c=None, kernel=None):
     """Quantize new key/value [T, Hkv, D] and write them at flat slots (slot = physical_page * PAGE + offset), the
-    cache-append hook of an engine (reference uqmt/vllm_adapter.py:48-59); one kernel launch.  The keyword options are the
-    reference's configurable quantiser (uqmt/quant.py): Hadamard-rotated keys and the 'paper' scale rule."""
-    uq_cuda.append_kv(kc, ks, vc, vs, key, value, slot_mapping, rotate_k=rotate_k, rule=rule, c=c)
+    cache-append hook of an engine (reference uqmt/vllm_adapter.py:48-59); one kernel launch, a decode step's tokens or a
+    whole prompt's.  The keyword options are the reference's configurable quantiser (uqmt/quant.py): Hadamard-rotated keys and
+    the 'paper' scale rule; `kernel` as in uq_cuda.append_kv."""
+    uq_cuda.append_kv(kc, ks, vc, vs, key, value, slot_mapping, rotate_k=rotate_k, rule=rule, c=c, kernel=kernel)

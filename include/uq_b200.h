@@ -59,8 +59,8 @@ int uqb_append_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const 
  *               (scale_exponent, uqmt/quant.py:52-60; quantize_on_write(rule="paper", c), :197-206); c > 0.
  *   flags & 4 / flags & 8   take the bulk kernel / the kernel with one warp per row, whatever the size of the call (both
  *               write the same bytes; without either bit a call of 4096 or more rows x streams whose key / value pointers
- *               are 16-byte aligned and whose keys are not rotated goes to the bulk kernel, which runs a prompt's worth of
- *               rows at memory bandwidth; flags & 4 on a call the bulk kernel does not serve is cudaErrorInvalidValue).
+ *               are 16-byte aligned goes to the bulk kernel, which runs a prompt's worth of rows at memory bandwidth;
+ *               flags & 4 on a call the bulk kernel does not serve is cudaErrorInvalidValue).
  * flags = 0 is uqb_append_launch.  Bit-exact with quantize(fwht(key), rule, c) of the reference's CPU functions. */
 int uqb_append_ex_launch(uint8_t* kc, uint8_t* ks, uint8_t* vc, uint8_t* vs, const void* key, const void* value,
                          const int64_t* slots, int T, int HKV, int D, int PAGE, int dtype, int flags, float c, void* stream);

@@ -82,7 +82,8 @@ def test_fwht_kernel_bit_exact(D):
 @pytest.mark.parametrize("D", DIMS)
 @pytest.mark.parametrize("rule", ["ceil", "paper"])
 @pytest.mark.parametrize("rotate", [False, True])
-def test_append_options_bit_exact(D, rule, rotate):
+@pytest.mark.parametrize("kernel", ["rows", "bulk"])
+def test_append_options_bit_exact(D, rule, rotate, kernel):
     """append_kv(rotate_k, rule): the key stream equals quantize(fwht(key), rule) of the reference, the value stream
     quantize(value, rule) (values are never rotated)."""
     from all_quant_b200 import vllm_adapter as A
@@ -94,7 +95,7 @@ def test_append_options_bit_exact(D, rule, rotate):
     vc, vs = torch.zeros_like(kc), torch.zeros_like(ks)
     slots = torch.from_numpy(np.random.default_rng(3).permutation(pages * PAGE)[:T].astype(np.int64)).cuda()
     xd = torch.from_numpy(x).cuda()
-    A.append_kv(kc, ks, vc, vs, xd, xd, slots, rotate_k=rotate, rule=rule, c=float(Z["c"]))
+    A.append_kv(kc, ks, vc, vs, xd, xd, slots, rotate_k=rotate, rule=rule, c=float(Z["c"]), kernel=kernel)
     pg, at = (slots // PAGE).cpu(), (slots % PAGE).cpu()
     src = "rot" if rotate else "plain"
     assert np.array_equal(kc.cpu()[pg, :, at].numpy(), Z[f"d{D}_{src}_{rule}_codes"])
@@ -113,9 +114,11 @@ def test_bf16_keys_rotate_like_the_reference_function():
     want_c, want_s = O.quantize(torch.from_numpy(O.fwht(xb.float().numpy())).bfloat16().float().numpy(), "ceil")
     kc = torch.zeros(1, HKV, PAGE, D // 2, dtype=torch.uint8, device="cuda")
     ks = torch.zeros(1, HKV, PAGE, D // 32, dtype=torch.uint8, device="cuda")
-    uq_cuda.append_kv(kc, ks, torch.zeros_like(kc), torch.zeros_like(ks), xb.cuda(), xb.cuda(), torch.arange(T, device="cuda"), rotate_k=True)
-    assert np.array_equal(kc.cpu().numpy()[0, :, :T].transpose(1, 0, 2), want_c)
-    assert np.array_equal(ks.cpu().numpy()[0, :, :T].transpose(1, 0, 2), want_s)
+    for kernel in ("rows", "bulk"):
+        kc.zero_(); ks.zero_()
+        uq_cuda.append_kv(kc, ks, torch.zeros_like(kc), torch.zeros_like(ks), xb.cuda(), xb.cuda(), torch.arange(T, device="cuda"), rotate_k=True, kernel=kernel)
+        assert np.array_equal(kc.cpu().numpy()[0, :, :T].transpose(1, 0, 2), want_c)
+        assert np.array_equal(ks.cpu().numpy()[0, :, :T].transpose(1, 0, 2), want_s)
 
 
 @pytest.mark.gpu

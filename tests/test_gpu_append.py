@@ -188,12 +188,37 @@ def test_bulk_kernel_writes_the_bytes_of_the_row_kernel_and_the_oracle(D, HKV, P
         assert np.array_equal(codes, ref_c) and np.array_equal(scales, ref_s)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,HKV", [(64, 3), (128, 8), (256, 2)])
+def test_bulk_kernel_rotates_keys_like_the_row_kernel(D, HKV, dtype):
+    """Rotated keys (the transform across the D / 8 lanes of a row, its result rounded to the input's type) and unrotated
+    values in one call: the bulk kernel's bytes equal the row kernel's, whose rotation is pinned to the reference's function."""
+    g = torch.Generator(device="cuda").manual_seed(7 * D + HKV)
+    T, PAGE = 777, 32
+    pages = (T + PAGE - 1) // PAGE
+    k = (torch.randn(T, HKV, D, generator=g, device="cuda") * torch.exp(torch.randn(1, HKV, D, generator=g, device="cuda"))).to(dtype)
+    v = torch.randn(T, HKV, D, generator=g, device="cuda").to(dtype)
+    slots = torch.randperm(pages * PAGE, generator=g, device="cuda")[:T]
+    out = {}
+    for kernel in KERNELS:
+        kc = torch.zeros(pages, HKV, PAGE, D // 2, dtype=torch.uint8, device="cuda")
+        ks = torch.zeros(pages, HKV, PAGE, D // 32, dtype=torch.uint8, device="cuda")
+        vc, vs = kc.clone(), ks.clone()
+        uq_cuda.append_kv(kc, ks, vc, vs, k, v, slots, rotate_k=True, rule="paper", kernel=kernel)
+        torch.cuda.synchronize()
+        out[kernel] = [t.cpu().numpy() for t in (kc, ks, vc, vs)]
+    for a, b in zip(out["rows"], out["bulk"]):
+        assert np.array_equal(a, b)
+    assert out["bulk"][0].any() and out["bulk"][2].any()
+
+
 def test_bulk_kernel_named_for_a_call_it_does_not_serve_is_an_error():
     kc = torch.zeros(4, 1, 16, 64, dtype=torch.uint8, device="cuda")
     ks = torch.zeros(4, 1, 16, 4, dtype=torch.uint8, device="cuda")
-    x = torch.randn(8, 1, 128, device="cuda")
+    x = torch.randn(8 * 128 + 1, device="cuda")[1:].view(8, 1, 128)   # contiguous, 4 bytes off a 16-byte boundary
     with pytest.raises(RuntimeError):
-        uq_cuda.append_kv(kc, ks, kc.clone(), ks.clone(), x, x, torch.arange(8, device="cuda"), rotate_k=True, kernel="bulk")
+        uq_cuda.append_kv(kc, ks, kc.clone(), ks.clone(), x, x, torch.arange(8, device="cuda"), kernel="bulk")
+    uq_cuda.append_kv(kc, ks, kc.clone(), ks.clone(), x, x, torch.arange(8, device="cuda"))          # by size: the row kernel takes it
     with pytest.raises(ValueError):
         uq_cuda.append_kv(kc, ks, kc.clone(), ks.clone(), x, x, torch.arange(8, device="cuda"), kernel="both")
 
