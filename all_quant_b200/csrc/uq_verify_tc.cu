@@ -542,14 +542,17 @@ struct RingPos {
 // The list is cut in WEIGHTED units: an item of n tiles counts n + kSegW, the extra units standing for what the start of
 // a segment costs (query conversion, first-tile reference, epilogue), so that a CTA whose chunk crosses into a second item
 // gets correspondingly fewer tiles and all CTAs finish together.  Measured from per-CTA exit times: about twelve tiles'
-// time at 64 rows, eight below.
+// time at 64 rows, eight at 32, five at 16.
 #ifndef UQ_SEGW64
 #define UQ_SEGW64 12
 #endif
 #ifndef UQ_SEGW
 #define UQ_SEGW 8
 #endif
-__host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? UQ_SEGW64 : UQ_SEGW; }
+#ifndef UQ_SEGW16
+#define UQ_SEGW16 5    // up to 16 rows: CTAs with a second segment finished 1.7 us before the others at 8
+#endif
+__host__ __device__ constexpr int seg_weight(int NT) { return NT >= 64 ? UQ_SEGW64 : (NT <= 16 ? UQ_SEGW16 : UQ_SEGW); }
 
 // n / d for a quotient known to be small (below 2^16: a CTA index, a head index): one fp32 division and a correction
 // instead of the 32-bit integer division's long dependent sequence.  0 <= n < 2^31, 0 < d; the fp32 estimate is off by
