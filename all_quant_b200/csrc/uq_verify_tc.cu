@@ -208,14 +208,33 @@ UQ_DEV void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "me
 UQ_DEV void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 UQ_DEV void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
 
+// The cache is read once per call and is larger than L2: its lines are marked "evict first", so that streaming it does not
+// push out what every call comes back to (the queries, the page table, the partials the combine kernel reads, the kernel's
+// own instructions).
+#ifndef UQ_EVICT_FIRST
+#define UQ_EVICT_FIRST 1
+#endif
+UQ_DEV uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 // 2-D tiled TMA load: box (inner 0.., rows y..) of the tensor map into shared memory, bytes counted on `bar`.
-UQ_DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+UQ_DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t pol) {
+  if (UQ_EVICT_FIRST)
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol) : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 // contiguous bulk copy (scale pages)
-UQ_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+UQ_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+  if (UQ_EVICT_FIRST)
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
+  else
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 // shared-memory matrix descriptor, 128-byte swizzle (sm_100 format: version bit 46, layout type 2 at bit 61)
@@ -817,6 +836,7 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
     const int spp_sh = __ffs(spp) - 1;
     UQ_PROF_DECL
     const uint32_t page_bytes_codes = (uint32_t)unit * C::kCodeRow, page_bytes_scales = (uint32_t)unit * C::kScaleB;
+    const uint64_t l2pol = l2_evict_first_policy();
     while (ok && next_seg(sg)) {
       if (!take()) continue;
       int off;
@@ -847,10 +867,10 @@ uq_verify_tc_kernel(const __grid_constant__ Params prm, const __grid_constant__ 
           const long long row0 = ((long long)pid * p.HKV + sg.hk) * p.PAGE + in_page * unit;
           const uint32_t fb = bar_raw_full(stage);
           // block-scaled: the K map unpacks (a page lands as PAGE x 128 bytes); the bytes counted on the barrier are the packed ones
-          if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, (int)row0, fb);
-          if (side & 2) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, (int)row0, fb);
-          if (side & 4) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
-          if (side & 8) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb);
+          if (side & 1) tma_load_2d(dst + lane * (C::kBS ? 2 : 1) * page_bytes_codes, &map_kc, 0, (int)row0, fb, l2pol);
+          if (side & 2) tma_load_2d(dst + C::kOffVC + lane * page_bytes_codes, &map_vc, 0, (int)row0, fb, l2pol);
+          if (side & 4) bulk_load(dst + C::kOffKS + lane * page_bytes_scales, p.ks + (size_t)row0 * C::kScaleB, page_bytes_scales, fb, l2pol);
+          if (side & 8) bulk_load(dst + C::kOffVS + lane * page_bytes_scales, p.vs + (size_t)row0 * C::kScaleB, page_bytes_scales, fb, l2pol);
         }
       }
     }
